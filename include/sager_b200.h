@@ -1,0 +1,180 @@
+/*
+ * sager_b200.h - C ABI of libsager_b200.so: the B200 (sm_100a) implementation of
+ * SAGER's Q4_K mixture-of-experts hot path.
+ *
+ * Every function replaces one launcher of the reference's device interface
+ * (include/sager/kernels/cuda_ops.hpp, namespace sager::cuda); the citation
+ * beside each declaration names it. Parameter lists are the reference's, with
+ * three mechanical changes that make them C: block types become `const void*`
+ * (Q4_K super-blocks of 144 bytes, Q8_K activation blocks of 276 bytes, layouts
+ * as in include/sager/kernels/q4_k.hpp:45-63), `cudaStream_t` becomes `void*`,
+ * and the return type is `int` instead of `void` (0 = launched; otherwise one
+ * of the SGR_E* codes - argument validation only, nothing is synchronised).
+ * include/sager_b200_shim.hpp turns these back into the C++ signatures.
+ *
+ * Conventions kept from the reference (cuda_ops.hpp:1-14): all calls are
+ * stream-ordered and never synchronise; all buffers are caller-owned device
+ * pointers; per-step values (row counts, tile counts, residency) are read from
+ * fixed-address device memory, so every call is legal inside stream capture.
+ * fp16 values travel as uint16_t. A null pointer-table entry means "expert
+ * not resident": its output rows are written as zero and, for the gate/up
+ * call, the expert id is posted to the mailbox.
+ */
+#ifndef SAGER_B200_H_
+#define SAGER_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SGR_OK 0
+#define SGR_EARG 1         /* null pointer, non-positive size, k not a multiple of 256 */
+#define SGR_EALIGN 2       /* activation blocks must be 4-byte aligned, fp16 rows 2-byte */
+#define SGR_EUNSUPPORTED 3 /* shape outside what the kernels were built for */
+#define SGR_ELAUNCH 4      /* the CUDA runtime refused the launch */
+#define SGR_EGEOMETRY 5    /* fused entry point: geometry mismatch (refused, never misindexed) */
+
+int sgr_abi_version(void);
+/* Device status word of the current device: non-zero after a bounded device-side
+ * wait gave up. Synchronises; diagnostics only. clear != 0 resets it. */
+int sgr_status(int clear);
+
+/* ---- activation quantiser ------------------------------------------------------ */
+/* cuda_ops.hpp:272  quantize_q8_k(x_f16, out, n, stream) */
+int sgr_quantize_q8_k(const uint16_t* x_f16, void* out_q8, long long n, void* stream);
+/* cuda_ops.hpp:235  quantize_q8_k_n(x_f16, out, d_rows, row_mult, n_max, stream) */
+int sgr_quantize_q8_k_n(const uint16_t* x_f16, void* out_q8, const int* d_rows, int row_mult,
+                        int n_max, void* stream);
+
+/* ---- Q4_K x Q8_K GEMV family --------------------------------------------------- */
+/* cuda_ops.hpp:41   gemv_q4_k_q8 (fp32 out) */
+int sgr_gemv_q4_k_q8(const void* w, const void* x_q8, float* y, int n_rows, int k, void* stream);
+/* cuda_ops.hpp:53   gemv_q4_k_q8_f16out */
+int sgr_gemv_q4_k_q8_f16out(const void* w, const void* x_q8, uint16_t* y, int n_rows, int k,
+                            void* stream);
+/* cuda_ops.hpp:60   gemv_ptrs_q4_k_q8_f16out: y[e*rows_per + r]; every pointer reads
+ * the same activation row, exactly as the reference kernel does. */
+int sgr_gemv_ptrs_q4_k_q8_f16out(const void* const* ptrs, const void* x_q8, uint16_t* y,
+                                 int n_ptrs, int rows_per, int k, void* stream);
+/* cuda_ops.hpp:67   gemv_q4_k_q8_f16out_batched: y[tok*n_rows + row] */
+int sgr_gemv_q4_k_q8_f16out_batched(const void* w, const void* x_q8, uint16_t* y, int n_rows,
+                                    int k, int n_tokens, void* stream);
+/* cuda_ops.hpp:72   gemv_q4_k_q8_batched (fp32 out) */
+int sgr_gemv_q4_k_q8_batched(const void* w, const void* x_q8, float* y, int n_rows, int k,
+                             int n_tokens, void* stream);
+/* cuda_ops.hpp:88   gemv_q4_k_q8_f16out_mtok */
+int sgr_gemv_q4_k_q8_f16out_mtok(const void* w, const void* xq, uint16_t* y, int n_rows, int k,
+                                 int n_tokens, void* stream);
+/* cuda_ops.hpp:95   mmq_q4_k_q8_f16out */
+int sgr_mmq_q4_k_q8_f16out(const void* w, const void* xq, uint16_t* y, int n_rows, int k,
+                           int n_tokens, void* stream);
+/* cuda_ops.hpp:100  mmq2_q4_k_q8_f16out (gate + up in one launch) */
+int sgr_mmq2_q4_k_q8_f16out(const void* wg, const void* wu, const void* xq, uint16_t* yg,
+                            uint16_t* yu, int n_rows, int k, int n_tokens, void* stream);
+/* cuda_ops.hpp:186  gemv2_q4_k_q8_f16out_mtok */
+int sgr_gemv2_q4_k_q8_f16out_mtok(const void* wg, const void* wu, const void* xq, uint16_t* yg,
+                                  uint16_t* yu, int n_rows, int k, int n_tokens, void* stream);
+/* cuda_ops.hpp:195  gemv_grouped2_q4_k_q8_f16out_mtok (host plan) */
+int sgr_gemv_grouped2_q4_k_q8_f16out_mtok(const void* const* wg, const void* const* wu,
+                                          const int* off, const int* m, const int* tile_base,
+                                          const int* job_of_tile, int n_tiles, const void* xq,
+                                          uint16_t* yg, uint16_t* yu, int n_rows, int k,
+                                          int tok_per, void* stream);
+/* cuda_ops.hpp:203  gemv_grouped_q4_k_q8_f16out_mtok (host plan, down projection) */
+int sgr_gemv_grouped_q4_k_q8_f16out_mtok(const void* const* w, const int* off, const int* m,
+                                         const int* tile_base, const int* job_of_tile,
+                                         int n_tiles, const void* xq, uint16_t* y, int n_rows,
+                                         int k, int tok_per, void* stream);
+/* cuda_ops.hpp:240  gemv_grouped2_tab_q4_k_q8_f16out_mtok (device plan + pointer table) */
+int sgr_gemv_grouped2_tab_q4_k_q8_f16out_mtok(const void* const* wg_tab,
+                                              const void* const* wu_tab, const int* off,
+                                              const int* toff, const int* meta, int* mail,
+                                              int* mail_n, int tiles_max, const void* xq,
+                                              uint16_t* yg, uint16_t* yu, int n_rows, int k,
+                                              int n_expert, int tok_per, void* stream);
+/* cuda_ops.hpp:247  gemv_grouped_tab_q4_k_q8_f16out_mtok (device plan, down projection) */
+int sgr_gemv_grouped_tab_q4_k_q8_f16out_mtok(const void* const* w_tab, const int* off,
+                                             const int* toff, const int* meta, int tiles_max,
+                                             const void* xq, uint16_t* y, int n_rows, int k,
+                                             int n_expert, int tok_per, void* stream);
+/* Parity probe, no counterpart launcher: the raw int32 sub-block dots of one
+ * activation row, out[(row*nb + blk)*8 + s] - the unit src/kernels/cuda/q4_k.cu:38-53
+ * and src/kernels/cpu/q4_avx2.cpp:99-119 both compute. */
+int sgr_q4k_subblock_dots(const void* w, const void* x_q8, int* out, int n_rows, int k,
+                          void* stream);
+
+/* ---- router --------------------------------------------------------------------- */
+/* cuda_ops.hpp:277  gemv_f32_out_f16x */
+int sgr_gemv_f32_out_f16x(const float* w_f32, const uint16_t* x_f16, float* y, int n_rows, int k,
+                          void* stream);
+/* cuda_ops.hpp:77   gemv_f32_out_f16x_batched */
+int sgr_gemv_f32_out_f16x_batched(const float* w_f32, const uint16_t* x_f16, float* y, int n_rows,
+                                  int k, int n_tokens, void* stream);
+/* cuda_ops.hpp:262  gemv_f32_out_f16x_mtok */
+int sgr_gemv_f32_out_f16x_mtok(const float* w_f32, const uint16_t* x_f16, float* y, int n_rows,
+                               int k, int n_tokens, void* stream);
+/* cuda_ops.hpp:351  router_topk */
+int sgr_router_topk(const float* logits, int* idx, float* weight, int n_expert,
+                    int n_expert_used, float shared_w, void* stream);
+/* cuda_ops.hpp:358  router_topk_batched */
+int sgr_router_topk_batched(const float* logits, int* idx, float* weight, int n_expert,
+                            int n_expert_used, int idx_stride, int n_rows, float shared_w,
+                            void* stream);
+/* cuda_ops.hpp:175  router_topk_fused (does not write slot K) */
+int sgr_router_topk_fused(const float* w_f32, const uint16_t* x_f16, int* idx, float* weight,
+                          int n_expert, int n_expert_used, int hidden, void* stream);
+
+/* ---- plan, row movement, SwiGLU, combine ------------------------------------------ */
+/* cuda_ops.hpp:219  moe_dispatch_scan */
+int sgr_moe_dispatch_scan(const int* idx, float* weight, int* gslot, int* grows, int* off,
+                          int* toff, int* meta, int* mail, int* mail_n, int n_rows, int k,
+                          int n_expert, int tok_per, void* stream);
+/* cuda_ops.hpp:364  gather_rows_q8 */
+int sgr_gather_rows_q8(void* dst, const void* src, const int* src_rows, int n_rows,
+                       int row_blocks, void* stream);
+/* cuda_ops.hpp:226  gather_rows_q8_n */
+int sgr_gather_rows_q8_n(void* dst, const void* src, const int* src_rows, const int* meta,
+                         int r_max, int row_blocks, void* stream);
+/* cuda_ops.hpp:229  gather_rows_f16_n */
+int sgr_gather_rows_f16_n(uint16_t* dst, const uint16_t* src, const int* src_rows,
+                          const int* meta, int r_max, int hidden, void* stream);
+/* cuda_ops.hpp:408  scatter_rows_f16 */
+int sgr_scatter_rows_f16(uint16_t* dst, const uint16_t* src, const int* dst_rows, int n_rows,
+                         int hidden, void* stream);
+/* cuda_ops.hpp:372  scatter_routed_f16 */
+int sgr_scatter_routed_f16(uint16_t* expert_y, const uint16_t* grouped_out, const int* gslot,
+                           int n_rows, int n_used, int hidden, void* stream);
+/* cuda_ops.hpp:403  scatter_miss_f32 */
+int sgr_scatter_miss_f32(uint16_t* expert_out, const int* d_slot_of_k, const float* miss_y,
+                         int k_rows, int hidden, void* stream);
+/* cuda_ops.hpp:391  scatter_rows_generic_f16 */
+int sgr_scatter_rows_generic_f16(uint16_t* dst, const float* src, const int* dst_flat,
+                                 int n_list, int hidden, void* stream);
+/* cuda_ops.hpp:305  silu_mul_f16 */
+int sgr_silu_mul_f16(uint16_t* out, const uint16_t* g, const uint16_t* u, int rows, int n_ff,
+                     void* stream);
+/* cuda_ops.hpp:232  silu_mul_f16_n */
+int sgr_silu_mul_f16_n(uint16_t* out, const uint16_t* g, const uint16_t* u, const int* d_rows,
+                       int rows_max, int n_ff, void* stream);
+/* cuda_ops.hpp:315  sigmoid_gate_scalar_f16 */
+int sgr_sigmoid_gate_scalar_f16(uint16_t* out, const float* g, int n, void* stream);
+/* cuda_ops.hpp:384  sigmoid_gate_scalar_batched_f16 */
+int sgr_sigmoid_gate_scalar_batched_f16(uint16_t* out, const float* g, int n_rows, int hidden,
+                                        void* stream);
+/* cuda_ops.hpp:397  moe_combine_f16 */
+int sgr_moe_combine_f16(uint16_t* out, const uint16_t* expert_out, const int* idx,
+                        const float* weight, int n_expert_used, int hidden, void* stream);
+/* cuda_ops.hpp:379  moe_combine_batched_f16 */
+int sgr_moe_combine_batched_f16(uint16_t* out, const uint16_t* expert_y, const float* weight,
+                                int n_used, int hidden, int n_rows, void* stream);
+/* cuda_ops.hpp:255  moe_combine_add_slots_f16 */
+int sgr_moe_combine_add_slots_f16(uint16_t* out, const uint16_t* expert_y, const float* weight,
+                                  const int* rk, int n_used, int hidden, int n_list,
+                                  void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAGER_B200_H_ */

@@ -1,0 +1,89 @@
+"""ctypes binding of libsager_b200.so.
+
+The prototypes are read from include/sager_b200.h, so the header is the single
+statement of the ABI: a symbol the header declares and the library lacks is an
+error at load time. There is no fallback: if the library is missing or was
+built for another toolkit, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import re
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+HEADER = os.path.join(ROOT, "include", "sager_b200.h")
+LIB_PATH = os.path.join(HERE, "libsager_b200.so")
+
+ERRORS = {1: "SGR_EARG", 2: "SGR_EALIGN", 3: "SGR_EUNSUPPORTED", 4: "SGR_ELAUNCH", 5: "SGR_EGEOMETRY"}
+
+_SCALARS = {"int": C.c_int, "float": C.c_float, "long long": C.c_longlong, "size_t": C.c_size_t,
+            "unsigned long long": C.c_ulonglong}
+
+
+class SagerError(RuntimeError):
+    def __init__(self, fn, code):
+        super().__init__(f"{fn} returned {code} ({ERRORS.get(code, 'unknown')})")
+        self.code = code
+
+
+def parse_header(path: str = HEADER):
+    """-> {name: (restype, [argtypes])} for every `int sgr_*(...)` in the header."""
+    text = open(path).read()
+    text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+    protos = {}
+    for m in re.finditer(r"\b(int|void)\s+(sgr_\w+)\s*\(([^)]*)\)\s*;", text):
+        ret, name, args = m.group(1), m.group(2), m.group(3).strip()
+        argtypes = []
+        if args and args != "void":
+            for a in args.split(","):
+                a = " ".join(a.split())
+                if "*" in a:
+                    argtypes.append(C.c_void_p)
+                else:
+                    base = a.rsplit(" ", 1)[0].replace("const ", "").strip()
+                    argtypes.append(_SCALARS[base])
+        protos[name] = (C.c_int if ret == "int" else None, argtypes)
+    return protos
+
+
+class Lib:
+    def __init__(self, path: str = LIB_PATH):
+        if not os.path.exists(path):
+            raise FileNotFoundError(
+                f"{path} is missing: build it with `python -m sager_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        self.path = path
+        self.cdll = C.CDLL(path)
+        self.protos = parse_header()
+        missing = []
+        for name, (res, args) in self.protos.items():
+            try:
+                fn = getattr(self.cdll, name)
+            except AttributeError:
+                missing.append(name)
+                continue
+            fn.restype = res
+            fn.argtypes = args
+        if missing:
+            raise RuntimeError(f"{path} lacks symbols declared in the header: {missing}")
+
+    def call(self, name, *args):
+        """Call an entry point; raise SagerError on a non-zero return."""
+        rc = getattr(self.cdll, name)(*args)
+        if rc != 0:
+            raise SagerError(name, rc)
+
+    def raw(self, name):
+        return getattr(self.cdll, name)
+
+
+_LIB = None
+
+
+def lib() -> Lib:
+    global _LIB
+    if _LIB is None:
+        _LIB = Lib()
+    return _LIB

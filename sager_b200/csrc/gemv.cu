@@ -1,0 +1,364 @@
+// gemv.cu - the Q4_K x Q8_K GEMV family behind the reference's launchers
+// (src/kernels/cuda/q4_k.cu:1534-1562, 1660-1849, 1926-1985 and
+// src/kernels/cuda/mmq.cu:368-378 of the reference): dense single-row and
+// multi-token, pointer-table, host-plan grouped and device-plan grouped with
+// the null-pointer mailbox. One kernel template, four planners; all of them
+// end in tile_run (tile.cuh).
+#include "api_util.cuh"
+#include "tile.cuh"
+
+namespace sgr {
+namespace {
+
+enum Mode : int { kDense = 0, kPtrs = 1, kGrouped = 2, kTab = 3 };
+
+struct GemvArgs {
+  const unsigned char* w[2];            // dense: matrix bases
+  const unsigned char* const* tab[2];   // ptrs / grouped / tab: per-job or per-expert bases
+  const unsigned char* xq;              // packed Q8_K rows, nb blocks each
+  void* y[2];
+  int n_rows, nb, n_tokens, tok_tile, rows_per, n_expert;
+  const int *off, *m, *tile_base, *job_of_tile;   // grouped (host plan)
+  const int *toff, *meta;                          // tab (device plan)
+  int *mail, *mail_n;
+  int* status;
+};
+
+// last e with toff[e] <= tile (toff is the E+1 exclusive prefix of tiles per expert)
+__device__ __forceinline__ int expert_of_tile(const int* toff, int n_expert, int tile) {
+  int lo = 0, hi = n_expert - 1, res = n_expert - 1;
+  while (lo <= hi) {
+    const int mid = (lo + hi) >> 1;
+    if (toff[mid + 1] <= tile) lo = mid + 1;
+    else { res = mid; hi = mid - 1; }
+  }
+  return res;
+}
+
+template <bool F16>
+__device__ __forceinline__ void store_out(void* y, size_t i, float v) {
+  if constexpr (F16) reinterpret_cast<uint16_t*>(y)[i] = f2h(v);
+  else reinterpret_cast<float*>(y)[i] = v;
+}
+
+template <int NMAT, int TT, int MODE, bool F16>
+__global__ void __launch_bounds__(kTileThreads) gemv_tile_kernel(const GemvArgs a) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int nb = a.nb;
+  const int rc = tile_rows(nb);
+  const int row0 = blockIdx.x * rc;
+  const size_t row_bytes = static_cast<size_t>(nb) * kW4;
+  const size_t xrow_bytes = static_cast<size_t>(nb) * kX8;
+
+  const unsigned char* wsrc[NMAT];
+  int nrows, ntok;
+  size_t xbase;          // first activation row of this tile
+  size_t ybase;          // output row index of token slot 0 (multiplied by n_rows below)
+  int ncols = a.n_rows;  // output row length
+
+  if constexpr (MODE == kDense) {
+    nrows = min(rc, a.n_rows - row0);
+    const int tok0 = blockIdx.y * a.tok_tile;
+    ntok = min(a.tok_tile, a.n_tokens - tok0);
+#pragma unroll
+    for (int m = 0; m < NMAT; ++m) wsrc[m] = a.w[m] + row0 * row_bytes;
+    xbase = tok0;
+    ybase = tok0;
+  } else if constexpr (MODE == kPtrs) {
+    // y[e * rows_per + r]; every expert reads the SAME activation row, as the
+    // reference kernel does (q4_k.cu:184-213 indexes xq[blk] only).
+    const int e = blockIdx.y;
+    nrows = min(rc, a.rows_per - row0);
+    ntok = 1;
+    wsrc[0] = a.tab[0][e] + row0 * row_bytes;
+    xbase = 0;
+    ybase = 0;
+    ncols = 0;
+  } else if constexpr (MODE == kGrouped) {
+    const int job = a.job_of_tile[blockIdx.y];
+    const int joff = a.off[job];
+    const int tok0 = (blockIdx.y - a.tile_base[job]) * a.tok_tile;
+    ntok = min(a.tok_tile, a.m[job] - tok0);
+    nrows = min(rc, a.n_rows - row0);
+    if (ntok <= 0) return;
+#pragma unroll
+    for (int m = 0; m < NMAT; ++m) wsrc[m] = a.tab[m][job] + row0 * row_bytes;
+    xbase = joff + tok0;
+    ybase = joff + tok0;
+  } else {
+    if (static_cast<int>(blockIdx.y) >= a.meta[1]) return;      // meta = {rows, tiles, bad}
+    const int e = expert_of_tile(a.toff, a.n_expert, blockIdx.y);
+    const int joff = a.off[e];
+    const int tok0 = (blockIdx.y - a.toff[e]) * a.tok_tile;
+    ntok = min(a.tok_tile, a.off[e + 1] - joff - tok0);
+    nrows = min(rc, a.n_rows - row0);
+    if (ntok <= 0) return;
+    bool absent = false;
+#pragma unroll
+    for (int m = 0; m < NMAT; ++m) {
+      const unsigned char* base = a.tab[m][e];
+      absent = absent || (base == nullptr);
+      wsrc[m] = base + row0 * row_bytes;
+    }
+    if (absent) {
+      // Absent expert: its rows read as zero in the combine; the gate/up launch
+      // posts the expert id once per tile for the host-side patch
+      // (q4_k.cu:697-710 of the reference).
+      for (int i = threadIdx.x; i < nrows * ntok; i += kTileThreads) {
+        const int r = i % nrows, t = i / nrows;
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m)
+          reinterpret_cast<uint16_t*>(a.y[m])[static_cast<size_t>(joff + tok0 + t) * a.n_rows + row0 + r] = 0;
+      }
+      if (a.mail != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+        const int mi = atomicAdd(a.mail_n, 1);
+        if (mi < a.n_expert) a.mail[mi] = e;
+      }
+      return;
+    }
+    xbase = joff + tok0;
+    ybase = joff + tok0;
+  }
+  if (nrows <= 0 || ntok <= 0) return;
+
+  tile_run<NMAT, TT>(
+      smem, wsrc, nrows, nb, ntok,
+      [&](int t) { return a.xq + (xbase + t) * xrow_bytes; },
+      [&](int r, int t0, int nt, float (&res)[NMAT][TT]) {
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+          for (int t = 0; t < TT; ++t)
+            if (t < nt) {
+              size_t oi;
+              if constexpr (MODE == kPtrs) oi = static_cast<size_t>(blockIdx.y) * a.rows_per + row0 + r;
+              else oi = (ybase + t0 + t) * ncols + row0 + r;
+              store_out<F16>(a.y[m], oi, res[m][t]);
+            }
+      },
+      a.status);
+}
+
+template <int NMAT, int TT, int MODE, bool F16>
+int launch_tile(const GemvArgs& a, dim3 grid, cudaStream_t stream) {
+  const size_t smem = tile_smem(NMAT, a.nb, TT);
+  if (smem > 200 * 1024) return kErrUnsupported;
+  auto kern = gemv_tile_kernel<NMAT, TT, MODE, F16>;
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return kErrLaunch;
+  }
+  kern<<<grid, kTileThreads, smem, stream>>>(a);
+  return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+// tokens per CTA of the dense multi-token kernels (walked in sub-tiles of 4)
+constexpr int kDenseTokTile = 16;
+
+template <int NMAT, bool F16>
+int launch_dense(const void* w0, const void* w1, const void* xq, void* y0, void* y1, int n_rows,
+                 int k, int n_tokens, cudaStream_t stream) {
+  if (n_tokens <= 0 || n_rows <= 0) return kOk;
+  if (!w0 || !xq || !y0 || (NMAT == 2 && (!w1 || !y1)) || k <= 0 || k % kQK != 0) return kErrArg;
+  if (reinterpret_cast<uintptr_t>(xq) & 3u) return kErrAlign;
+  GemvArgs a{};
+  a.w[0] = static_cast<const unsigned char*>(w0);
+  a.w[1] = static_cast<const unsigned char*>(w1);
+  a.xq = static_cast<const unsigned char*>(xq);
+  a.y[0] = y0;
+  a.y[1] = y1;
+  a.n_rows = n_rows;
+  a.nb = k / kQK;
+  a.n_tokens = n_tokens;
+  a.status = status_word();
+  const int rc = tile_rows(a.nb);
+  if (n_tokens == 1) {
+    a.tok_tile = 1;
+    return launch_tile<NMAT, 1, kDense, F16>(a, dim3((n_rows + rc - 1) / rc, 1), stream);
+  }
+  a.tok_tile = kDenseTokTile;
+  return launch_tile<NMAT, 4, kDense, F16>(
+      a, dim3((n_rows + rc - 1) / rc, (n_tokens + kDenseTokTile - 1) / kDenseTokTile), stream);
+}
+
+template <int NMAT>
+int launch_grouped(const void* const* t0, const void* const* t1, const int* off, const int* m,
+                   const int* tile_base, const int* job_of_tile, int n_tiles, const void* xq,
+                   void* y0, void* y1, int n_rows, int k, int tok_per, cudaStream_t stream) {
+  if (n_tiles <= 0) return kOk;
+  if (!t0 || (NMAT == 2 && (!t1 || !y1)) || !off || !m || !tile_base || !job_of_tile || !xq ||
+      !y0 || n_rows <= 0 || k <= 0 || k % kQK != 0 || tok_per <= 0)
+    return kErrArg;
+  if (reinterpret_cast<uintptr_t>(xq) & 3u) return kErrAlign;
+  GemvArgs a{};
+  a.tab[0] = reinterpret_cast<const unsigned char* const*>(t0);
+  a.tab[1] = reinterpret_cast<const unsigned char* const*>(t1);
+  a.off = off; a.m = m; a.tile_base = tile_base; a.job_of_tile = job_of_tile;
+  a.xq = static_cast<const unsigned char*>(xq);
+  a.y[0] = y0; a.y[1] = y1;
+  a.n_rows = n_rows; a.nb = k / kQK; a.tok_tile = tok_per;
+  a.status = status_word();
+  const int rc = tile_rows(a.nb);
+  const dim3 grid((n_rows + rc - 1) / rc, n_tiles);
+  return tok_per == 1 ? launch_tile<NMAT, 1, kGrouped, true>(a, grid, stream)
+                      : launch_tile<NMAT, 4, kGrouped, true>(a, grid, stream);
+}
+
+template <int NMAT>
+int launch_tab(const void* const* t0, const void* const* t1, const int* off, const int* toff,
+               const int* meta, int* mail, int* mail_n, int tiles_max, const void* xq, void* y0,
+               void* y1, int n_rows, int k, int n_expert, int tok_per, cudaStream_t stream) {
+  if (tiles_max <= 0) return kOk;
+  if (!t0 || (NMAT == 2 && (!t1 || !y1)) || !off || !toff || !meta || !xq || !y0 || n_rows <= 0 ||
+      k <= 0 || k % kQK != 0 || tok_per <= 0 || n_expert <= 0 || (mail && !mail_n))
+    return kErrArg;
+  if (reinterpret_cast<uintptr_t>(xq) & 3u) return kErrAlign;
+  GemvArgs a{};
+  a.tab[0] = reinterpret_cast<const unsigned char* const*>(t0);
+  a.tab[1] = reinterpret_cast<const unsigned char* const*>(t1);
+  a.off = off; a.toff = toff; a.meta = meta; a.mail = mail; a.mail_n = mail_n;
+  a.xq = static_cast<const unsigned char*>(xq);
+  a.y[0] = y0; a.y[1] = y1;
+  a.n_rows = n_rows; a.nb = k / kQK; a.tok_tile = tok_per; a.n_expert = n_expert;
+  a.status = status_word();
+  const int rc = tile_rows(a.nb);
+  const dim3 grid((n_rows + rc - 1) / rc, tiles_max);
+  return tok_per == 1 ? launch_tile<NMAT, 1, kTab, true>(a, grid, stream)
+                      : launch_tile<NMAT, 4, kTab, true>(a, grid, stream);
+}
+
+// Raw int32 sub-block dots of token 0: out[(r*nb + blk)*8 + s]. Parity probe for
+// the integer unit every kernel shares (block_dot).
+__global__ void subblock_dots_kernel(const unsigned char* w, const unsigned char* xq, int* out,
+                                     int n_rows, int nb) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  unsigned char* wsm = smem;                       // one block per thread
+  const XTile xt = xtile_at(smem + static_cast<size_t>(blockDim.x) * kW4, 1, nb);
+  xtile_stage(xt, 1, [&](int) { return xq; }, threadIdx.x, blockDim.x);
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;   // (row, blk) pair
+  const bool live = i < n_rows * nb;
+  if (live) {
+    const unsigned char* src = w + static_cast<size_t>(i) * kW4;
+    for (int b = 0; b < kW4 / 2; ++b)
+      reinterpret_cast<uint16_t*>(wsm + threadIdx.x * kW4)[b] = reinterpret_cast<const uint16_t*>(src)[b];
+  }
+  __syncthreads();
+  if (!live) return;
+  float acc[1] = {0.f};
+  int dots[8];
+  block_dot<1>(reinterpret_cast<const uint4*>(wsm + threadIdx.x * kW4), xt, i % nb, 1, acc, dots);
+  for (int s = 0; s < 8; ++s) out[static_cast<size_t>(i) * 8 + s] = dots[s];
+}
+
+}  // namespace
+}  // namespace sgr
+
+using namespace sgr;
+
+SGR_API int sgr_gemv_q4_k_q8(const void* w, const void* x_q8, float* y, int n_rows, int k,
+                             void* stream) {
+  return launch_dense<1, false>(w, nullptr, x_q8, y, nullptr, n_rows, k, 1, as_stream(stream));
+}
+
+SGR_API int sgr_gemv_q4_k_q8_f16out(const void* w, const void* x_q8, uint16_t* y, int n_rows, int k,
+                                    void* stream) {
+  return launch_dense<1, true>(w, nullptr, x_q8, y, nullptr, n_rows, k, 1, as_stream(stream));
+}
+
+SGR_API int sgr_gemv_q4_k_q8_batched(const void* w, const void* x_q8, float* y, int n_rows, int k,
+                                     int n_tokens, void* stream) {
+  return launch_dense<1, false>(w, nullptr, x_q8, y, nullptr, n_rows, k, n_tokens, as_stream(stream));
+}
+
+SGR_API int sgr_gemv_q4_k_q8_f16out_batched(const void* w, const void* x_q8, uint16_t* y,
+                                            int n_rows, int k, int n_tokens, void* stream) {
+  return launch_dense<1, true>(w, nullptr, x_q8, y, nullptr, n_rows, k, n_tokens, as_stream(stream));
+}
+
+SGR_API int sgr_gemv_q4_k_q8_f16out_mtok(const void* w, const void* xq, uint16_t* y, int n_rows,
+                                         int k, int n_tokens, void* stream) {
+  return launch_dense<1, true>(w, nullptr, xq, y, nullptr, n_rows, k, n_tokens, as_stream(stream));
+}
+
+SGR_API int sgr_mmq_q4_k_q8_f16out(const void* w, const void* xq, uint16_t* y, int n_rows, int k,
+                                   int n_tokens, void* stream) {
+  return launch_dense<1, true>(w, nullptr, xq, y, nullptr, n_rows, k, n_tokens, as_stream(stream));
+}
+
+SGR_API int sgr_gemv2_q4_k_q8_f16out_mtok(const void* wg, const void* wu, const void* xq,
+                                          uint16_t* yg, uint16_t* yu, int n_rows, int k,
+                                          int n_tokens, void* stream) {
+  return launch_dense<2, true>(wg, wu, xq, yg, yu, n_rows, k, n_tokens, as_stream(stream));
+}
+
+SGR_API int sgr_mmq2_q4_k_q8_f16out(const void* wg, const void* wu, const void* xq, uint16_t* yg,
+                                    uint16_t* yu, int n_rows, int k, int n_tokens, void* stream) {
+  return launch_dense<2, true>(wg, wu, xq, yg, yu, n_rows, k, n_tokens, as_stream(stream));
+}
+
+SGR_API int sgr_gemv_ptrs_q4_k_q8_f16out(const void* const* ptrs, const void* x_q8, uint16_t* y,
+                                         int n_ptrs, int rows_per, int k, void* stream) {
+  if (n_ptrs <= 0 || rows_per <= 0) return kOk;
+  if (!ptrs || !x_q8 || !y || k <= 0 || k % kQK != 0) return kErrArg;
+  if (reinterpret_cast<uintptr_t>(x_q8) & 3u) return kErrAlign;
+  GemvArgs a{};
+  a.tab[0] = reinterpret_cast<const unsigned char* const*>(ptrs);
+  a.xq = static_cast<const unsigned char*>(x_q8);
+  a.y[0] = y;
+  a.rows_per = rows_per;
+  a.n_rows = rows_per;
+  a.nb = k / kQK;
+  a.tok_tile = 1;
+  a.status = status_word();
+  const int rc = tile_rows(a.nb);
+  return launch_tile<1, 1, kPtrs, true>(a, dim3((rows_per + rc - 1) / rc, n_ptrs), as_stream(stream));
+}
+
+SGR_API int sgr_gemv_grouped2_q4_k_q8_f16out_mtok(const void* const* wg, const void* const* wu,
+                                                  const int* off, const int* m,
+                                                  const int* tile_base, const int* job_of_tile,
+                                                  int n_tiles, const void* xq, uint16_t* yg,
+                                                  uint16_t* yu, int n_rows, int k, int tok_per,
+                                                  void* stream) {
+  return launch_grouped<2>(wg, wu, off, m, tile_base, job_of_tile, n_tiles, xq, yg, yu, n_rows, k,
+                           tok_per, as_stream(stream));
+}
+
+SGR_API int sgr_gemv_grouped_q4_k_q8_f16out_mtok(const void* const* w, const int* off, const int* m,
+                                                 const int* tile_base, const int* job_of_tile,
+                                                 int n_tiles, const void* xq, uint16_t* y,
+                                                 int n_rows, int k, int tok_per, void* stream) {
+  return launch_grouped<1>(w, nullptr, off, m, tile_base, job_of_tile, n_tiles, xq, y, nullptr,
+                           n_rows, k, tok_per, as_stream(stream));
+}
+
+SGR_API int sgr_gemv_grouped2_tab_q4_k_q8_f16out_mtok(
+    const void* const* wg_tab, const void* const* wu_tab, const int* off, const int* toff,
+    const int* meta, int* mail, int* mail_n, int tiles_max, const void* xq, uint16_t* yg,
+    uint16_t* yu, int n_rows, int k, int n_expert, int tok_per, void* stream) {
+  return launch_tab<2>(wg_tab, wu_tab, off, toff, meta, mail, mail_n, tiles_max, xq, yg, yu, n_rows,
+                       k, n_expert, tok_per, as_stream(stream));
+}
+
+SGR_API int sgr_gemv_grouped_tab_q4_k_q8_f16out_mtok(const void* const* w_tab, const int* off,
+                                                     const int* toff, const int* meta,
+                                                     int tiles_max, const void* xq, uint16_t* y,
+                                                     int n_rows, int k, int n_expert, int tok_per,
+                                                     void* stream) {
+  return launch_tab<1>(w_tab, nullptr, off, toff, meta, nullptr, nullptr, tiles_max, xq, y, nullptr,
+                       n_rows, k, n_expert, tok_per, as_stream(stream));
+}
+
+SGR_API int sgr_q4k_subblock_dots(const void* w, const void* x_q8, int* out, int n_rows, int k,
+                                  void* stream) {
+  if (!w || !x_q8 || !out || n_rows <= 0 || k <= 0 || k % kQK != 0) return kErrArg;
+  if (reinterpret_cast<uintptr_t>(x_q8) & 3u) return kErrAlign;
+  const int nb = k / kQK;
+  const int threads = 128;
+  const size_t smem = static_cast<size_t>(threads) * kW4 + xtile_bytes(1, nb);
+  if (smem > 48 * 1024) return kErrUnsupported;
+  subblock_dots_kernel<<<(n_rows * nb + threads - 1) / threads, threads, smem, as_stream(stream)>>>(
+      static_cast<const unsigned char*>(w), static_cast<const unsigned char*>(x_q8), out, n_rows, nb);
+  return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
