@@ -23,6 +23,7 @@
 #ifndef SAGER_B200_H_
 #define SAGER_B200_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -173,6 +174,56 @@ int sgr_moe_combine_batched_f16(uint16_t* out, const uint16_t* expert_y, const f
 int sgr_moe_combine_add_slots_f16(uint16_t* out, const uint16_t* expert_y, const float* weight,
                                   const int* rk, int n_used, int hidden, int n_list,
                                   void* stream);
+
+/* ---- one MoE layer of a decode step, fused ------------------------------------------
+ * Replaces the launch sequence of Session::moe_dispatch_device for n <= 64 token rows
+ * (src/core/session.cpp:2482-3030 of the reference; the launchers it strings together
+ * are listed at the top of csrc/moe_layer.cu) with three dependent launches. Same
+ * contracts: xn fp16 rows, router [E][H] fp32, [3][E] pointer table (gate, up, down;
+ * null = expert absent: zero contribution, id posted to mail[]), route_idx / route_w
+ * rows of stride K+1 with slot K = shared_w, residual stream x_f16 updated in place.
+ * Intermediate g, u, h, y stay fp32 (the arithmetic of the CPU expert FFN,
+ * src/kernels/cpu/q4_avx2.cpp:175-196).
+ *
+ * Expert parallelism: only routes to experts in [expert_lo, expert_hi) are computed
+ * (expert_hi == 0 means n_expert) and the shared expert only for rows
+ * [shared_lo, shared_hi) (shared_hi == 0 means n). With routing_given != 0 the router
+ * is skipped: route_idx / route_w and xq_in (packed Q8_K rows) are inputs. With
+ * no_residual != 0 out_f32 receives the weighted expert sum alone.
+ *
+ * The workspace (size from sgr_moe_layer_workspace_bytes, 256-byte aligned) must be
+ * cleared once with sgr_moe_layer_workspace_init before its first use; one layer call
+ * may be in flight per workspace. */
+typedef struct sgr_moe_layer {
+  int n;                 /* token rows this call, 1..n_max */
+  int n_max;             /* rows the workspace was sized for, <= 64 */
+  int hidden, n_ff, n_expert, n_used;
+  int expert_lo, expert_hi;
+  int shared_lo, shared_hi;
+  int routing_given;
+  int no_residual;
+  float shared_w;        /* written to route_w[row][K] by the router */
+  const uint16_t* xn;    /* [n][hidden] fp16, 16-byte aligned */
+  const void* xq_in;     /* optional [n][hidden/256] Q8_K blocks: skip the quantiser */
+  const float* router_w; /* [n_expert][hidden] */
+  const float* router_bias; /* optional [n_expert], added to the logits */
+  const void* const* w_tab; /* [3][n_expert] device pointers to Q4_K matrices */
+  const void* shared_gate;  /* shared expert matrices, or all NULL */
+  const void* shared_up;
+  const void* shared_down;
+  uint16_t* x_f16;       /* optional [n][hidden]: residual in, residual + MoE out */
+  float* out_f32;        /* optional [n][hidden] fp32 copy of the result */
+  int* route_idx;        /* [n][n_used+1] */
+  float* route_w;        /* [n][n_used+1] */
+  int* mail;             /* optional [n_expert] absent-expert mailbox */
+  int* mail_n;           /* [1], reset by every call */
+  void* workspace;
+  size_t workspace_bytes;
+} sgr_moe_layer;
+
+size_t sgr_moe_layer_workspace_bytes(int n_max, int hidden, int n_ff, int n_expert, int n_used);
+int sgr_moe_layer_workspace_init(void* workspace, size_t bytes, void* stream);
+int sgr_moe_layer_decode(const sgr_moe_layer* args, void* stream);
 
 #ifdef __cplusplus
 }

@@ -37,7 +37,8 @@ def needs_build() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + [os.path.abspath(__file__)]
+    deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + [os.path.abspath(__file__)] + \
+        glob.glob(os.path.join(os.path.dirname(HERE), "include", "*.h"))
     return any(os.path.getmtime(p) > t for p in deps)
 
 
@@ -45,7 +46,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     if not force and not needs_build():
         return LIB
     cmd = [nvcc_path()] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + \
-        ["-I", CSRC, "-o", LIB] + sources()
+        ["-I", CSRC, "-I", os.path.join(os.path.dirname(HERE), "include"), "-o", LIB] + sources()
     if verbose:
         print(" ".join(cmd))
     res = subprocess.run(cmd, capture_output=True, text=True)

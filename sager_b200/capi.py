@@ -33,7 +33,7 @@ def parse_header(path: str = HEADER):
     text = open(path).read()
     text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
     protos = {}
-    for m in re.finditer(r"\b(int|void)\s+(sgr_\w+)\s*\(([^)]*)\)\s*;", text):
+    for m in re.finditer(r"\b(int|void|size_t)\s+(sgr_\w+)\s*\(([^)]*)\)\s*;", text):
         ret, name, args = m.group(1), m.group(2), m.group(3).strip()
         argtypes = []
         if args and args != "void":
@@ -44,7 +44,7 @@ def parse_header(path: str = HEADER):
                 else:
                     base = a.rsplit(" ", 1)[0].replace("const ", "").strip()
                     argtypes.append(_SCALARS[base])
-        protos[name] = (C.c_int if ret == "int" else None, argtypes)
+        protos[name] = ({"int": C.c_int, "size_t": C.c_size_t, "void": None}[ret], argtypes)
     return protos
 
 
@@ -70,13 +70,33 @@ class Lib:
             raise RuntimeError(f"{path} lacks symbols declared in the header: {missing}")
 
     def call(self, name, *args):
-        """Call an entry point; raise SagerError on a non-zero return."""
+        """Call an int-returning entry point; raise SagerError on a non-zero return."""
         rc = getattr(self.cdll, name)(*args)
         if rc != 0:
             raise SagerError(name, rc)
 
     def raw(self, name):
         return getattr(self.cdll, name)
+
+
+class MoeLayerArgs(C.Structure):
+    """struct sgr_moe_layer of include/sager_b200.h (field order is the ABI)."""
+    _fields_ = [
+        ("n", C.c_int), ("n_max", C.c_int),
+        ("hidden", C.c_int), ("n_ff", C.c_int), ("n_expert", C.c_int), ("n_used", C.c_int),
+        ("expert_lo", C.c_int), ("expert_hi", C.c_int),
+        ("shared_lo", C.c_int), ("shared_hi", C.c_int),
+        ("routing_given", C.c_int), ("no_residual", C.c_int),
+        ("shared_w", C.c_float),
+        ("xn", C.c_void_p), ("xq_in", C.c_void_p),
+        ("router_w", C.c_void_p), ("router_bias", C.c_void_p),
+        ("w_tab", C.c_void_p),
+        ("shared_gate", C.c_void_p), ("shared_up", C.c_void_p), ("shared_down", C.c_void_p),
+        ("x_f16", C.c_void_p), ("out_f32", C.c_void_p),
+        ("route_idx", C.c_void_p), ("route_w", C.c_void_p),
+        ("mail", C.c_void_p), ("mail_n", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
 
 
 _LIB = None

@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "sager_b200.h"   // the public prototypes: definitions must agree with them
+
 #define SGR_API extern "C" __attribute__((visibility("default")))
 
 namespace sgr {

@@ -122,20 +122,24 @@ __device__ __forceinline__ void tile_compute(const TileSmem& s, const XTile& xt,
 }
 
 // Whole tile: load weights once, then walk the token list in sub-tiles of TT.
-//   xrow(t)            -> pointer to the packed Q8_K row of token slot t (0 <= t < ntok)
+//   before_x()            runs after the weight copies were issued and before any
+//                         activation is read (the place for a dependent-launch wait)
+//   stage(xt, t0, nt)     fills the tile with token slots t0 .. t0+nt-1 (all threads)
 //   emit(row, t0, nt, res) with res[m][i] for token slot t0 + i
-template <int NMAT, int TT, typename XRow, typename Emit>
-__device__ __forceinline__ void tile_run(unsigned char* smem,
-                                         const unsigned char* const (&wsrc)[NMAT], int nrows,
-                                         int nb, int ntok, XRow xrow, Emit emit, int* status) {
+template <int NMAT, int TT, typename BeforeX, typename Stage, typename Emit>
+__device__ __forceinline__ void tile_run_staged(unsigned char* smem,
+                                                const unsigned char* const (&wsrc)[NMAT],
+                                                int nrows, int nb, int ntok, BeforeX before_x,
+                                                Stage stage, Emit emit, int* status) {
   const TileSmem s = tile_smem_view(smem, NMAT, nb);
   const XTile xt = xtile_at(s.x, TT, nb);
   const bool tma = tile_load_weights<NMAT>(s, wsrc, nrows, nb, status);
+  before_x();
   bool ok = true;
   for (int t0 = 0; t0 < ntok; t0 += TT) {
     const int nt = min(TT, ntok - t0);
     if (t0 > 0) __syncthreads();                    // previous sub-tile fully consumed
-    xtile_stage(xt, nt, [&](int t) { return xrow(t0 + t); }, threadIdx.x, kTileThreads);
+    stage(xt, t0, nt);
     __syncthreads();                                // x staged; mbarrier init visible
     if (t0 == 0 && tma) ok = __syncthreads_and(mbar_wait(s.bar, 0)) != 0;
     if (!ok) break;                                 // uniform: every thread saw the same vote
@@ -143,6 +147,20 @@ __device__ __forceinline__ void tile_run(unsigned char* smem,
                            [&](int r, float (&res)[NMAT][TT]) { emit(r, t0, nt, res); });
   }
   if (!ok && threadIdx.x == 0 && status != nullptr) atomicExch(status, 1);
+}
+
+// Same, with the activations taken from packed Q8_K rows in global memory:
+//   xrow(t) -> pointer to the row of token slot t (0 <= t < ntok)
+template <int NMAT, int TT, typename XRow, typename Emit>
+__device__ __forceinline__ void tile_run(unsigned char* smem,
+                                         const unsigned char* const (&wsrc)[NMAT], int nrows,
+                                         int nb, int ntok, XRow xrow, Emit emit, int* status) {
+  tile_run_staged<NMAT, TT>(
+      smem, wsrc, nrows, nb, ntok, [] {},
+      [&](const XTile& xt, int t0, int nt) {
+        xtile_stage(xt, nt, [&](int t) { return xrow(t0 + t); }, threadIdx.x, kTileThreads);
+      },
+      emit, status);
 }
 
 }  // namespace sgr

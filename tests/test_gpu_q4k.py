@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from sager_b200 import ops
-from tests.util import DEV, GEMV_TOL, dev, f16_ulp_diff, make_q4k, make_x16, rel
+from tests.util import DEV, GEMV_TOL, dev, f16_close, make_q4k, make_x16, rel
 
 pytestmark = pytest.mark.gpu
 
@@ -93,7 +93,7 @@ def test_gemv_sweep_vs_oracle(oracle, rows, k, batch):
     else:
         ops.gemv_q4_k_q8_f16out_batched(w_dev, xq, y16, rows, k, batch)
     # the fp16 store rounds the same fp32 value: at most one fp16 step from the oracle's
-    assert f16_ulp_diff(y16.cpu().numpy(), want.astype(np.float16)) <= 1
+    assert f16_close(y16.cpu().numpy(), want)
 
 
 def test_multi_token_variants_agree(oracle):
@@ -111,7 +111,7 @@ def test_multi_token_variants_agree(oracle):
         getattr(ops, name)(w_dev, xq, y, rows, k, tok)
         outs[name] = y.cpu().numpy()
         assert rel(outs[name].astype(np.float32), want) < 1e-3      # fp16 storage
-        assert f16_ulp_diff(outs[name], want.astype(np.float16)) <= 1
+        assert f16_close(outs[name], want)
     # the reference promises bit-identical outputs between these three launchers
     assert np.array_equal(outs["gemv_q4_k_q8_f16out_batched"].view(np.uint16),
                           outs["gemv_q4_k_q8_f16out_mtok"].view(np.uint16))
@@ -122,7 +122,7 @@ def test_multi_token_variants_agree(oracle):
         yu = torch.zeros(tok, rows, dtype=torch.float16, device=DEV)
         getattr(ops, name)(w_dev, w2_dev, xq, yg, yu, rows, k, tok)
         assert np.array_equal(yg.cpu().numpy().view(np.uint16), outs["mmq_q4_k_q8_f16out"].view(np.uint16))
-        assert f16_ulp_diff(yu.cpu().numpy(), want2.astype(np.float16)) <= 1
+        assert f16_close(yu.cpu().numpy(), want2)
 
 
 def test_ragged_rows_and_many_tokens(oracle):
@@ -164,7 +164,7 @@ def test_pointer_table_gemv(oracle):
         y = torch.zeros(5 * rows_per, dtype=torch.float16, device=DEV)
         ops.gemv_ptrs_q4_k_q8_f16out(tab, xq, y, 5, rows_per, k)
         want = np.concatenate([oracle.gemv(m[0], xq.cpu().numpy()[0], rows_per, k) for m in mats])
-        assert f16_ulp_diff(y.cpu().numpy(), want.astype(np.float16)) <= 1
+        assert f16_close(y.cpu().numpy(), want)
 
 
 def _host_plan(m_per_job, tok_per):
@@ -204,9 +204,9 @@ def test_grouped_host_plan(oracle, tok_per):
     for j in range(jobs):
         for t in range(m_per_job[j]):
             r = off[j] + t
-            assert f16_ulp_diff(yg[r].cpu().numpy(), oracle.gemv(gates[j][0], xq_np[r], n_ff, hidden).astype(np.float16)) <= 1
-            assert f16_ulp_diff(yu[r].cpu().numpy(), oracle.gemv(ups[j][0], xq_np[r], n_ff, hidden).astype(np.float16)) <= 1
-            assert f16_ulp_diff(yd[r].cpu().numpy(), oracle.gemv(downs[j][0], hq_np[r], hidden, n_ff).astype(np.float16)) <= 1
+            assert f16_close(yg[r].cpu().numpy(), oracle.gemv(gates[j][0], xq_np[r], n_ff, hidden))
+            assert f16_close(yu[r].cpu().numpy(), oracle.gemv(ups[j][0], xq_np[r], n_ff, hidden))
+            assert f16_close(yd[r].cpu().numpy(), oracle.gemv(downs[j][0], hq_np[r], hidden, n_ff))
 
 
 @pytest.mark.parametrize("tok_per", [1, 4])
@@ -254,8 +254,8 @@ def test_grouped_device_plan_with_absent_experts(oracle, tok_per):
             mails_expected += [e] * int(plan["toff"][e + 1] - plan["toff"][e])
             continue
         for r in range(lo, hi):
-            assert f16_ulp_diff(yg[r].cpu().numpy(), oracle.gemv(mats[e][0][0], xqg_np[r], n_ff, hidden).astype(np.float16)) <= 1
-            assert f16_ulp_diff(yu[r].cpu().numpy(), oracle.gemv(mats[e][1][0], xqg_np[r], n_ff, hidden).astype(np.float16)) <= 1
-            assert f16_ulp_diff(yd[r].cpu().numpy(), oracle.gemv(mats[e][2][0], hq_np[r], hidden, n_ff).astype(np.float16)) <= 1
+            assert f16_close(yg[r].cpu().numpy(), oracle.gemv(mats[e][0][0], xqg_np[r], n_ff, hidden))
+            assert f16_close(yu[r].cpu().numpy(), oracle.gemv(mats[e][1][0], xqg_np[r], n_ff, hidden))
+            assert f16_close(yd[r].cpu().numpy(), oracle.gemv(mats[e][2][0], hq_np[r], hidden, n_ff))
     n_mail = int(mail_n.item())
     assert sorted(mail.cpu().numpy()[:n_mail].tolist()) == sorted(mails_expected)

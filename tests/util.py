@@ -49,3 +49,14 @@ def f16_ulp_diff(a_u16, b_u16):
         u = u.astype(np.int32)
         return np.where(u & 0x8000, -(u & 0x7FFF), u & 0x7FFF)
     return int(np.abs(key(np.asarray(a_u16).view(np.uint16)) - key(np.asarray(b_u16).view(np.uint16))).max())
+
+
+def f16_close(got_f16, want_f32, tol=GEMV_TOL):
+    """fp16 outputs of an fp32 computation: within one fp16 step of the oracle's fp32
+    value, plus the fp32 tolerance relative to the largest output (values near zero
+    come from cancellation and carry the absolute error of the large terms)."""
+    got = np.asarray(got_f16).view(np.float16).astype(np.float64).reshape(-1)
+    want = np.asarray(want_f32, dtype=np.float64).reshape(-1)
+    step = np.spacing(np.abs(want).astype(np.float16)).astype(np.float64)
+    bound = step + tol * np.abs(want).max()
+    return bool(np.all(np.abs(got - want) <= bound))
