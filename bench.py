@@ -1,0 +1,408 @@
+#!/usr/bin/env python3
+"""Decode-throughput benchmark of the Q4_K MoE expert path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload (one "step" = one decode step of the MoE halves of a 40-layer stack):
+64 concurrent token rows, hidden 2048, 256 routed experts (FFN 512, top-8) plus
+one shared expert per layer, Q4_K weights drawn from N(0, 0.02), fp16 inputs
+drawn from N(0, 1), router logits skewed with a Zipf(s=1.1) bias so that about
+20 % of the experts take about 70 % of the routed picks. With N > 1 the experts
+of every layer are sharded contiguously over the ranks (expert parallelism) and
+token rows travel by all-to-all. Everything is synthetic and seeded.
+
+Prints one JSON line (rank 0). `value` is tokens/s with the inputs resident in
+HBM, `e2e` the same through host buffers, `roofline` describes the dominant
+kernel (the expert kernel: gate/up/down projections of all routed experts), `cpu_baseline` the reference's CPU expert pool on
+this machine's cores over a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, FF, E, K, LAYERS, TOKENS = 2048, 512, 256, 8, 40, 64
+SEED = 20260718 + 1000 * 4
+MAT_BYTES = 589_824           # one 512x2048 or 2048x512 Q4_K matrix
+EXPERT_BYTES = 3 * MAT_BYTES
+ROUTER_BYTES = E * H * 4
+HOT_TARGET = 0.70
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while a region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()          # the exact process started above
+        self.t.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [c.strip() for c in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                  "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------
+def build_workload(device, rank, world, layers, tokens):
+    """Seeded weights (this rank's expert shard only when world > 1), inputs, biases."""
+    import torch
+    from sager_b200 import synth
+    ws = []
+    for li in range(layers):
+        ws.append(synth.MoeWeights(H, FF, E, device, seed=SEED + li))
+    inputs = [synth.normal_fp16((tokens, H), SEED + 500 + li, device) for li in range(layers)]
+    x0 = synth.normal_fp16((tokens, H), SEED + 499, device)
+    # Zipf bias: one alpha for the stack, found by bisection on layer 0 so that the
+    # top 20 % of the experts take ~70 % of the picks
+    ranks0 = synth.zipf_bias(E, SEED + 900, 1.0)
+
+    def share(alpha):
+        lg = inputs[0].float() @ ws[0].router.t() + torch.from_numpy(ranks0 * alpha).to(device)
+        idx = lg.topk(K, dim=1).indices.cpu().numpy()
+        return synth.hot_share(idx, E)
+
+    lo, hi = 0.0, 4.0
+    for _ in range(24):
+        mid = 0.5 * (lo + hi)
+        if share(mid) < HOT_TARGET:
+            lo = mid
+        else:
+            hi = mid
+    alpha = 0.5 * (lo + hi)
+    biases = [torch.from_numpy(synth.zipf_bias(E, SEED + 900 + li, alpha)).to(device)
+              for li in range(layers)]
+    return ws, inputs, x0, biases, alpha
+
+
+def cpu_pool_sample(ws0, xn0, bias0, budget_s=12.0):
+    """Time the reference's CPU expert pool (oracle/_ref) - or, without it, the C port -
+    on layer 0 of the workload: router + top-8 on one thread, then one pool job per
+    (token, expert) and per (token, shared expert), weighted sum on the host."""
+    from oracle import oracle as orc
+    o = orc.Oracle() if os.path.exists(os.path.join(orc.HERE, "libsager_oracle.so")) else None
+    if o is None:
+        orc.build(ref_root="/nonexistent")
+        o = orc.Oracle()
+    cores = os.cpu_count() or 1
+    x16 = xn0.cpu().numpy()
+    router = ws0.router.cpu().numpy()
+    bias = bias0.cpu().numpy()
+    n = x16.shape[0]
+    blob = ws0.blob.cpu().numpy()
+    gu, dn = ws0.gu_bytes, ws0.dn_bytes
+    base = blob.ctypes.data
+
+    def ptrs(e):
+        b = base + e * ws0.expert_bytes
+        return [b, b + gu, b + 2 * gu]
+
+    try:
+        ref = orc.Reference()
+        pool = ref.pool(cores, H, FF, E)
+        kind = "reference"
+    except (FileNotFoundError, OSError, RuntimeError):
+        ref, pool, kind = None, None, "port"
+
+    def one_layer():
+        t0 = time.perf_counter()
+        idx = np.zeros((n, K + 1), dtype=np.int32)
+        wts = np.zeros((n, K + 1), dtype=np.float32)
+        for t in range(n):
+            lg = o.router_logits(router, x16[t]) + bias
+            idx[t], wts[t] = o.router_topk(lg, K, shared_w=1.0)
+        w3, xs = [], []
+        xf = x16.astype(np.float32)
+        for t in range(n):
+            for kk in range(K + 1):
+                w3 += ptrs(int(idx[t, kk]) if kk < K else E)
+                xs.append(xf[t])
+        xs = np.stack(xs)
+        if pool is not None:
+            ys = pool.run(w3, xs)
+        else:
+            ys = _port_batch(o, w3, xs, cores)
+        out = xf.copy()
+        ys = ys.reshape(n, K + 1, H)
+        for kk in range(K + 1):
+            out += wts[:, kk:kk + 1] * ys[:, kk]
+        return time.perf_counter() - t0
+
+    one_layer()                                   # warm-up (page in the weights)
+    times = []
+    t_start = time.perf_counter()
+    while time.perf_counter() - t_start < budget_s and len(times) < 20:
+        times.append(one_layer())
+    if pool is not None:
+        pool.close()
+    t_layer = float(np.median(times))
+    del blob
+    return {"t_layer_s": t_layer, "cores": cores, "kind": kind, "layers_timed": len(times)}
+
+
+def _port_batch(o, w3_ptrs, xs, cores):
+    """expert_ffn_batch on raw addresses (the C port takes void* either way)."""
+    import ctypes as C
+    n_jobs = xs.shape[0]
+    y = np.zeros((n_jobs, H), dtype=np.float32)
+    arr = (C.c_void_p * len(w3_ptrs))(*w3_ptrs)
+    o.lib.orc_expert_ffn_batch(arr, xs.ctypes.data_as(C.c_void_p), y.ctypes.data_as(C.c_void_p),
+                               n_jobs, H, FF, cores)
+    return y
+
+
+def run_reference_arm(args):
+    """The reference's own CPU implementation of the path on this machine's cores:
+    each step is a bounded sample (layer 0 of the workload, 64 token rows: 576 expert
+    FFNs through the reference's CpuPool); tokens/s is scaled to the 40-layer step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    device = "cuda:0" if torch.cuda.is_available() else "cpu"
+    from sager_b200 import synth
+    w0 = synth.MoeWeights(H, FF, E, device, seed=SEED)
+    xn0 = synth.normal_fp16((TOKENS, H), SEED + 500, device)
+    bias0 = torch.from_numpy(synth.zipf_bias(E, SEED + 900, 1.0)).to(device)
+    per_step = max(2.0, min(20.0, 150.0 / max(1, args.steps + args.warmup)))
+    res = None
+    t_all = []
+    for i in range(args.warmup + args.steps):
+        res = cpu_pool_sample(w0, xn0, bias0, budget_s=per_step)
+        if i >= args.warmup:
+            t_all.append(res["t_layer_s"])
+    t_layer = float(np.median(t_all))
+    value = TOKENS / (t_layer * LAYERS)
+    sample = (f"layer 0 of the stack, {TOKENS} token rows: router + {TOKENS * (K + 1)} expert FFNs "
+              f"through the CPU pool; step time = {LAYERS} x layer time")
+    line = {
+        "impl": "reference", "metric": "q4k_moe_decode_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": t_layer * LAYERS * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8 dots, fp32 accumulate", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": res["cores"], "kind": res["kind"],
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus):
+    return {"workload": "expert-parallel decode: 40 MoE layers x 256 Q4_K experts (top-8 + shared), "
+                        "64 token rows, Zipf-skewed routing",
+            "hidden": H, "expert_ffn": FF, "experts": E, "top_k": K, "layers": LAYERS,
+            "tokens": TOKENS, "experts_per_gpu": E // n_gpus,
+            "parallelism": f"ep{n_gpus}" if n_gpus > 1 else "single",
+            "l2": "per-step weight traffic (>5 GB) far exceeds the 126 MB L2; no flush needed"}
+
+
+# ---------------------------------------------------------------------------------------
+def main():
+    global LAYERS, TOKENS
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="shrink the stack (profiling captures)")
+    ap.add_argument("--tokens", type=int, default=TOKENS, help="token rows per step, 1..64")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    LAYERS, TOKENS = args.layers, args.tokens
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from sager_b200 import lib
+    from sager_b200.layer import MoeStack
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    lib()                                              # fails loudly when the .so is missing
+    device = f"cuda:{local_rank}"
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(device))
+
+    if world > 1:
+        from sager_b200.ep import run_ep_bench
+        line = run_ep_bench(args, rank, world, device)
+        if rank == 0:
+            print(json.dumps(line))
+        dist.destroy_process_group()
+        return
+
+    ws, inputs, x0, biases, alpha = build_workload(device, rank, world, LAYERS, TOKENS)
+    n = TOKENS
+    stack = MoeStack(ws, n, K, device, biases=biases, inputs=inputs, per_layer_ws=True)
+    stack.x.copy_(x0)
+    stack.capture(n)
+
+    # ---- value: graph replays, inputs resident ---------------------------------------
+    def step():
+        stack.x.copy_(x0, non_blocking=True)
+        stack.replay()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms_step = ev0.elapsed_time(ev1) / args.steps
+    value = n / (ms_step * 1e-3)
+
+    # ---- e2e: host buffers in, host buffer out ------------------------------------------
+    h_in = torch.empty(LAYERS + 1, n, H, dtype=torch.float16).pin_memory()
+    h_in[0].copy_(x0.cpu())
+    for li in range(LAYERS):
+        h_in[li + 1].copy_(inputs[li].cpu())
+    d_in = torch.empty(LAYERS + 1, n, H, dtype=torch.float16, device=device)
+    h_out = torch.empty(n, H, dtype=torch.float16).pin_memory()
+    stack_inputs_backup = stack.inputs
+    # the graph reads stack.inputs[l]; point them at d_in by copying into place each step
+    def e2e_step():
+        d_in.copy_(h_in, non_blocking=True)
+        stack.x.copy_(d_in[0], non_blocking=True)
+        for li in range(LAYERS):
+            stack_inputs_backup[li].copy_(d_in[li + 1], non_blocking=True)
+        stack.replay()
+        h_out.copy_(stack.x, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+    e2e = {"value": n / (ms_e2e * 1e-3), "unit": "tokens/s",
+           "h2d_bytes_per_step": int(h_in.numel() * 2), "d2h_bytes_per_step": int(h_out.numel() * 2)}
+
+    # ---- roofline of the dominant kernel: gate/up of every layer, back to back -------------
+    idx = stack.idx.cpu().numpy()[:, :n, :K]
+    uniq = [len(np.unique(idx[li])) for li in range(LAYERS)]
+    ex_bytes = sum((u + 1) * EXPERT_BYTES for u in uniq)
+    step_bytes = sum((u + 1) * EXPERT_BYTES + ROUTER_BYTES for u in uniq)
+    stage_ms = {}
+    for name, mask in (("route", 1), ("experts", 6)):
+        g = stack.capture_stage(n, mask)          # that stage of all layers, back to back
+        g.replay()
+        torch.cuda.synchronize()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        s0.record()
+        for _ in range(reps):
+            g.replay()
+        s1.record()
+        torch.cuda.synchronize()
+        stage_ms[name] = s0.elapsed_time(s1) / reps
+    peak, peak_kind = load_peaks()
+    ex_gbs = ex_bytes / (stage_ms["experts"] * 1e-3) / 1e9
+    roofline = {"kernel": "expert_stream_kernel", "bound": "hbm", "achieved": ex_gbs, "peak": peak,
+                "unit": "GB/s", "frac": ex_gbs / peak, "peak_source": f"{peak_kind} copy bandwidth (burst)",
+                "traffic": None,
+                "bytes_per_launch": ex_bytes / LAYERS, "us_per_launch": stage_ms["experts"] * 1e3 / LAYERS,
+                "stage_ms_per_step": stage_ms,
+                "step": {"algorithmic_bytes": step_bytes, "gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+                         "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak}}
+    from sager_b200 import synth
+    hot = float(np.mean([synth.hot_share(idx[li], E) for li in range(LAYERS)]))
+
+    line = {
+        "metric": "q4k_moe_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8 dots, fp32 accumulate",
+        "data": "synthetic",
+        "config": dict(workload_config(1), zipf_alpha=alpha, hot20_share=hot,
+                       distinct_experts_per_layer=float(np.mean(uniq))),
+        "e2e": e2e, "gpu_launches": stack.launches_per_step * args.steps, "clocks": clocks,
+        "roofline": roofline,
+    }
+    if lib().raw("sgr_status")(0) != 0:
+        line["device_status"] = "a bounded device-side wait gave up"
+    if not args.no_cpu_baseline:
+        res = cpu_pool_sample(ws[0], inputs[0], biases[0])
+        line["cpu_baseline"] = {
+            "value": n / (res["t_layer_s"] * LAYERS), "unit": "tokens/s", "cores": res["cores"],
+            "kind": res["kind"],
+            "sample": f"layer 0 of the stack ({n} rows: router + {n * (K + 1)} expert FFNs through the "
+                      f"CPU pool), median of {res['layers_timed']} runs; step time = {LAYERS} x layer time"}
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

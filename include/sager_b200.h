@@ -178,7 +178,7 @@ int sgr_moe_combine_add_slots_f16(uint16_t* out, const uint16_t* expert_y, const
 /* ---- one MoE layer of a decode step, fused ------------------------------------------
  * Replaces the launch sequence of Session::moe_dispatch_device for n <= 64 token rows
  * (src/core/session.cpp:2482-3030 of the reference; the launchers it strings together
- * are listed at the top of csrc/moe_layer.cu) with three dependent launches. Same
+ * are listed at the top of csrc/moe_layer.cu) with two dependent launches. Same
  * contracts: xn fp16 rows, router [E][H] fp32, [3][E] pointer table (gate, up, down;
  * null = expert absent: zero contribution, id posted to mail[]), route_idx / route_w
  * rows of stride K+1 with slot K = shared_w, residual stream x_f16 updated in place.
@@ -224,6 +224,10 @@ typedef struct sgr_moe_layer {
 size_t sgr_moe_layer_workspace_bytes(int n_max, int hidden, int n_ff, int n_expert, int n_used);
 int sgr_moe_layer_workspace_init(void* workspace, size_t bytes, void* stream);
 int sgr_moe_layer_decode(const sgr_moe_layer* args, void* stream);
+/* The same layer, only the launches named in `stages` (1 = route/plan, 2 or 4 or 6 =
+ * the expert kernel), on a workspace that still holds what the earlier stage of a
+ * previous call left there. For measuring one kernel at a time. */
+int sgr_moe_layer_decode_stages(const sgr_moe_layer* args, int stages, void* stream);
 
 #ifdef __cplusplus
 }

@@ -124,17 +124,14 @@ __global__ void __launch_bounds__(kTileThreads) gemv_tile_kernel(const GemvArgs 
   tile_run<NMAT, TT>(
       smem, wsrc, nrows, nb, ntok,
       [&](int t) { return a.xq + (xbase + t) * xrow_bytes; },
-      [&](int r, int t0, int nt, float (&res)[NMAT][TT]) {
+      [&](int r, int t, const float (&v)[NMAT]) {
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m)
-#pragma unroll
-          for (int t = 0; t < TT; ++t)
-            if (t < nt) {
-              size_t oi;
-              if constexpr (MODE == kPtrs) oi = static_cast<size_t>(blockIdx.y) * a.rows_per + row0 + r;
-              else oi = (ybase + t0 + t) * ncols + row0 + r;
-              store_out<F16>(a.y[m], oi, res[m][t]);
-            }
+        for (int m = 0; m < NMAT; ++m) {
+          size_t oi;
+          if constexpr (MODE == kPtrs) oi = static_cast<size_t>(blockIdx.y) * a.rows_per + row0 + r;
+          else oi = (ybase + t) * ncols + row0 + r;
+          store_out<F16>(a.y[m], oi, v[m]);
+        }
       },
       a.status);
 }
@@ -153,7 +150,7 @@ int launch_tile(const GemvArgs& a, dim3 grid, cudaStream_t stream) {
   return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
-// tokens per CTA of the dense multi-token kernels (walked in sub-tiles of 4)
+// tokens per CTA of the dense multi-token kernels (walked in sub-tiles of 8)
 constexpr int kDenseTokTile = 16;
 
 template <int NMAT, bool F16>
@@ -178,7 +175,7 @@ int launch_dense(const void* w0, const void* w1, const void* xq, void* y0, void*
     return launch_tile<NMAT, 1, kDense, F16>(a, dim3((n_rows + rc - 1) / rc, 1), stream);
   }
   a.tok_tile = kDenseTokTile;
-  return launch_tile<NMAT, 4, kDense, F16>(
+  return launch_tile<NMAT, 8, kDense, F16>(
       a, dim3((n_rows + rc - 1) / rc, (n_tokens + kDenseTokTile - 1) / kDenseTokTile), stream);
 }
 
@@ -202,7 +199,7 @@ int launch_grouped(const void* const* t0, const void* const* t1, const int* off,
   const int rc = tile_rows(a.nb);
   const dim3 grid((n_rows + rc - 1) / rc, n_tiles);
   return tok_per == 1 ? launch_tile<NMAT, 1, kGrouped, true>(a, grid, stream)
-                      : launch_tile<NMAT, 4, kGrouped, true>(a, grid, stream);
+                      : launch_tile<NMAT, 8, kGrouped, true>(a, grid, stream);
 }
 
 template <int NMAT>
@@ -225,7 +222,7 @@ int launch_tab(const void* const* t0, const void* const* t1, const int* off, con
   const int rc = tile_rows(a.nb);
   const dim3 grid((n_rows + rc - 1) / rc, tiles_max);
   return tok_per == 1 ? launch_tile<NMAT, 1, kTab, true>(a, grid, stream)
-                      : launch_tile<NMAT, 4, kTab, true>(a, grid, stream);
+                      : launch_tile<NMAT, 8, kTab, true>(a, grid, stream);
 }
 
 // Raw int32 sub-block dots of token 0: out[(r*nb + blk)*8 + s]. Parity probe for
@@ -245,9 +242,10 @@ __global__ void subblock_dots_kernel(const unsigned char* w, const unsigned char
   }
   __syncthreads();
   if (!live) return;
-  float acc[1] = {0.f};
+  float acc[1][1] = {{0.f}};
   int dots[8];
-  block_dot<1>(reinterpret_cast<const uint4*>(wsm + threadIdx.x * kW4), xt, i % nb, 1, acc, dots);
+  const uint4* wb[1] = {reinterpret_cast<const uint4*>(wsm + threadIdx.x * kW4)};
+  block_dot<1, 1>(wb, xt, i % nb, 1, acc, dots);
   for (int s = 0; s < 8; ++s) out[static_cast<size_t>(i) * 8 + s] = dots[s];
 }
 

@@ -1,13 +1,19 @@
-// moe_layer.cu - one MoE layer of a decode step (1..64 token rows) in three
+// moe_layer.cu - one MoE layer of a decode step (1..64 token rows) in two
 // launches chained with programmatic dependent launch:
 //
-//   route    : Q8_K-quantise the rows, router logits, softmax/top-k, and - in the
-//              last CTA to finish - the expert-major plan of the layer
-//   gate_up  : for every (expert, 16-token tile, 16-row chunk): gate and up
-//              projections and SwiGLU, fp32 h rows
-//   down     : for every (expert, tile, 64-row chunk): Q8_K-quantise h in the
-//              prologue, down projection, fp32 y rows; the last CTA to finish a
-//              row chunk adds residual + sum_k w_k * y_k + shared expert
+//   route   : Q8_K-quantise the rows, router logits, softmax/top-k, and - in the
+//             last CTA to finish - the expert-major plan of the layer (tiles of up
+//             to 16 rows per expert)
+//   experts : a persistent kernel, one CTA per SM. Work items are (tile, row chunk)
+//             pairs: first every gate/up item (16 rows of gate and of up for one
+//             tile: SwiGLU, fp32 h rows), then every down item (64 rows of the down
+//             matrix: Q8_K-quantise h, fp32 y rows). A producer warp streams the
+//             weight rows of the CTA's items through a ring of shared-memory
+//             stages with TMA bulk copies, several items ahead of the eight
+//             consumer warps, which run int8 tensor-core MMAs on them. Down items
+//             wait (bounded) for the gate/up items of their tile; their weights are
+//             already in flight by then. The last CTA to finish a 64-row chunk of
+//             the output adds residual + sum_k w_k * y_k + shared expert.
 //
 // It replaces the launch sequence of the reference's device-dispatch path
 // (Session::moe_dispatch_device, src/core/session.cpp:2482-3030: quantize_q8_k,
@@ -21,10 +27,9 @@
 // g, u, h and y stay fp32 and h is quantised from fp32, so the result tracks the
 // AVX2 path more closely than the reference's fp16-staged device path does.
 //
-// Every weight byte is read once: the weight rows of a CTA arrive by one TMA
-// bulk copy, the down kernel issues its copies before it waits for gate_up, and
-// the route kernel prefetches the router matrix into L2 before it waits for the
-// previous layer.
+// Every weight byte is read once, and the weight stream never stops at the
+// gate/up -> down dependency. The route kernel prefetches the router matrix into
+// L2 before it waits for the previous layer.
 #include <algorithm>
 
 #include "api_util.cuh"
@@ -37,9 +42,15 @@ namespace sgr {
 namespace {
 
 constexpr int kMaxRows = 64;       // token rows per call (row masks are 64-bit)
-constexpr int kTokTile = 16;       // token rows per CTA of the expert kernels
+constexpr int kTokTile = 16;       // token rows per tile of the expert kernel
 constexpr int kRouteTok = 8;       // token rows per CTA of the route kernel
 constexpr int kRouteWarps = 4;
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kStreamThreads = kConsumers + 32;   // + one producer warp
+constexpr int kStages = 4;
+constexpr unsigned kSpinLimit = 1u << 22;         // bounded waits: give up, raise the status word
 
 struct LayerDev {
   int n, H, FF, E, K, nbh, nbf;
@@ -62,22 +73,23 @@ struct LayerDev {
   unsigned char* xq;
   float* logits;
   int* off;        // [E+1] exclusive prefix of routed rows per expert
-  int* tile_e;     // [max_tiles] expert of a tile (E = shared expert)
-  int* tile_t0;    // [max_tiles] first row of the tile inside its expert
-  int* meta;       // {routed rows, tiles incl. shared, bad ids, -}
+  int4* rec;       // [max_tiles] {expert (E = shared), rows, first h/y row, first slot / token row}
+  int* meta;       // {routed rows, tiles incl. shared, bad ids, routed tiles}
   int* gslot;      // [n*K] grouped slot of a route, -1 = not computed here
   int* grows;      // [n*K] source row of a grouped slot
-  unsigned* cnt;   // [0..7] route tiles, [8] route tiles done, [16..] down row chunks
+  unsigned* cnt;   // [0..7] route tiles, [8] route tiles done, [16..] output row chunks
+  unsigned* tile_cnt;  // [max_tiles] finished gate/up items per tile
   float* hbuf;     // [(n_max*K + n_max)][FF]
   float* ybuf;     // [(n_max*K + n_max)][H]
   int n_max;
   int* status;
+  long long* prof;   // SGR_PROFILE builds only: [grid][8] cycle totals
 };
 
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct WsLayout {
-  size_t xq, logits, off, tile_e, tile_t0, meta, gslot, grows, cnt, hbuf, ybuf, total;
+  size_t xq, logits, off, rec, meta, gslot, grows, cnt, tile_cnt, hbuf, ybuf, total;
 };
 inline WsLayout ws_layout(int n_max, int H, int FF, int E, int K) {
   WsLayout l{};
@@ -88,12 +100,12 @@ inline WsLayout ws_layout(int n_max, int H, int FF, int E, int K) {
   l.xq = take(static_cast<size_t>(n_max) * (H / kQK) * kX8);
   l.logits = take(static_cast<size_t>(n_max) * E * 4);
   l.off = take(static_cast<size_t>(E + 2) * 4);
-  l.tile_e = take(tiles * 4);
-  l.tile_t0 = take(tiles * 4);
+  l.rec = take(tiles * 16);
   l.meta = take(16);
   l.gslot = take(static_cast<size_t>(n_max) * K * 4);
   l.grows = take(static_cast<size_t>(n_max) * K * 4);
-  l.cnt = take((16 + static_cast<size_t>(H) / 64 + 1) * 4);
+  l.cnt = take((16 + static_cast<size_t>(H) / 16 + 1) * 4);
+  l.tile_cnt = take(tiles * 4);
   l.hbuf = take(rows * FF * 4);
   l.ybuf = take(rows * H * 4);
   l.total = p;
@@ -153,8 +165,9 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
     if (L.sh[0] != nullptr && L.sh_hi > L.sh_lo) {
       sh_tiles = (L.sh_hi - L.sh_lo + kTokTile - 1) / kTokTile;
       for (int i = 0; i < sh_tiles; ++i) {
-        L.tile_e[at + i] = L.E;
-        L.tile_t0[at + i] = i * kTokTile;
+        const int t0 = i * kTokTile;
+        L.rec[at + i] = make_int4(L.E, min(kTokTile, L.sh_hi - L.sh_lo - t0),
+                                  L.n_max * L.K + L.sh_lo + t0, L.sh_lo + t0);
       }
     }
     L.off[L.E] = ar;
@@ -164,6 +177,7 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
     L.meta[3] = at;
     if (L.mail_n != nullptr) *L.mail_n = 0;
   }
+  for (int i = tid; i < L.n_max * L.K + L.n_max; i += blockDim.x) L.tile_cnt[i] = 0u;
   __syncthreads();
   {
     int ar = scan_rows[tid], at = scan_tiles[tid];
@@ -171,8 +185,7 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
       const int c = __popcll(mask[e]);
       L.off[e] = ar;
       for (int t0 = 0; t0 < c; t0 += kTokTile) {
-        L.tile_e[at] = e;
-        L.tile_t0[at] = t0;
+        L.rec[at] = make_int4(e, min(kTokTile, c - t0), ar + t0, ar + t0);
         ++at;
       }
       ar += c;
@@ -274,81 +287,72 @@ __global__ void __launch_bounds__(128) plan_kernel(const LayerDev L) {
   build_plan(L, smem);
 }
 
-// ---- shared decode of a tile index -------------------------------------------------------
-struct TileRef {
-  int e;        // expert, E = shared
-  int ntok;     // rows in this tile
-  int hrow0;    // first row of the tile in hbuf / ybuf
-  int p0;       // first grouped slot (routed) or first token row (shared)
+// ---- launch 2: the persistent expert kernel ----------------------------------------------
+struct ItemDesc {
+  int kind;     // 0 gate/up, 1 down
+  int mode;     // 0 weights arrive by TMA, 1 expert absent, 2 unaligned: consumers copy
+  int tile, chunk;
+  int e, ntok, hrow0, p0;
+  int row0, nrows;
+  int pad[2];
 };
-__device__ __forceinline__ bool decode_tile(const LayerDev& L, int tile, TileRef* t) {
-  if (tile >= L.meta[1]) return false;
-  t->e = L.tile_e[tile];
-  const int t0 = L.tile_t0[tile];
-  if (t->e == L.E) {
-    t->ntok = min(kTokTile, L.sh_hi - L.sh_lo - t0);
-    t->p0 = L.sh_lo + t0;
-    t->hrow0 = L.n_max * L.K + L.sh_lo + t0;
-  } else {
-    const int o = L.off[t->e];
-    t->ntok = min(kTokTile, L.off[t->e + 1] - o - t0);
-    t->p0 = o + t0;
-    t->hrow0 = o + t0;
-  }
-  return t->ntok > 0;
+
+struct StreamGeom {
+  int rows_gu, rows_dn;          // rows of one matrix per item
+  int ws_gu, ws_dn;              // shared-memory row strides
+  int chunks_gu, chunks_dn;
+  int stage_bytes;
+  int x_bytes;
+};
+__host__ __device__ inline StreamGeom stream_geom(int H, int FF) {
+  StreamGeom g;
+  const int nbh = H / kQK, nbf = FF / kQK;
+  g.rows_gu = tile_rows(nbh);
+  g.rows_dn = tile_rows(nbf);
+  g.ws_gu = tile_wstride(nbh);
+  g.ws_dn = tile_wstride(nbf);
+  g.chunks_gu = (FF + g.rows_gu - 1) / g.rows_gu;
+  g.chunks_dn = (H + g.rows_dn - 1) / g.rows_dn;
+  const int a = 2 * g.rows_gu * g.ws_gu, b = g.rows_dn * g.ws_dn;
+  g.stage_bytes = (a > b ? a : b);
+  const int xa = static_cast<int>(xtile_bytes(kTokTile, nbh)), xb = static_cast<int>(xtile_bytes(kTokTile, nbf));
+  g.x_bytes = (xa > xb ? xa : xb);
+  g.x_bytes = (g.x_bytes + 15) & ~15;
+  return g;
+}
+constexpr int kStreamHdr = 256 + kStages * 64;                 // barriers + flags, item descriptors
+constexpr int kStreamRed = kConsumerWarps * 2 * 2 * 128 * 4;   // [warp][matrix][token group][128]
+inline size_t stream_smem(int H, int FF) {
+  const StreamGeom g = stream_geom(H, FF);
+  return kStreamHdr + static_cast<size_t>(kStages) * g.stage_bytes + g.x_bytes + kStreamRed;
 }
 
-// ---- launch 2: gate + up + SwiGLU ------------------------------------------------------------
-// grid (FF / tile_rows(nbh), max tiles), 128 threads
-template <int TT>
-__global__ void __launch_bounds__(kTileThreads) gate_up_kernel(const LayerDev L) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  pdl_wait();
-  pdl_launch_dependents();
-  TileRef t;
-  if (!decode_tile(L, blockIdx.y, &t)) return;
-  const int rc = tile_rows(L.nbh);
-  const int row0 = blockIdx.x * rc;
-  const int nrows = min(rc, L.FF - row0);
-  const size_t row_bytes = static_cast<size_t>(L.nbh) * kW4;
-  const bool shared = t.e == L.E;
-  const unsigned char* wg = shared ? L.sh[0] : L.tab[t.e];
-  const unsigned char* wu = shared ? L.sh[1] : L.tab[L.E + t.e];
-  const unsigned char* wd = shared ? L.sh[2] : L.tab[2 * L.E + t.e];
-  if (wg == nullptr || wu == nullptr || wd == nullptr) {
-    // absent expert: the down kernel writes zero rows; post the id once per tile
-    if (L.mail != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && !shared) {
-      const int mi = atomicAdd(L.mail_n, 1);
-      if (mi < L.E) L.mail[mi] = t.e;
-    }
-    return;
-  }
-  const unsigned char* wsrc[2] = {wg + row0 * row_bytes, wu + row0 * row_bytes};
-  const unsigned char* xq = L.xq_in != nullptr ? L.xq_in : L.xq;
-  const size_t xrow_bytes = static_cast<size_t>(L.nbh) * kX8;
-  tile_run<2, TT>(
-      smem, wsrc, nrows, L.nbh, t.ntok,
-      [&](int i) {
-        const int r = shared ? t.p0 + i : L.grows[t.p0 + i];
-        return xq + r * xrow_bytes;
-      },
-      [&](int r, int t0, int nt, float (&res)[2][TT]) {
-#pragma unroll
-        for (int i = 0; i < TT; ++i)
-          if (i < nt) {
-            const float g = res[0][i], u = res[1][i];
-            L.hbuf[static_cast<size_t>(t.hrow0 + t0 + i) * L.FF + row0 + r] = g / (1.f + expf(-g)) * u;
-          }
-      },
-      L.status);
+#ifdef SGR_PROFILE
+#define PROF_T0() long long _pt = clock64()
+#define PROF_ADD(slot) do { const long long _n = clock64(); if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == _pw) \
+    atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + blockIdx.x * 8 + (slot)), static_cast<unsigned long long>(_n - _pt)); _pt = _n; } while (0)
+#else
+#define PROF_T0() do {} while (0)
+#define PROF_ADD(slot) do {} while (0)
+#endif
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
+
+__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 // Q8_K-quantise fp32 rows straight into a staged tile (one warp per 256 values;
 // arithmetic of src/kernels/cpu/q4_avx2.cpp:77-94 in the reference).
 __device__ __forceinline__ void stage_quantized_f32(const XTile& xt, int nt, const float* src,
-                                                    size_t row_stride) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int job = warp; job < nt * xt.nb; job += kTileThreads / 32) {
+                                                    size_t row_stride, int warp, int nwarps) {
+  const int lane = threadIdx.x & 31;
+  for (int job = warp; job < nt * xt.nb; job += nwarps) {
     const int t = job / xt.nb, blk = job - t * xt.nb;
     const float4* p = reinterpret_cast<const float4*>(src + t * row_stride + blk * kQK) + lane * 2;
     const float4 a = __ldcg(p), b = __ldcg(p + 1);
@@ -369,7 +373,7 @@ __device__ __forceinline__ void stage_quantized_f32(const XTile& xt, int nt, con
     }
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-    int8_t* qs = xt.qs + (static_cast<size_t>(t) * xt.nb + blk) * kXqStride + lane * 8;
+    int8_t* qs = xt.qs + static_cast<size_t>(t) * xt.tok_stride + blk * kXqStride + lane * 8;
     reinterpret_cast<uint32_t*>(qs)[0] = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) |
                                          (static_cast<uint32_t>(q[3] & 0xFF) << 24);
     reinterpret_cast<uint32_t*>(qs)[1] = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) |
@@ -379,68 +383,84 @@ __device__ __forceinline__ void stage_quantized_f32(const XTile& xt, int nt, con
   }
 }
 
-// ---- launch 3: down projection + combine ---------------------------------------------------------
-// grid (H / tile_rows(nbf), max tiles), 128 threads
-template <int TT>
-__global__ void __launch_bounds__(kTileThreads) down_kernel(const LayerDev L) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ int last_sh;
-  const int rc = tile_rows(L.nbf);
-  const int row0 = blockIdx.x * rc;
-  const int nrows = min(rc, L.H - row0);
-  const size_t row_bytes = static_cast<size_t>(L.nbf) * kW4;
-  // The plan is final here: this grid starts only after every gate_up CTA passed
-  // its own wait on the route kernel.
-  const int n_tiles = L.meta[1];
-  TileRef t;
-  const bool live = decode_tile(L, blockIdx.y, &t);
-  if (!live && !(blockIdx.y == 0 && n_tiles == 0)) return;
-
-  if (live) {
-    const bool shared = t.e == L.E;
-    const unsigned char* wg = shared ? L.sh[0] : L.tab[t.e];
-    const unsigned char* wu = shared ? L.sh[1] : L.tab[L.E + t.e];
-    const unsigned char* wd = shared ? L.sh[2] : L.tab[2 * L.E + t.e];
-    if (wg == nullptr || wu == nullptr || wd == nullptr) {
-      for (int i = threadIdx.x; i < nrows * t.ntok; i += kTileThreads)
-        L.ybuf[static_cast<size_t>(t.hrow0 + i / nrows) * L.H + row0 + i % nrows] = 0.f;
-      pdl_wait();
-    } else {
-      const unsigned char* wsrc[1] = {wd + row0 * row_bytes};
-      tile_run_staged<1, TT>(
-          smem, wsrc, nrows, L.nbf, t.ntok, [] { pdl_wait(); },
-          [&](const XTile& xt, int t0, int nt) {
-            stage_quantized_f32(xt, nt, L.hbuf + static_cast<size_t>(t.hrow0 + t0) * L.FF, L.FF);
-          },
-          [&](int r, int t0, int nt, float (&res)[1][TT]) {
-#pragma unroll
-            for (int i = 0; i < TT; ++i)
-              if (i < nt) L.ybuf[static_cast<size_t>(t.hrow0 + t0 + i) * L.H + row0 + r] = res[0][i];
-          },
-          L.status);
-    }
-  } else {
-    pdl_wait();
+// All eight consumer warps on one item: the (16-row group, super-block) units go
+// round the warps; warps that share a group meet in shared memory and the group's
+// first warp adds the partial sums in warp order (reproducible) and emits.
+template <int NMAT, int NT, typename Emit>
+__device__ __forceinline__ void item_compute(const unsigned char* w, int wstride, int mat_stride,
+                                             const XTile& xt, float* red, int nrows, int nb,
+                                             int ntok, Emit emit) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int groups = (nrows + 15) / 16;
+  const int units = groups * nb;
+  int grp, blk0, bstep, contrib;
+  bool active;
+  if (units <= kConsumerWarps) {          // one unit per warp
+    active = warp < units;
+    grp = warp / nb;
+    blk0 = warp - grp * nb;
+    bstep = nb;
+    contrib = nb;
+  } else {                                // a single group (host-checked): blocks go round the warps
+    active = warp < min(kConsumerWarps, nb);
+    grp = 0;
+    blk0 = warp;
+    bstep = kConsumerWarps;
+    contrib = min(kConsumerWarps, nb);
   }
-  pdl_launch_dependents();
+  float acc[NMAT][NT][4];
+  if (active) warp_mma_rows<NMAT, NT>(w, wstride, mat_stride, xt, grp * 16, nrows, nb, blk0, bstep, acc);
+  const int first = grp * (units <= kConsumerWarps ? nb : 0);   // first warp of this group
+  if (contrib > 1) {
+    if (active && warp != first) {
+#pragma unroll
+      for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) red[((warp * 2 + m) * 2 + n) * 128 + j * 32 + lane] = acc[m][n][j];
+    }
+    consumer_sync();
+    if (active && warp == first) {
+#pragma unroll
+      for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float v = acc[m][n][j];
+            for (int p = 1; p < contrib; ++p) v += red[(((first + p) * 2 + m) * 2 + n) * 128 + j * 32 + lane];
+            acc[m][n][j] = v;
+          }
+    }
+  }
+  if (active && warp == first) {
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = grp * 16 + gid + (j >> 1) * 8, t = 8 * n + 2 * tig + (j & 1);
+        if (r < nrows && t < ntok) {
+          float v[NMAT];
+#pragma unroll
+          for (int m = 0; m < NMAT; ++m) v[m] = acc[m][n][j];
+          emit(r, t, v);
+        }
+      }
+  }
+}
 
-  // last CTA of this row chunk blends
-  const unsigned expected = n_tiles > 0 ? static_cast<unsigned>(n_tiles) : 1u;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) last_sh = atomicAdd(&L.cnt[16 + blockIdx.x], 1u) == expected - 1 ? 1 : 0;
-  __syncthreads();
-  if (!last_sh) return;
-  __threadfence();
-  if (threadIdx.x == 0) L.cnt[16 + blockIdx.x] = 0u;
-  const bool has_shared = L.sh[0] != nullptr && L.sh[1] != nullptr && L.sh[2] != nullptr;
-  for (int i = threadIdx.x; i < nrows * L.n; i += kTileThreads) {
+// residual + sum_k w_k * y_k + shared expert for output rows [row0, row0+nrows), all tokens
+__device__ __forceinline__ void combine_rows(const LayerDev& L, int row0, int nrows, int tid, int nthr) {
+  const bool has_shared = L.sh[0] != nullptr;
+  for (int i = tid; i < nrows * L.n; i += nthr) {
     const int tk = i / nrows, r = row0 + i % nrows;
     const size_t o = static_cast<size_t>(tk) * L.H + r;
     float acc = (L.add_residual && L.x_f16 != nullptr) ? h2f(L.x_f16[o]) : 0.f;
     const float* wr = L.w + static_cast<size_t>(tk) * (L.K + 1);
     for (int kk = 0; kk < L.K; ++kk) {
-      const int gs = L.gslot[tk * L.K + kk];
+      const int gs = __ldcg(L.gslot + tk * L.K + kk);
       if (gs >= 0) acc += __ldcg(wr + kk) * __ldcg(L.ybuf + static_cast<size_t>(gs) * L.H + r);
     }
     if (has_shared && tk >= L.sh_lo && tk < L.sh_hi)
@@ -449,6 +469,233 @@ __global__ void __launch_bounds__(kTileThreads) down_kernel(const LayerDev L) {
     if (L.x_f16 != nullptr && L.add_residual) L.x_f16[o] = f2h(acc);
   }
 }
+
+__global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const LayerDev L) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const StreamGeom G = stream_geom(L.H, L.FF);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* empty = full + kStages;
+  int* flag = reinterpret_cast<int*>(smem + 128);                 // consumer broadcast slots
+  ItemDesc* desc = reinterpret_cast<ItemDesc*>(smem + 256);
+  unsigned char* stages = smem + kStreamHdr;
+  unsigned char* xbase = stages + static_cast<size_t>(kStages) * G.stage_bytes;
+  float* red = reinterpret_cast<float*>(xbase + G.x_bytes);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kConsumerWarps);
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+  pdl_wait();                       // plan, routing and quantised rows come from the route kernel
+  pdl_launch_dependents();
+
+  const int n_tiles = L.meta[1];
+  if (n_tiles == 0) {               // nothing routed here and no shared expert: residual only
+    if (warp < kConsumerWarps)
+      for (int c = blockIdx.x; c < G.chunks_dn; c += gridDim.x)
+        combine_rows(L, c * G.rows_dn, min(G.rows_dn, L.H - c * G.rows_dn), tid, kConsumers);
+    return;
+  }
+  const long long n_gu = static_cast<long long>(n_tiles) * G.chunks_gu;
+  const long long n_dn = static_cast<long long>(n_tiles) * G.chunks_dn;
+  const int gu_lo = static_cast<int>(n_gu * blockIdx.x / gridDim.x);
+  const int gu_cnt = static_cast<int>(n_gu * (blockIdx.x + 1) / gridDim.x) - gu_lo;
+  const int dn_lo = static_cast<int>(n_dn * blockIdx.x / gridDim.x);
+  const int dn_cnt = static_cast<int>(n_dn * (blockIdx.x + 1) / gridDim.x) - dn_lo;
+  const int n_items = gu_cnt + dn_cnt;
+  const size_t rb_h = static_cast<size_t>(L.nbh) * kW4, rb_f = static_cast<size_t>(L.nbf) * kW4;
+
+  if (warp == kConsumerWarps) {
+    // ---------------- producer warp ----------------
+#ifdef SGR_PROFILE
+    const int _pw = kConsumerWarps;
+#endif
+    PROF_T0();
+    for (int i = 0; i < n_items; ++i) {
+      const int s = i % kStages;
+      const unsigned ph = (i / kStages) & 1;
+      if (!mbar_wait(&empty[s], ph ^ 1u)) {
+        if (lane == 0) atomicExch(L.status, 2);
+        return;
+      }
+      PROF_ADD(5);
+      const int kind = i < gu_cnt ? 0 : 1;
+      const int id = kind == 0 ? gu_lo + i : dn_lo + (i - gu_cnt);
+      const int chunks = kind == 0 ? G.chunks_gu : G.chunks_dn;
+      const int tile = id / chunks, chunk = id - tile * chunks;
+      const int4 rc = __ldcg(L.rec + tile);
+      const bool shared = rc.x == L.E;
+      const unsigned char* w0 = shared ? L.sh[0] : L.tab[rc.x];
+      const unsigned char* w1 = shared ? L.sh[1] : L.tab[L.E + rc.x];
+      const unsigned char* w2 = shared ? L.sh[2] : L.tab[2 * L.E + rc.x];
+      const bool absent = w0 == nullptr || w1 == nullptr || w2 == nullptr;
+      const bool aligned = ((reinterpret_cast<uintptr_t>(w0) | reinterpret_cast<uintptr_t>(w1) |
+                             reinterpret_cast<uintptr_t>(w2)) & 15u) == 0;
+      const int rows_per = kind == 0 ? G.rows_gu : G.rows_dn;
+      const int row0 = chunk * rows_per;
+      const int nrows = min(rows_per, (kind == 0 ? L.FF : L.H) - row0);
+      const int mode = absent ? 1 : (aligned ? 0 : 2);
+      if (lane == 0) {
+        ItemDesc d;
+        d.kind = kind; d.mode = mode; d.tile = tile; d.chunk = chunk;
+        d.e = rc.x; d.ntok = rc.y; d.hrow0 = rc.z; d.p0 = rc.w;
+        d.row0 = row0; d.nrows = nrows; d.pad[0] = d.pad[1] = 0;
+        desc[s] = d;
+        const uint32_t bytes = mode != 0 ? 0u
+                               : static_cast<uint32_t>(nrows) * static_cast<uint32_t>(kind == 0 ? 2 * rb_h : rb_f);
+        mbar_expect_tx(&full[s], bytes);
+      }
+      __syncwarp();
+      if (mode == 0) {
+        unsigned char* st = stages + static_cast<size_t>(s) * G.stage_bytes;
+        if (kind == 0) {
+          const int ms = G.rows_gu * G.ws_gu;
+          for (int j = lane; j < 2 * nrows; j += 32) {
+            const int m = j / nrows, r = j - m * nrows;
+            bulk_g2s(st + m * ms + r * G.ws_gu, (m == 0 ? w0 : w1) + (row0 + r) * rb_h,
+                     static_cast<uint32_t>(rb_h), &full[s]);
+          }
+        } else {
+          for (int r = lane; r < nrows; r += 32)
+            bulk_g2s(st + r * G.ws_dn, w2 + (row0 + r) * rb_f, static_cast<uint32_t>(rb_f), &full[s]);
+        }
+      }
+      PROF_ADD(6);
+    }
+    return;
+  }
+
+  // ---------------- consumer warps ----------------
+  int cur_kind = -1, cur_tile = -1;
+  XTile xt = xtile_at(xbase, kTokTile, L.nbh);
+  const unsigned char* xq = L.xq_in != nullptr ? L.xq_in : L.xq;
+#ifdef SGR_PROFILE
+  const int _pw = 0;
+#endif
+  PROF_T0();
+  for (int i = 0; i < n_items; ++i) {
+    const int s = i % kStages;
+    const unsigned ph = (i / kStages) & 1;
+    if (!mbar_wait(&full[s], ph)) {
+      if (tid == 0) atomicExch(L.status, 3);
+      return;                                  // every consumer gives up on the same item
+    }
+    PROF_ADD(0);
+    const ItemDesc d = desc[s];
+    unsigned char* st = stages + static_cast<size_t>(s) * G.stage_bytes;
+    if (d.kind != cur_kind || d.tile != cur_tile) {
+      consumer_sync();                         // previous activation tile fully consumed
+      if (d.kind == 0) {
+        xt = xtile_at(xbase, kTokTile, L.nbh);
+        const bool shared = d.e == L.E;
+        xtile_stage(xt, d.ntok,
+                    [&](int t) {
+                      const int r = shared ? d.p0 + t : __ldcg(L.grows + d.p0 + t);
+                      return xq + static_cast<size_t>(r) * L.nbh * kX8;
+                    },
+                    tid, kConsumers);
+      } else {
+        xt = xtile_at(xbase, kTokTile, L.nbf);
+        if (tid == 0) {                        // wait for the gate/up items of this tile
+          unsigned it = 0;
+          while (ld_acquire(L.tile_cnt + d.tile) < static_cast<unsigned>(G.chunks_gu) && ++it < kSpinLimit)
+            __nanosleep(40);
+          flag[0] = it < kSpinLimit ? 1 : 0;
+        }
+        consumer_sync();
+        if (!flag[0]) {
+          if (tid == 0) atomicExch(L.status, 4);
+          return;
+        }
+        if (d.mode != 1)
+          stage_quantized_f32(xt, d.ntok, L.hbuf + static_cast<size_t>(d.hrow0) * L.FF, L.FF, warp,
+                              kConsumerWarps);
+      }
+      consumer_sync();
+      cur_kind = d.kind;
+      cur_tile = d.tile;
+      PROF_ADD(1);
+    }
+    if (d.mode == 2) {                         // unaligned weights: copy them here
+      if (d.kind == 0) {
+        const bool shared = d.e == L.E;
+        const unsigned char* w0 = shared ? L.sh[0] : L.tab[d.e];
+        const unsigned char* w1 = shared ? L.sh[1] : L.tab[L.E + d.e];
+        for (int r = 0; r < d.nrows; ++r) {
+          copy_unaligned(st + r * G.ws_gu, w0 + (d.row0 + r) * rb_h, static_cast<int>(rb_h), tid, kConsumers);
+          copy_unaligned(st + G.rows_gu * G.ws_gu + r * G.ws_gu, w1 + (d.row0 + r) * rb_h,
+                         static_cast<int>(rb_h), tid, kConsumers);
+        }
+      } else {
+        const unsigned char* w2 = d.e == L.E ? L.sh[2] : L.tab[2 * L.E + d.e];
+        for (int r = 0; r < d.nrows; ++r)
+          copy_unaligned(st + r * G.ws_dn, w2 + (d.row0 + r) * rb_f, static_cast<int>(rb_f), tid, kConsumers);
+      }
+      consumer_sync();
+    }
+
+    if (d.kind == 0) {
+      if (d.mode != 1) {
+        auto emit = [&](int r, int t, const float (&v)[2]) {
+          const float g = v[0], u = v[1];
+          L.hbuf[static_cast<size_t>(d.hrow0 + t) * L.FF + d.row0 + r] = g / (1.f + expf(-g)) * u;
+        };
+        if (d.ntok > 8)
+          item_compute<2, 2>(st, G.ws_gu, G.rows_gu * G.ws_gu, xt, red, d.nrows, L.nbh, d.ntok, emit);
+        else
+          item_compute<2, 1>(st, G.ws_gu, G.rows_gu * G.ws_gu, xt, red, d.nrows, L.nbh, d.ntok, emit);
+      } else if (d.chunk == 0 && tid == 0 && L.mail != nullptr && d.e != L.E) {
+        const int mi = atomicAdd(L.mail_n, 1);          // absent expert: post the id once per tile
+        if (mi < L.E) L.mail[mi] = d.e;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);            // this warp is done with the stage
+      PROF_ADD(2);
+      __threadfence();
+      consumer_sync();
+      if (tid == 0) atomicAdd(L.tile_cnt + d.tile, 1u);
+      PROF_ADD(3);
+    } else {
+      if (d.mode != 1) {
+        auto emit = [&](int r, int t, const float (&v)[1]) {
+          L.ybuf[static_cast<size_t>(d.hrow0 + t) * L.H + d.row0 + r] = v[0];
+        };
+        if (d.ntok > 8)
+          item_compute<1, 2>(st, G.ws_dn, 0, xt, red, d.nrows, L.nbf, d.ntok, emit);
+        else
+          item_compute<1, 1>(st, G.ws_dn, 0, xt, red, d.nrows, L.nbf, d.ntok, emit);
+      } else {
+        for (int j = tid; j < d.nrows * d.ntok; j += kConsumers)
+          L.ybuf[static_cast<size_t>(d.hrow0 + j / d.nrows) * L.H + d.row0 + j % d.nrows] = 0.f;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+      PROF_ADD(2);
+      __threadfence();
+      consumer_sync();
+      if (tid == 0) {
+        const unsigned prev = atomicAdd(&L.cnt[16 + d.chunk], 1u);
+        flag[1] = prev == static_cast<unsigned>(n_tiles) - 1 ? 1 : 0;
+        if (flag[1]) L.cnt[16 + d.chunk] = 0u;
+      }
+      consumer_sync();
+      if (flag[1]) {                                    // last tile of this row chunk: blend
+        __threadfence();
+        combine_rows(L, d.row0, d.nrows, tid, kConsumers);
+      }
+      PROF_ADD(4);
+    }
+  }
+}
+
+#ifdef SGR_PROFILE
+long long* g_prof_buf = nullptr;
+#endif
 
 template <typename Kern>
 int launch_pdl(Kern kern, dim3 grid, int threads, size_t smem, cudaStream_t stream,
@@ -487,8 +734,8 @@ SGR_API int sgr_moe_layer_workspace_init(void* workspace, size_t bytes, void* st
   return cudaMemsetAsync(workspace, 0, bytes, as_stream(stream)) == cudaSuccess ? kOk : kErrLaunch;
 }
 
-SGR_API int sgr_moe_layer_decode(const sgr_moe_layer* a, void* stream) {
-  if (a == nullptr) return kErrArg;
+SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void* stream) {
+  if (a == nullptr || (stages & 7) == 0) return kErrArg;
   if (a->n <= 0) return kOk;
   if (a->hidden <= 0 || a->hidden % kQK || a->n_ff <= 0 || a->n_ff % kQK || a->n_expert <= 0 ||
       a->n_used <= 0 || a->n_used > a->n_expert || a->n_max < a->n || a->n_max > kMaxRows)
@@ -535,8 +782,8 @@ SGR_API int sgr_moe_layer_decode(const sgr_moe_layer* a, void* stream) {
   L.xq = ws + lay.xq;
   L.logits = reinterpret_cast<float*>(ws + lay.logits);
   L.off = reinterpret_cast<int*>(ws + lay.off);
-  L.tile_e = reinterpret_cast<int*>(ws + lay.tile_e);
-  L.tile_t0 = reinterpret_cast<int*>(ws + lay.tile_t0);
+  L.rec = reinterpret_cast<int4*>(ws + lay.rec);
+  L.tile_cnt = reinterpret_cast<unsigned*>(ws + lay.tile_cnt);
   L.meta = reinterpret_cast<int*>(ws + lay.meta);
   L.gslot = reinterpret_cast<int*>(ws + lay.gslot);
   L.grows = reinterpret_cast<int*>(ws + lay.grows);
@@ -545,10 +792,19 @@ SGR_API int sgr_moe_layer_decode(const sgr_moe_layer* a, void* stream) {
   L.ybuf = reinterpret_cast<float*>(ws + lay.ybuf);
   L.n_max = a->n_max;
   L.status = status_word();
+#ifdef SGR_PROFILE
+  if (g_prof_buf == nullptr) {
+    cudaMalloc(&g_prof_buf, 1024 * 8 * sizeof(long long));
+    cudaMemset(g_prof_buf, 0, 1024 * 8 * sizeof(long long));
+  }
+  L.prof = g_prof_buf;
+#endif
   cudaStream_t s = as_stream(stream);
 
-  int rc;
-  if (!a->routing_given) {
+  int rc = kOk;
+  if (!(stages & 1)) {
+    // plan, xq and routing are taken from the workspace as a previous call left them
+  } else if (!a->routing_given) {
     const size_t smem = std::max<size_t>(
         std::max<size_t>(static_cast<size_t>(kRouteTok) * L.H * 2, static_cast<size_t>(kRouteWarps) * L.E * 4),
         plan_smem(L.E));
@@ -560,17 +816,34 @@ SGR_API int sgr_moe_layer_decode(const sgr_moe_layer* a, void* stream) {
   }
   if (rc != kOk) return rc;
 
-  const int local_e = L.e_hi - L.e_lo;
-  const int routed_tiles = std::min(L.n * L.K, local_e + L.n * L.K / kTokTile);
-  const int max_tiles = std::max(1, routed_tiles + (L.sh_hi - L.sh_lo + kTokTile - 1) / kTokTile);
-  const dim3 g2((L.FF + tile_rows(L.nbh) - 1) / tile_rows(L.nbh), max_tiles);
-  const dim3 g3((L.H + tile_rows(L.nbf) - 1) / tile_rows(L.nbf), max_tiles);
-  if (L.n == 1) {
-    rc = launch_pdl(gate_up_kernel<1>, g2, kTileThreads, tile_smem(2, L.nbh, 1), s, L);
-    if (rc != kOk) return rc;
-    return launch_pdl(down_kernel<1>, g3, kTileThreads, tile_smem(1, L.nbf, 1), s, L);
+  if (stages & 6) {
+    // geometry the consumer mapping was written for: a tile of rows is one 16-row
+    // group, or at most eight (group, super-block) units
+    const StreamGeom g = stream_geom(L.H, L.FF);
+    auto units_ok = [](int rows, int nb) { const int grp = (rows + 15) / 16; return grp == 1 || grp * nb <= kConsumerWarps; };
+    if (!units_ok(g.rows_gu, L.nbh) || !units_ok(g.rows_dn, L.nbf)) return kErrUnsupported;
+    const size_t smem = stream_smem(L.H, L.FF);
+    if (smem > 227 * 1024) return kErrUnsupported;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      return kErrLaunch;
+    rc = launch_pdl(expert_stream_kernel, dim3(sms), kStreamThreads, smem, s, L);
   }
-  rc = launch_pdl(gate_up_kernel<4>, g2, kTileThreads, tile_smem(2, L.nbh, 4), s, L);
-  if (rc != kOk) return rc;
-  return launch_pdl(down_kernel<4>, g3, kTileThreads, tile_smem(1, L.nbf, 4), s, L);
+  return rc;
+}
+
+#ifdef SGR_PROFILE
+// profiling builds: copy out (and clear) the per-CTA cycle totals [grid][8]
+extern "C" __attribute__((visibility("default"))) int sgr_prof_read(long long* host_out, int n) {
+  if (g_prof_buf == nullptr) return -1;
+  cudaDeviceSynchronize();
+  cudaMemcpy(host_out, g_prof_buf, static_cast<size_t>(n) * sizeof(long long), cudaMemcpyDeviceToHost);
+  cudaMemset(g_prof_buf, 0, 1024 * 8 * sizeof(long long));
+  return 0;
+}
+#endif
+
+SGR_API int sgr_moe_layer_decode(const sgr_moe_layer* a, void* stream) {
+  return sgr_moe_layer_decode_stages(a, 7, stream);
 }

@@ -96,17 +96,27 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 
 // ---- staged activations -------------------------------------------------------
 // One tile of up to TT Q8_K rows re-laid for 16-byte shared loads:
-//   qs   [TT][nb][272]  int8 codes (256 used)
-//   bs   [TT][nb][8]    int16 sub-block sums (one uint4 per block)
-//   d    [TT][nb]       fp32 scales
+//   qs   [TT][tok_stride]   int8 codes, 272 bytes per block (256 used)
+//   bs   [TT][nb][8]        int16 sub-block sums (one uint4 per block)
+//   d    [TT][nb]           fp32 scales
+// Blocks are 68 words apart and token rows tok_stride/4 = 4 (mod 8) words apart,
+// so eight lanes that read the same 16 bytes of eight different blocks - or of
+// eight different tokens - touch eight distinct 4-bank groups.
+__host__ __device__ constexpr int xtile_tok_stride(int nb) {
+  return nb * kXqStride + ((nb & 1) ? 0 : 16);
+}
+
 struct XTile {
   int8_t* qs;
   int16_t* bs;
   float* d;
   int nb;
+  int tok_stride;
+  __device__ __forceinline__ const int8_t* code_ptr(int t, int blk, int sb) const {
+    return qs + static_cast<size_t>(t) * tok_stride + blk * kXqStride + sb * 32;
+  }
   __device__ __forceinline__ const uint4* codes(int t, int blk, int sb) const {
-    return reinterpret_cast<const uint4*>(qs + (static_cast<size_t>(t) * nb + blk) * kXqStride +
-                                          sb * 32);
+    return reinterpret_cast<const uint4*>(code_ptr(t, blk, sb));
   }
   __device__ __forceinline__ uint4 sums(int t, int blk) const {
     return *reinterpret_cast<const uint4*>(bs + (static_cast<size_t>(t) * nb + blk) * 8);
@@ -115,15 +125,16 @@ struct XTile {
 };
 
 __host__ __device__ constexpr size_t xtile_bytes(int tt, int nb) {
-  return static_cast<size_t>(tt) * nb * (kXqStride + 16 + 4);
+  return static_cast<size_t>(tt) * (xtile_tok_stride(nb) + nb * (16 + 4));
 }
 
 __device__ __forceinline__ XTile xtile_at(unsigned char* base, int tt, int nb) {
   XTile x;
-  x.qs = reinterpret_cast<int8_t*>(base);
-  x.bs = reinterpret_cast<int16_t*>(base + static_cast<size_t>(tt) * nb * kXqStride);
-  x.d = reinterpret_cast<float*>(base + static_cast<size_t>(tt) * nb * (kXqStride + 16));
   x.nb = nb;
+  x.tok_stride = xtile_tok_stride(nb);
+  x.qs = reinterpret_cast<int8_t*>(base);
+  x.bs = reinterpret_cast<int16_t*>(base + static_cast<size_t>(tt) * x.tok_stride);
+  x.d = reinterpret_cast<float*>(base + static_cast<size_t>(tt) * (x.tok_stride + nb * 16));
   return x;
 }
 
@@ -143,7 +154,7 @@ __device__ __forceinline__ void xtile_stage(const XTile& xt, int nt, RowOf row_o
     if (w == 0) {
       xt.d[t * xt.nb + blk] = __uint_as_float(v);
     } else if (w <= 64) {
-      reinterpret_cast<uint32_t*>(xt.qs + (static_cast<size_t>(t) * xt.nb + blk) * kXqStride)[w - 1] = v;
+      reinterpret_cast<uint32_t*>(xt.qs + static_cast<size_t>(t) * xt.tok_stride + blk * kXqStride)[w - 1] = v;
     } else {
       reinterpret_cast<uint32_t*>(xt.bs + (static_cast<size_t>(t) * xt.nb + blk) * 8)[w - 65] = v;
     }
@@ -179,49 +190,62 @@ __device__ __forceinline__ int dot8(const uint32_t (&w)[8], const uint4& a, cons
   return acc;
 }
 
-// One Q4_K block (in shared memory, 16-byte aligned) against `nt` staged
-// activation rows. For every token the eight sub-block dots are integers
-// (exact); they are combined as
-//     acc[t] += xd * ( d * sum_s sc[s]*dot[s]  -  dmin * sum_s mn[s]*bsum[s] )
-// with both inner sums held in int32 (|.| <= 8*63*60960 < 2^25), so only the
-// last line rounds. The reference rounds sd = d*sc first and sums eight fp32
-// terms (q4_k.cu:57-91, q4_avx2.cpp:124-145); the two agree to fp32 rounding.
-// If dots_out != nullptr the raw sub-block dots of token 0 are stored there.
-template <int TT>
-__device__ __forceinline__ void block_dot(const uint4* __restrict__ wblk, const XTile& xt, int blk,
-                                          int nt, float (&acc)[TT], int* dots_out = nullptr) {
-  const uint4 hdr = wblk[0];
-  const float d = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x & 0xFFFFu)));
-  const float dmin = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x >> 16)));
-  const Scales6 s6 = unpack_scales6(hdr.y, hdr.z, hdr.w);
-
-  int isum[TT];
+// The same block position `blk` of NMAT weight rows (blocks in shared memory,
+// 16-byte aligned) against `nt` staged activation rows; the activation codes are
+// loaded once and used for every matrix. For every token the eight sub-block dots
+// are integers (exact); they are combined as
+//     acc += xd * ( d * sum_s sc[s]*dot[s]  -  dmin * sum_s mn[s]*bsum[s] )
+// with both inner sums held in int32 (|.| <= 8*63*60960 < 2^25), so only the last
+// line rounds. The reference rounds sd = d*sc first and sums eight fp32 terms
+// (q4_k.cu:57-91, q4_avx2.cpp:124-145); the two agree to fp32 rounding.
+// If dots_out != nullptr the raw sub-block dots of matrix 0, token 0 are stored.
+template <int NMAT, int TT>
+__device__ __forceinline__ void block_dot(const uint4* const (&wblk)[NMAT], const XTile& xt,
+                                          int blk, int nt, float (&acc)[NMAT][TT],
+                                          int* dots_out = nullptr) {
+  float d[NMAT], dmin[NMAT];
+  Scales6 s6[NMAT];
+  int isum[NMAT][TT];
 #pragma unroll
-  for (int t = 0; t < TT; ++t) isum[t] = 0;
-
+  for (int m = 0; m < NMAT; ++m) {
+    const uint4 hdr = wblk[m][0];
+    d[m] = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x & 0xFFFFu)));
+    dmin[m] = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x >> 16)));
+    s6[m] = unpack_scales6(hdr.y, hdr.z, hdr.w);
+#pragma unroll
+    for (int t = 0; t < TT; ++t) isum[m][t] = 0;
+  }
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
-    const uint4 q0 = wblk[1 + 2 * g];
-    const uint4 q1 = wblk[2 + 2 * g];
-    const uint32_t raw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-    uint32_t lo[8], hi[8];
+    uint32_t lo[NMAT][8], hi[NMAT][8];
+    int sc_lo[NMAT], sc_hi[NMAT];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      lo[i] = raw[i] & 0x0F0F0F0Fu;
-      hi[i] = (raw[i] >> 4) & 0x0F0F0F0Fu;
+    for (int m = 0; m < NMAT; ++m) {
+      const uint4 q0 = wblk[m][1 + 2 * g];
+      const uint4 q1 = wblk[m][2 + 2 * g];
+      const uint32_t raw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        lo[m][i] = raw[i] & 0x0F0F0F0Fu;
+        hi[m][i] = (raw[i] >> 4) & 0x0F0F0F0Fu;
+      }
+      sc_lo[m] = (s6[m].sc[g >> 1] >> (16 * (g & 1))) & 0xFF;       // scale of sub-block 2g
+      sc_hi[m] = (s6[m].sc[g >> 1] >> (16 * (g & 1) + 8)) & 0xFF;   // scale of sub-block 2g+1
     }
-    const int sc_lo = (s6.sc[g >> 1] >> (16 * (g & 1))) & 0xFF;       // scale of sub-block 2g
-    const int sc_hi = (s6.sc[g >> 1] >> (16 * (g & 1) + 8)) & 0xFF;   // scale of sub-block 2g+1
 #pragma unroll
     for (int t = 0; t < TT; ++t) {
       if (t < nt) {
         const uint4* xa = xt.codes(t, blk, 2 * g);
-        const int dl = dot8(lo, xa[0], xa[1]);
-        const int dh = dot8(hi, xa[2], xa[3]);
-        isum[t] += sc_lo * dl + sc_hi * dh;
-        if (dots_out != nullptr && t == 0) {
-          dots_out[2 * g] = dl;
-          dots_out[2 * g + 1] = dh;
+        const uint4 x0 = xa[0], x1 = xa[1], x2 = xa[2], x3 = xa[3];
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) {
+          const int dl = dot8(lo[m], x0, x1);
+          const int dh = dot8(hi[m], x2, x3);
+          isum[m][t] += sc_lo[m] * dl + sc_hi[m] * dh;
+          if (dots_out != nullptr && t == 0 && m == 0) {
+            dots_out[2 * g] = dl;
+            dots_out[2 * g + 1] = dh;
+          }
         }
       }
     }
@@ -230,13 +254,16 @@ __device__ __forceinline__ void block_dot(const uint4* __restrict__ wblk, const 
   for (int t = 0; t < TT; ++t) {
     if (t < nt) {
       const uint4 bs = xt.sums(t, blk);
-      // bs.x = bsum0 | bsum1<<16 ... ; mn[0] bytes = mins 0..3
-      int msum = __dp2a_lo(static_cast<int>(bs.x), static_cast<int>(s6.mn[0]), 0);
-      msum = __dp2a_hi(static_cast<int>(bs.y), static_cast<int>(s6.mn[0]), msum);
-      msum = __dp2a_lo(static_cast<int>(bs.z), static_cast<int>(s6.mn[1]), msum);
-      msum = __dp2a_hi(static_cast<int>(bs.w), static_cast<int>(s6.mn[1]), msum);
-      acc[t] += xt.scale(t, blk) *
-                (d * static_cast<float>(isum[t]) - dmin * static_cast<float>(msum));
+      const float xd = xt.scale(t, blk);
+#pragma unroll
+      for (int m = 0; m < NMAT; ++m) {
+        // bs.x = bsum0 | bsum1<<16 ... ; mn[0] bytes = mins 0..3
+        int msum = __dp2a_lo(static_cast<int>(bs.x), static_cast<int>(s6[m].mn[0]), 0);
+        msum = __dp2a_hi(static_cast<int>(bs.y), static_cast<int>(s6[m].mn[0]), msum);
+        msum = __dp2a_lo(static_cast<int>(bs.z), static_cast<int>(s6[m].mn[1]), msum);
+        msum = __dp2a_hi(static_cast<int>(bs.w), static_cast<int>(s6[m].mn[1]), msum);
+        acc[m][t] += xd * (d[m] * static_cast<float>(isum[m][t]) - dmin[m] * static_cast<float>(msum));
+      }
     }
   }
 }

@@ -67,36 +67,64 @@ class MoeLayerRunner:
 
 
 class MoeStack:
-    """L layers of synthetic weights and a graph-replayed decode step: the residual
-    stream x [n][H] fp16 goes through the MoE half of every layer in turn (each
-    layer reads x as its input and adds its output to it)."""
+    """L layers of weights and a graph-replayed decode step over them.
 
-    def __init__(self, layers, n_max, n_used, device, biases=None):
+    The residual stream x [n][H] fp16 passes through the MoE half of every layer in
+    turn: layer l reads its input rows from `inputs[l]` (or from x itself when no
+    inputs are given) and adds its output to x. With `per_layer_ws` every layer
+    keeps its own workspace, so that after a step each layer's plan and staged
+    activations are still there and single stages can be re-launched (timing)."""
+
+    def __init__(self, layers, n_max, n_used, device, biases=None, inputs=None,
+                 per_layer_ws=False):
         self.layers = layers
         w0 = layers[0]
         self.device = device
-        self.runner = MoeLayerRunner(n_max, w0.hidden, w0.n_ff, w0.n_expert, n_used, device)
+        n_ws = len(layers) if per_layer_ws else 1
+        self.runners = [MoeLayerRunner(n_max, w0.hidden, w0.n_ff, w0.n_expert, n_used, device)
+                        for _ in range(n_ws)]
+        self.runner = self.runners[0]
         self.tables = [w.table() for w in layers]
         self.biases = biases
+        self.inputs = inputs
         self.n_used = n_used
         self.graph = None
         self.x = torch.zeros(n_max, w0.hidden, dtype=torch.float16, device=device)
         # per-layer routing records, so a finished step can be inspected
         self.idx = torch.zeros(len(layers), n_max, n_used + 1, dtype=torch.int32, device=device)
         self.w = torch.zeros(len(layers), n_max, n_used + 1, dtype=torch.float32, device=device)
-        self._args = []
+        self.launches_per_step = 2 * len(layers)     # route + experts
 
-    def _issue(self, n):
-        self._args = []
-        for li, w in enumerate(self.layers):
-            a = self.runner.args(n, self.x, w.router, self.tables[li], w.shared_ptrs(),
-                                 x_f16=self.x, bias=None if self.biases is None else self.biases[li],
-                                 route_idx=self.idx[li], route_w=self.w[li])
-            self._args.append(a)
-            self.runner.run(a)
+    def layer_args(self, li, n):
+        w = self.layers[li]
+        r = self.runners[li % len(self.runners)]
+        xn = self.x if self.inputs is None else self.inputs[li]
+        return r, r.args(n, xn, w.router, self.tables[li], w.shared_ptrs(), x_f16=self.x,
+                         bias=None if self.biases is None else self.biases[li],
+                         route_idx=self.idx[li], route_w=self.w[li])
+
+    def _issue(self, n, stages=7):
+        for li in range(len(self.layers)):
+            r, a = self.layer_args(li, n)
+            lib().call("sgr_moe_layer_decode_stages", C.byref(a), stages, stream_ptr())
 
     def step_eager(self, n):
         self._issue(n)
+
+    def stage_only(self, n, stages):
+        """Re-launch one stage of every layer back to back (needs per_layer_ws and a
+        finished step)."""
+        assert len(self.runners) == len(self.layers)
+        self._issue(n, stages)
+
+    def capture_stage(self, n, stages):
+        """A graph of one stage of every layer back to back (needs per_layer_ws and a
+        finished step, whose plans the workspaces still hold)."""
+        assert len(self.runners) == len(self.layers)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._issue(n, stages)
+        return g
 
     def capture(self, n):
         s = torch.cuda.Stream(device=self.device)

@@ -40,3 +40,34 @@ def test_shim_header_compiles_against_c_abi():
     res = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-I", os.path.join(ROOT, "include"),
                           "-x", "c++", "-"], input=src, capture_output=True, text=True)
     assert res.returncode == 0, res.stderr
+
+
+def test_shim_defines_exactly_the_reference_launchers(tmp_path):
+    """Link check against the reference's own header: a translation unit that only
+    sees include/sager/kernels/cuda_ops.hpp takes the address of every launcher the
+    shim claims to provide; it links only if the shim defines those exact
+    signatures. Needs the reference tree and the CUDA headers."""
+    import pytest
+    ref_inc = "/root/reference/include"
+    cuda_inc = "/usr/local/cuda/include"
+    if not (os.path.isdir(ref_inc) and os.path.isdir(cuda_inc)):
+        pytest.skip("reference tree or CUDA headers not present")
+    import re
+    shim = open(os.path.join(ROOT, "include", "sager_b200_shim.hpp")).read()
+    body = shim.split("int b200_last_error();", 1)[1].split("#ifdef SAGER_B200_SHIM_IMPLEMENTATION", 1)[0]
+    names = re.findall(r"^void (\w+)\(", body, flags=re.M)
+    assert len(names) >= 36
+    user = tmp_path / "user.cpp"
+    user.write_text('#include "sager/kernels/cuda_ops.hpp"\n'
+                    "const void* volatile sink[] = {\n" +
+                    "".join(f"  reinterpret_cast<const void*>(&sager::cuda::{n}),\n" for n in names) +
+                    "};\nint main() { return sink[0] != nullptr ? 0 : 1; }\n")
+    impl = tmp_path / "impl.cpp"
+    impl.write_text('#include "sager/kernels/cuda_ops.hpp"\n#define SAGER_B200_SHIM_IMPLEMENTATION\n'
+                    '#include "sager_b200_shim.hpp"\n')
+    lib = sbuild.build()
+    exe = tmp_path / "a.out"
+    cmd = ["g++", "-std=c++20", "-I", ref_inc, "-I", cuda_inc, "-I", os.path.join(ROOT, "include"),
+           str(user), str(impl), lib, f"-Wl,-rpath,{os.path.dirname(lib)}", "-o", str(exe)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-3000:]
