@@ -42,12 +42,14 @@ namespace sgr {
 namespace {
 
 constexpr int kMaxRows = 64;       // token rows per call (row masks are 64-bit)
-constexpr int kTokTile = 16;       // token rows per tile of the expert kernel
+constexpr int kTokTile = 8;        // token rows per tile of the expert kernel (one MMA n-tile)
 constexpr int kRouteTok = 8;       // token rows per CTA of the route kernel
 constexpr int kRouteWarps = 4;
 
-constexpr int kConsumerWarps = 8;
-constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kTeams = 2;                         // consumer teams, items alternate between them
+constexpr int kTeamWarps = 8;
+constexpr int kTeamThreads = kTeamWarps * 32;
+constexpr int kConsumers = kTeams * kTeamThreads;
 constexpr int kStreamThreads = kConsumers + 32;   // + one producer warp
 constexpr int kStages = 4;
 constexpr unsigned kSpinLimit = 1u << 22;         // bounded waits: give up, raise the status word
@@ -77,7 +79,7 @@ struct LayerDev {
   int* meta;       // {routed rows, tiles incl. shared, bad ids, routed tiles}
   int* gslot;      // [n*K] grouped slot of a route, -1 = not computed here
   int* grows;      // [n*K] source row of a grouped slot
-  unsigned* cnt;   // [0..7] route tiles, [8] route tiles done, [16..] output row chunks
+  unsigned* cnt;   // [0..7] route tiles, [8] route tiles done, [9] expert kernel grid barrier
   unsigned* tile_cnt;  // [max_tiles] finished gate/up items per tile
   float* hbuf;     // [(n_max*K + n_max)][FF]
   float* ybuf;     // [(n_max*K + n_max)][H]
@@ -176,6 +178,7 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
     L.meta[2] = bad_sh;
     L.meta[3] = at;
     if (L.mail_n != nullptr) *L.mail_n = 0;
+    L.cnt[9] = 0u;                        // grid barrier of the expert kernel
   }
   for (int i = tid; i < L.n_max * L.K + L.n_max; i += blockDim.x) L.tile_cnt[i] = 0u;
   __syncthreads();
@@ -302,42 +305,48 @@ struct StreamGeom {
   int ws_gu, ws_dn;              // shared-memory row strides
   int chunks_gu, chunks_dn;
   int stage_bytes;
-  int x_bytes;
+  int x_bytes;                   // one team's activation tile
 };
 __host__ __device__ inline StreamGeom stream_geom(int H, int FF) {
   StreamGeom g;
   const int nbh = H / kQK, nbf = FF / kQK;
   g.rows_gu = tile_rows(nbh);
   g.rows_dn = tile_rows(nbf);
-  g.ws_gu = tile_wstride(nbh);
-  g.ws_dn = tile_wstride(nbf);
+  // Packed rows: one bulk copy brings a whole matrix tile. Issuing a copy per row
+  // (to pad the row stride) costs the producer warp more than the 8-way bank
+  // conflicts of the four weight ldmatrix per unit cost the consumers.
+  g.ws_gu = nbh * kW4;
+  g.ws_dn = nbf * kW4;
   g.chunks_gu = (FF + g.rows_gu - 1) / g.rows_gu;
   g.chunks_dn = (H + g.rows_dn - 1) / g.rows_dn;
   const int a = 2 * g.rows_gu * g.ws_gu, b = g.rows_dn * g.ws_dn;
-  g.stage_bytes = (a > b ? a : b);
+  g.stage_bytes = ((a > b ? a : b) + 127) & ~127;
   const int xa = static_cast<int>(xtile_bytes(kTokTile, nbh)), xb = static_cast<int>(xtile_bytes(kTokTile, nbf));
-  g.x_bytes = (xa > xb ? xa : xb);
-  g.x_bytes = (g.x_bytes + 15) & ~15;
+  g.x_bytes = ((xa > xb ? xa : xb) + 127) & ~127;
   return g;
 }
-constexpr int kStreamHdr = 256 + kStages * 64;                 // barriers + flags, item descriptors
-constexpr int kStreamRed = kConsumerWarps * 2 * 2 * 128 * 4;   // [warp][matrix][token group][128]
+constexpr int kStreamHdr = 512;                                          // barriers, flags, item descriptors
+constexpr int kTeamRed = 2 * kTeamWarps * 2 * 128 * 4;                   // two buffers of [warp][matrix][128] floats
 inline size_t stream_smem(int H, int FF) {
   const StreamGeom g = stream_geom(H, FF);
-  return kStreamHdr + static_cast<size_t>(kStages) * g.stage_bytes + g.x_bytes + kStreamRed;
+  return kStreamHdr + static_cast<size_t>(kStages) * g.stage_bytes + kTeams * (g.x_bytes + kTeamRed);
 }
 
 #ifdef SGR_PROFILE
 #define PROF_T0() long long _pt = clock64()
 #define PROF_ADD(slot) do { const long long _n = clock64(); if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == _pw) \
-    atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + blockIdx.x * 8 + (slot)), static_cast<unsigned long long>(_n - _pt)); _pt = _n; } while (0)
+    atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + blockIdx.x * 16 + (slot)), static_cast<unsigned long long>(_n - _pt)); _pt = _n; } while (0)
 #else
 #define PROF_T0() do {} while (0)
 #define PROF_ADD(slot) do {} while (0)
 #endif
 
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
-
+__device__ __forceinline__ void team_sync(int team) {
+  asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "n"(kTeamThreads) : "memory");
+}
+__device__ __forceinline__ void consumers_sync() {
+  asm volatile("bar.sync 3, %0;" ::"n"(kConsumers) : "memory");
+}
 __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
   unsigned v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -383,79 +392,78 @@ __device__ __forceinline__ void stage_quantized_f32(const XTile& xt, int nt, con
   }
 }
 
-// All eight consumer warps on one item: the (16-row group, super-block) units go
-// round the warps; warps that share a group meet in shared memory and the group's
-// first warp adds the partial sums in warp order (reproducible) and emits.
-template <int NMAT, int NT, typename Emit>
-__device__ __forceinline__ void item_compute(const unsigned char* w, int wstride, int mat_stride,
-                                             const XTile& xt, float* red, int nrows, int nb,
-                                             int ntok, Emit emit) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int gid = lane >> 2, tig = lane & 3;
+// One team (eight warps) on one item. The (16-row group, super-block) units go
+// round the team's warps; every warp leaves its partial sums in shared memory,
+// the stage is released, and after one team barrier all 256 threads add the
+// partials of their output element in warp order (reproducible) and emit it.
+//   emit(row, token, v[NMAT])
+template <int NMAT, typename Emit>
+__device__ __forceinline__ void item_compute(const LayerDev& L, const unsigned char* w, int wstride,
+                                             int mat_stride, const XTile& xt, float* red, int nrows,
+                                             int nb, int ntok, int team, uint64_t* release, Emit emit) {
+#ifdef SGR_PROFILE
+  const int _pw = 0;
+#endif
+  PROF_T0();
+  const int tw = (threadIdx.x >> 5) & (kTeamWarps - 1), lane = threadIdx.x & 31;
+  const int ttid = threadIdx.x & (kTeamThreads - 1);
   const int groups = (nrows + 15) / 16;
   const int units = groups * nb;
   int grp, blk0, bstep, contrib;
   bool active;
-  if (units <= kConsumerWarps) {          // one unit per warp
-    active = warp < units;
-    grp = warp / nb;
-    blk0 = warp - grp * nb;
+  if (units <= kTeamWarps) {              // one unit per warp
+    active = tw < units;
+    grp = tw / nb;
+    blk0 = tw - grp * nb;
     bstep = nb;
     contrib = nb;
   } else {                                // a single group (host-checked): blocks go round the warps
-    active = warp < min(kConsumerWarps, nb);
+    active = tw < min(kTeamWarps, nb);
     grp = 0;
-    blk0 = warp;
-    bstep = kConsumerWarps;
-    contrib = min(kConsumerWarps, nb);
+    blk0 = tw;
+    bstep = kTeamWarps;
+    contrib = min(kTeamWarps, nb);
   }
-  float acc[NMAT][NT][4];
-  if (active) warp_mma_rows<NMAT, NT>(w, wstride, mat_stride, xt, grp * 16, nrows, nb, blk0, bstep, acc);
-  const int first = grp * (units <= kConsumerWarps ? nb : 0);   // first warp of this group
-  if (contrib > 1) {
-    if (active && warp != first) {
+  if (active) {
+    float acc[NMAT][1][4];
+    warp_mma_rows<NMAT, 1>(w, wstride, mat_stride, xt, grp * 16, nrows, nb, blk0, bstep, acc);
 #pragma unroll
-      for (int m = 0; m < NMAT; ++m)
+    for (int m = 0; m < NMAT; ++m)
 #pragma unroll
-        for (int n = 0; n < NT; ++n)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) red[((warp * 2 + m) * 2 + n) * 128 + j * 32 + lane] = acc[m][n][j];
-    }
-    consumer_sync();
-    if (active && warp == first) {
-#pragma unroll
-      for (int m = 0; m < NMAT; ++m)
-#pragma unroll
-        for (int n = 0; n < NT; ++n)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float v = acc[m][n][j];
-            for (int p = 1; p < contrib; ++p) v += red[(((first + p) * 2 + m) * 2 + n) * 128 + j * 32 + lane];
-            acc[m][n][j] = v;
-          }
-    }
+      for (int j = 0; j < 4; ++j) red[(tw * 2 + m) * 128 + j * 32 + lane] = acc[m][0][j];
   }
-  if (active && warp == first) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(release);     // this warp no longer reads the weight stage
+  PROF_ADD(8);
+  team_sync(team);
+  PROF_ADD(9);
+  // element q of a group: fragment slot j = q / 32 of lane q % 32
+  const int per_group = units <= kTeamWarps ? nb : 0;       // warps of group g start at g * per_group
+  for (int o = ttid; o < groups * 128; o += kTeamThreads) {
+    const int g = o >> 7, q = o & 127;
+    const int j = q >> 5, ln = q & 31;
+    const int r = g * 16 + (ln >> 2) + (j >> 1) * 8, t = 2 * (ln & 3) + (j & 1);
+    if (r < nrows && t < ntok) {
+      float v[NMAT];
+      const int w0 = g * per_group;
 #pragma unroll
-    for (int n = 0; n < NT; ++n)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int r = grp * 16 + gid + (j >> 1) * 8, t = 8 * n + 2 * tig + (j & 1);
-        if (r < nrows && t < ntok) {
-          float v[NMAT];
-#pragma unroll
-          for (int m = 0; m < NMAT; ++m) v[m] = acc[m][n][j];
-          emit(r, t, v);
-        }
+      for (int m = 0; m < NMAT; ++m) {
+        float a = red[(w0 * 2 + m) * 128 + q];
+        for (int p = 1; p < contrib; ++p) a += red[((w0 + p) * 2 + m) * 128 + q];
+        v[m] = a;
       }
+      emit(r, t, v);
+    }
   }
+  PROF_ADD(10);
 }
 
-// residual + sum_k w_k * y_k + shared expert for output rows [row0, row0+nrows), all tokens
-__device__ __forceinline__ void combine_rows(const LayerDev& L, int row0, int nrows, int tid, int nthr) {
+// residual + sum_k w_k * y_k + shared expert for output rows [row0, row0+nrows), tokens [t_lo, t_hi)
+__device__ __forceinline__ void combine_rows(const LayerDev& L, int row0, int nrows, int t_lo, int t_hi,
+                                             int tid, int nthr) {
   const bool has_shared = L.sh[0] != nullptr;
-  for (int i = tid; i < nrows * L.n; i += nthr) {
-    const int tk = i / nrows, r = row0 + i % nrows;
+  for (int i = tid; i < nrows * (t_hi - t_lo); i += nthr) {
+    const int tk = t_lo + i / nrows, r = row0 + i % nrows;
     const size_t o = static_cast<size_t>(tk) * L.H + r;
     float acc = (L.add_residual && L.x_f16 != nullptr) ? h2f(L.x_f16[o]) : 0.f;
     const float* wr = L.w + static_cast<size_t>(tk) * (L.K + 1);
@@ -475,17 +483,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
   const StreamGeom G = stream_geom(L.H, L.FF);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + kStages;
-  int* flag = reinterpret_cast<int*>(smem + 128);                 // consumer broadcast slots
+  int* flag = reinterpret_cast<int*>(smem + 128);                 // broadcast slots
   ItemDesc* desc = reinterpret_cast<ItemDesc*>(smem + 256);
   unsigned char* stages = smem + kStreamHdr;
-  unsigned char* xbase = stages + static_cast<size_t>(kStages) * G.stage_bytes;
-  float* red = reinterpret_cast<float*>(xbase + G.x_bytes);
+  unsigned char* team_base = stages + static_cast<size_t>(kStages) * G.stage_bytes;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], kConsumerWarps);
+      mbar_init(&empty[s], kTeamWarps);
     }
     fence_barrier_init();
     fence_proxy_async();
@@ -495,12 +502,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
   pdl_launch_dependents();
 
   const int n_tiles = L.meta[1];
-  if (n_tiles == 0) {               // nothing routed here and no shared expert: residual only
-    if (warp < kConsumerWarps)
-      for (int c = blockIdx.x; c < G.chunks_dn; c += gridDim.x)
-        combine_rows(L, c * G.rows_dn, min(G.rows_dn, L.H - c * G.rows_dn), tid, kConsumers);
-    return;
-  }
   const long long n_gu = static_cast<long long>(n_tiles) * G.chunks_gu;
   const long long n_dn = static_cast<long long>(n_tiles) * G.chunks_dn;
   const int gu_lo = static_cast<int>(n_gu * blockIdx.x / gridDim.x);
@@ -510,29 +511,36 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
   const int n_items = gu_cnt + dn_cnt;
   const size_t rb_h = static_cast<size_t>(L.nbh) * kW4, rb_f = static_cast<size_t>(L.nbf) * kW4;
 
-  if (warp == kConsumerWarps) {
+  if (warp == kConsumers / 32) {
     // ---------------- producer warp ----------------
 #ifdef SGR_PROFILE
-    const int _pw = kConsumerWarps;
+    const int _pw = kConsumers / 32;
 #endif
     PROF_T0();
+    int cached_tile = -1;
+    int4 rc = make_int4(0, 0, 0, 0);
+    const unsigned char *w0 = nullptr, *w1 = nullptr, *w2 = nullptr;
     for (int i = 0; i < n_items; ++i) {
       const int s = i % kStages;
       const unsigned ph = (i / kStages) & 1;
+      const int kind = i < gu_cnt ? 0 : 1;
+      const int id = kind == 0 ? gu_lo + i : dn_lo + (i - gu_cnt);
+      const int chunks = kind == 0 ? G.chunks_gu : G.chunks_dn;
+      const int tile = id / chunks, chunk = id - tile * chunks;
+      if (tile != cached_tile) {                  // consecutive items share their tile
+        rc = __ldcg(L.rec + tile);
+        const bool shared = rc.x == L.E;
+        w0 = shared ? L.sh[0] : L.tab[rc.x];
+        w1 = shared ? L.sh[1] : L.tab[L.E + rc.x];
+        w2 = shared ? L.sh[2] : L.tab[2 * L.E + rc.x];
+        cached_tile = tile;
+      }
+      PROF_ADD(6);
       if (!mbar_wait(&empty[s], ph ^ 1u)) {
         if (lane == 0) atomicExch(L.status, 2);
         return;
       }
       PROF_ADD(5);
-      const int kind = i < gu_cnt ? 0 : 1;
-      const int id = kind == 0 ? gu_lo + i : dn_lo + (i - gu_cnt);
-      const int chunks = kind == 0 ? G.chunks_gu : G.chunks_dn;
-      const int tile = id / chunks, chunk = id - tile * chunks;
-      const int4 rc = __ldcg(L.rec + tile);
-      const bool shared = rc.x == L.E;
-      const unsigned char* w0 = shared ? L.sh[0] : L.tab[rc.x];
-      const unsigned char* w1 = shared ? L.sh[1] : L.tab[L.E + rc.x];
-      const unsigned char* w2 = shared ? L.sh[2] : L.tab[2 * L.E + rc.x];
       const bool absent = w0 == nullptr || w1 == nullptr || w2 == nullptr;
       const bool aligned = ((reinterpret_cast<uintptr_t>(w0) | reinterpret_cast<uintptr_t>(w1) |
                              reinterpret_cast<uintptr_t>(w2)) & 15u) == 0;
@@ -555,41 +563,66 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
         unsigned char* st = stages + static_cast<size_t>(s) * G.stage_bytes;
         if (kind == 0) {
           const int ms = G.rows_gu * G.ws_gu;
-          for (int j = lane; j < 2 * nrows; j += 32) {
-            const int m = j / nrows, r = j - m * nrows;
-            bulk_g2s(st + m * ms + r * G.ws_gu, (m == 0 ? w0 : w1) + (row0 + r) * rb_h,
-                     static_cast<uint32_t>(rb_h), &full[s]);
+          if (G.ws_gu == static_cast<int>(rb_h)) {
+            if (lane < 2) bulk_g2s(st + lane * ms, (lane == 0 ? w0 : w1) + row0 * rb_h,
+                                   static_cast<uint32_t>(nrows * rb_h), &full[s]);
+          } else {
+            for (int j = lane; j < 2 * nrows; j += 32) {
+              const int m = j / nrows, r = j - m * nrows;
+              bulk_g2s(st + m * ms + r * G.ws_gu, (m == 0 ? w0 : w1) + (row0 + r) * rb_h,
+                       static_cast<uint32_t>(rb_h), &full[s]);
+            }
           }
         } else {
-          for (int r = lane; r < nrows; r += 32)
-            bulk_g2s(st + r * G.ws_dn, w2 + (row0 + r) * rb_f, static_cast<uint32_t>(rb_f), &full[s]);
+          if (G.ws_dn == static_cast<int>(rb_f)) {
+            if (lane == 0) bulk_g2s(st, w2 + row0 * rb_f, static_cast<uint32_t>(nrows * rb_f), &full[s]);
+          } else {
+            for (int r = lane; r < nrows; r += 32)
+              bulk_g2s(st + r * G.ws_dn, w2 + (row0 + r) * rb_f, static_cast<uint32_t>(rb_f), &full[s]);
+          }
         }
       }
-      PROF_ADD(6);
     }
     return;
   }
 
-  // ---------------- consumer warps ----------------
-  int cur_kind = -1, cur_tile = -1;
-  XTile xt = xtile_at(xbase, kTokTile, L.nbh);
+  // ---------------- consumer teams ----------------
+  const int team = warp / kTeamWarps, tw = warp - team * kTeamWarps, ttid = tid - team * kTeamThreads;
+  unsigned char* xbase = team_base + static_cast<size_t>(team) * (G.x_bytes + kTeamRed);
+  float* red = reinterpret_cast<float*>(xbase + G.x_bytes);
   const unsigned char* xq = L.xq_in != nullptr ? L.xq_in : L.xq;
+  int cur_kind = -1, cur_tile = -1, pending = 0, parity = 0;
+  XTile xt = xtile_at(xbase, kTokTile, L.nbh);
+  bool ok = true;
 #ifdef SGR_PROFILE
   const int _pw = 0;
 #endif
   PROF_T0();
-  for (int i = 0; i < n_items; ++i) {
+  // publish the gate/up chunks this team finished for its current tile
+  auto publish = [&]() {
+    if (cur_kind == 0 && pending > 0) {
+      __threadfence();
+      team_sync(team);
+      if (ttid == 0) atomicAdd(L.tile_cnt + cur_tile, static_cast<unsigned>(pending));
+    }
+    pending = 0;
+  };
+  for (int i = team; i < n_items && ok; i += kTeams) {
     const int s = i % kStages;
     const unsigned ph = (i / kStages) & 1;
     if (!mbar_wait(&full[s], ph)) {
-      if (tid == 0) atomicExch(L.status, 3);
-      return;                                  // every consumer gives up on the same item
+      if (ttid == 0) atomicExch(L.status, 3);
+      ok = false;                              // the whole team sees the same expiry
+      break;
     }
     PROF_ADD(0);
     const ItemDesc d = desc[s];
     unsigned char* st = stages + static_cast<size_t>(s) * G.stage_bytes;
     if (d.kind != cur_kind || d.tile != cur_tile) {
-      consumer_sync();                         // previous activation tile fully consumed
+      publish();
+      team_sync(team);                         // previous activation tile fully consumed
+      cur_kind = d.kind;
+      cur_tile = d.tile;
       if (d.kind == 0) {
         xt = xtile_at(xbase, kTokTile, L.nbh);
         const bool shared = d.e == L.E;
@@ -598,27 +631,25 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
                       const int r = shared ? d.p0 + t : __ldcg(L.grows + d.p0 + t);
                       return xq + static_cast<size_t>(r) * L.nbh * kX8;
                     },
-                    tid, kConsumers);
+                    ttid, kTeamThreads);
       } else {
         xt = xtile_at(xbase, kTokTile, L.nbf);
-        if (tid == 0) {                        // wait for the gate/up items of this tile
+        if (ttid == 0) {                       // wait for the gate/up items of this tile
           unsigned it = 0;
           while (ld_acquire(L.tile_cnt + d.tile) < static_cast<unsigned>(G.chunks_gu) && ++it < kSpinLimit)
-            __nanosleep(40);
-          flag[0] = it < kSpinLimit ? 1 : 0;
+            __nanosleep(32);
+          flag[team] = it < kSpinLimit ? 1 : 0;
         }
-        consumer_sync();
-        if (!flag[0]) {
-          if (tid == 0) atomicExch(L.status, 4);
-          return;
+        team_sync(team);
+        if (!flag[team]) {
+          if (ttid == 0) atomicExch(L.status, 4);
+          ok = false;
+          break;
         }
         if (d.mode != 1)
-          stage_quantized_f32(xt, d.ntok, L.hbuf + static_cast<size_t>(d.hrow0) * L.FF, L.FF, warp,
-                              kConsumerWarps);
+          stage_quantized_f32(xt, d.ntok, L.hbuf + static_cast<size_t>(d.hrow0) * L.FF, L.FF, tw, kTeamWarps);
       }
-      consumer_sync();
-      cur_kind = d.kind;
-      cur_tile = d.tile;
+      team_sync(team);
       PROF_ADD(1);
     }
     if (d.mode == 2) {                         // unaligned weights: copy them here
@@ -627,70 +658,81 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
         const unsigned char* w0 = shared ? L.sh[0] : L.tab[d.e];
         const unsigned char* w1 = shared ? L.sh[1] : L.tab[L.E + d.e];
         for (int r = 0; r < d.nrows; ++r) {
-          copy_unaligned(st + r * G.ws_gu, w0 + (d.row0 + r) * rb_h, static_cast<int>(rb_h), tid, kConsumers);
+          copy_unaligned(st + r * G.ws_gu, w0 + (d.row0 + r) * rb_h, static_cast<int>(rb_h), ttid, kTeamThreads);
           copy_unaligned(st + G.rows_gu * G.ws_gu + r * G.ws_gu, w1 + (d.row0 + r) * rb_h,
-                         static_cast<int>(rb_h), tid, kConsumers);
+                         static_cast<int>(rb_h), ttid, kTeamThreads);
         }
       } else {
         const unsigned char* w2 = d.e == L.E ? L.sh[2] : L.tab[2 * L.E + d.e];
         for (int r = 0; r < d.nrows; ++r)
-          copy_unaligned(st + r * G.ws_dn, w2 + (d.row0 + r) * rb_f, static_cast<int>(rb_f), tid, kConsumers);
+          copy_unaligned(st + r * G.ws_dn, w2 + (d.row0 + r) * rb_f, static_cast<int>(rb_f), ttid, kTeamThreads);
       }
-      consumer_sync();
+      team_sync(team);
     }
-
-    if (d.kind == 0) {
-      if (d.mode != 1) {
-        auto emit = [&](int r, int t, const float (&v)[2]) {
-          const float g = v[0], u = v[1];
-          L.hbuf[static_cast<size_t>(d.hrow0 + t) * L.FF + d.row0 + r] = g / (1.f + expf(-g)) * u;
-        };
-        if (d.ntok > 8)
-          item_compute<2, 2>(st, G.ws_gu, G.rows_gu * G.ws_gu, xt, red, d.nrows, L.nbh, d.ntok, emit);
-        else
-          item_compute<2, 1>(st, G.ws_gu, G.rows_gu * G.ws_gu, xt, red, d.nrows, L.nbh, d.ntok, emit);
-      } else if (d.chunk == 0 && tid == 0 && L.mail != nullptr && d.e != L.E) {
-        const int mi = atomicAdd(L.mail_n, 1);          // absent expert: post the id once per tile
-        if (mi < L.E) L.mail[mi] = d.e;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);            // this warp is done with the stage
-      PROF_ADD(2);
-      __threadfence();
-      consumer_sync();
-      if (tid == 0) atomicAdd(L.tile_cnt + d.tile, 1u);
-      PROF_ADD(3);
-    } else {
-      if (d.mode != 1) {
-        auto emit = [&](int r, int t, const float (&v)[1]) {
-          L.ybuf[static_cast<size_t>(d.hrow0 + t) * L.H + d.row0 + r] = v[0];
-        };
-        if (d.ntok > 8)
-          item_compute<1, 2>(st, G.ws_dn, 0, xt, red, d.nrows, L.nbf, d.ntok, emit);
-        else
-          item_compute<1, 1>(st, G.ws_dn, 0, xt, red, d.nrows, L.nbf, d.ntok, emit);
+    if (d.mode == 1) {                         // absent expert: zero rows, one mail per tile
+      if (d.kind == 0) {
+        if (d.chunk == 0 && ttid == 0 && L.mail != nullptr && d.e != L.E) {
+          const int mi = atomicAdd(L.mail_n, 1);
+          if (mi < L.E) L.mail[mi] = d.e;
+        }
       } else {
-        for (int j = tid; j < d.nrows * d.ntok; j += kConsumers)
+        for (int j = ttid; j < d.nrows * d.ntok; j += kTeamThreads)
           L.ybuf[static_cast<size_t>(d.hrow0 + j / d.nrows) * L.H + d.row0 + j % d.nrows] = 0.f;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
-      PROF_ADD(2);
-      __threadfence();
-      consumer_sync();
-      if (tid == 0) {
-        const unsigned prev = atomicAdd(&L.cnt[16 + d.chunk], 1u);
-        flag[1] = prev == static_cast<unsigned>(n_tiles) - 1 ? 1 : 0;
-        if (flag[1]) L.cnt[16 + d.chunk] = 0u;
-      }
-      consumer_sync();
-      if (flag[1]) {                                    // last tile of this row chunk: blend
-        __threadfence();
-        combine_rows(L, d.row0, d.nrows, tid, kConsumers);
-      }
-      PROF_ADD(4);
+    } else if (d.kind == 0) {
+      // partial sums alternate between two buffers: a warp may start the next item
+      // while another thread of the team still adds up this one
+      item_compute<2>(L, st, G.ws_gu, G.rows_gu * G.ws_gu, xt, red + (parity ^= 1) * (kTeamRed / 8), d.nrows,
+                      L.nbh, d.ntok, team, &empty[s],
+                      [&](int r, int t, const float (&v)[2]) {
+                        const float g = v[0], u = v[1];
+                        L.hbuf[static_cast<size_t>(d.hrow0 + t) * L.FF + d.row0 + r] = g / (1.f + expf(-g)) * u;
+                      });
+    } else {
+      item_compute<1>(L, st, G.ws_dn, 0, xt, red + (parity ^= 1) * (kTeamRed / 8), d.nrows, L.nbf, d.ntok,
+                      team, &empty[s],
+                      [&](int r, int t, const float (&v)[1]) {
+                        L.ybuf[static_cast<size_t>(d.hrow0 + t) * L.H + d.row0 + r] = v[0];
+                      });
     }
+    if (d.kind == 0) ++pending;
+    PROF_ADD(2);
   }
+  if (ok) publish();
+  PROF_ADD(3);
+
+  // ---- all down rows written everywhere: blend ------------------------------------------------
+  __threadfence();
+  consumers_sync();
+  if (tid == 0) {
+    atomicAdd(&L.cnt[9], 1u);
+    unsigned it = 0;
+    while (ld_acquire(&L.cnt[9]) < gridDim.x && ++it < kSpinLimit) __nanosleep(32);
+    flag[2] = it < kSpinLimit ? 1 : 0;
+  }
+  consumers_sync();
+  if (!flag[2]) {
+    if (tid == 0) atomicExch(L.status, 5);
+    return;
+  }
+  const int tgroups = (L.n + 15) / 16;
+  for (int job = blockIdx.x; job < G.chunks_dn * tgroups; job += gridDim.x) {
+    const int c = job / tgroups, tg = job - c * tgroups;
+    combine_rows(L, c * G.rows_dn, min(G.rows_dn, L.H - c * G.rows_dn), tg * 16, min(L.n, tg * 16 + 16), tid,
+                 kConsumers);
+  }
+  PROF_ADD(4);
+}
+
+// Re-arms the counters the plan normally resets, for launches of the expert kernel
+// alone on a workspace that already ran once.
+__global__ void rearm_kernel(const LayerDev L) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int i = threadIdx.x; i < L.n_max * L.K + L.n_max; i += blockDim.x) L.tile_cnt[i] = 0u;
+  if (threadIdx.x == 0) L.cnt[9] = 0u;
 }
 
 #ifdef SGR_PROFILE
@@ -794,8 +836,8 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   L.status = status_word();
 #ifdef SGR_PROFILE
   if (g_prof_buf == nullptr) {
-    cudaMalloc(&g_prof_buf, 1024 * 8 * sizeof(long long));
-    cudaMemset(g_prof_buf, 0, 1024 * 8 * sizeof(long long));
+    cudaMalloc(&g_prof_buf, 1024 * 16 * sizeof(long long));
+    cudaMemset(g_prof_buf, 0, 1024 * 16 * sizeof(long long));
   }
   L.prof = g_prof_buf;
 #endif
@@ -820,7 +862,7 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
     // geometry the consumer mapping was written for: a tile of rows is one 16-row
     // group, or at most eight (group, super-block) units
     const StreamGeom g = stream_geom(L.H, L.FF);
-    auto units_ok = [](int rows, int nb) { const int grp = (rows + 15) / 16; return grp == 1 || grp * nb <= kConsumerWarps; };
+    auto units_ok = [](int rows, int nb) { const int grp = (rows + 15) / 16; return grp == 1 || grp * nb <= kTeamWarps; };
     if (!units_ok(g.rows_gu, L.nbh) || !units_ok(g.rows_dn, L.nbf)) return kErrUnsupported;
     const size_t smem = stream_smem(L.H, L.FF);
     if (smem > 227 * 1024) return kErrUnsupported;
@@ -828,6 +870,10 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
     if (cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
       return kErrLaunch;
+    if (!(stages & 1)) {
+      rc = launch_pdl(rearm_kernel, dim3(1), 256, 0, s, L);
+      if (rc != kOk) return rc;
+    }
     rc = launch_pdl(expert_stream_kernel, dim3(sms), kStreamThreads, smem, s, L);
   }
   return rc;
@@ -839,7 +885,7 @@ extern "C" __attribute__((visibility("default"))) int sgr_prof_read(long long* h
   if (g_prof_buf == nullptr) return -1;
   cudaDeviceSynchronize();
   cudaMemcpy(host_out, g_prof_buf, static_cast<size_t>(n) * sizeof(long long), cudaMemcpyDeviceToHost);
-  cudaMemset(g_prof_buf, 0, 1024 * 8 * sizeof(long long));
+  cudaMemset(g_prof_buf, 0, 1024 * 16 * sizeof(long long));
   return 0;
 }
 #endif

@@ -29,9 +29,12 @@ constexpr int kTileThreads = 128;
 // rows of one matrix a CTA takes for rows of nb super-blocks
 __host__ __device__ constexpr int tile_rows(int nb) { return kTileThreads / next_pow2_cap32(nb); }
 
-// Shared-memory row stride: rows of an even number of blocks are padded by 16
-// bytes so that the stride is 4 (mod 8) words.
-__host__ __device__ constexpr int tile_wstride(int nb) { return nb * kW4 + ((nb & 1) ? 0 : 16); }
+// Shared-memory row stride. A row of nb blocks is 36*nb words: for nb a multiple of
+// four that is 0 or 16 (mod 32) and eight rows would pile onto one or two bank
+// groups, so those rows are padded by 16 bytes (stride 4 mod 8 words, conflict
+// free, one bulk copy per row). Other nb keep the packed stride and a single bulk
+// copy (conflict free for odd nb, two-way at worst for nb = 2 mod 4).
+__host__ __device__ constexpr int tile_wstride(int nb) { return nb * kW4 + ((nb & 3) ? 0 : 16); }
 
 // dynamic shared memory of a tile CTA (the last term is the cross-warp reduction
 // scratch of the MMA path)
