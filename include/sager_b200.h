@@ -36,6 +36,8 @@ extern "C" {
 #define SGR_EUNSUPPORTED 3 /* shape outside what the kernels were built for */
 #define SGR_ELAUNCH 4      /* the CUDA runtime refused the launch */
 #define SGR_EGEOMETRY 5    /* fused entry point: geometry mismatch (refused, never misindexed) */
+#define SGR_ESTATICLIMIT 6 /* sgr_moe_layer_decode_static: the shape needs more scratch than the
+                              library's built-in array holds (sgr_moe_layer_static_limit bytes) */
 
 int sgr_abi_version(void);
 /* Device status word of the current device: non-zero after a bounded device-side
@@ -228,6 +230,21 @@ int sgr_moe_layer_decode(const sgr_moe_layer* args, void* stream);
  * the expert kernel), on a workspace that still holds what the earlier stage of a
  * previous call left there. For measuring one kernel at a time. */
 int sgr_moe_layer_decode_stages(const sgr_moe_layer* args, int stages, void* stream);
+
+/* No counterpart in the reference. sgr_moe_layer_decode for callers that cannot
+ * allocate device memory - an engine whose whole VRAM budget was handed out at
+ * start-up (KV cache, expert slab) and that treats any later cudaMalloc as a bug,
+ * a host binding with no way to own CUDA buffers, code that only ever runs inside a
+ * captured region. The scratch is a file-scope device array inside the library,
+ * sgr_moe_layer_static_limit() bytes (1 MiB: e.g. 8 token rows at hidden 2048,
+ * expert FFN 512, 256 experts, top-8); `workspace` / `workspace_bytes` of the
+ * argument block are ignored, inputs and outputs are still the caller's. A shape
+ * whose scratch would not fit returns SGR_ESTATICLIMIT and launches nothing. The first
+ * call on each device looks up the array's device address and must be made outside
+ * stream capture. Every call on a device uses the same array: calls that overlap on
+ * the GPU race. */
+size_t sgr_moe_layer_static_limit(void);
+int sgr_moe_layer_decode_static(const sgr_moe_layer* args, void* stream);
 
 #ifdef __cplusplus
 }

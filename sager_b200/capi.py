@@ -16,7 +16,8 @@ ROOT = os.path.dirname(HERE)
 HEADER = os.path.join(ROOT, "include", "sager_b200.h")
 LIB_PATH = os.path.join(HERE, "libsager_b200.so")
 
-ERRORS = {1: "SGR_EARG", 2: "SGR_EALIGN", 3: "SGR_EUNSUPPORTED", 4: "SGR_ELAUNCH", 5: "SGR_EGEOMETRY"}
+ERRORS = {1: "SGR_EARG", 2: "SGR_EALIGN", 3: "SGR_EUNSUPPORTED", 4: "SGR_ELAUNCH", 5: "SGR_EGEOMETRY",
+          6: "SGR_ESTATICLIMIT"}
 
 _SCALARS = {"int": C.c_int, "float": C.c_float, "long long": C.c_longlong, "size_t": C.c_size_t,
             "unsigned long long": C.c_ulonglong}

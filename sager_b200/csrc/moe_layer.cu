@@ -726,6 +726,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
   PROF_ADD(4);
 }
 
+// Scratch of the allocation-free entry point (sgr_moe_layer_decode_static): the
+// same layout a caller-provided workspace has, held by every device that loads
+// the library until the process exits.
+constexpr size_t kStaticWsBytes = 1u << 20;
+static __device__ __align__(256) unsigned char g_static_ws[kStaticWsBytes];
+constexpr int kStaticMaxDevices = 64;
+unsigned char* g_static_ws_addr[kStaticMaxDevices];     // per-device address of g_static_ws
+
 // Re-arms the counters the plan normally resets, for launches of the expert kernel
 // alone on a workspace that already ran once.
 __global__ void rearm_kernel(const LayerDev L) {
@@ -892,4 +900,42 @@ extern "C" __attribute__((visibility("default"))) int sgr_prof_read(long long* h
 
 SGR_API int sgr_moe_layer_decode(const sgr_moe_layer* a, void* stream) {
   return sgr_moe_layer_decode_stages(a, 7, stream);
+}
+
+SGR_API size_t sgr_moe_layer_static_limit(void) { return kStaticWsBytes; }
+
+// The fused layer for callers that may not allocate device memory. `workspace`
+// and `workspace_bytes` of the argument block are ignored: the scratch is the
+// library's own file-scope device array of sgr_moe_layer_static_limit() bytes.
+// In host code that array's name is only a stand-in, so the first call on a
+// device asks the runtime for the array's device address (with that device
+// current), and every later call reuses it; that first call must therefore be
+// made outside stream capture. Nothing here calls cudaMalloc, cudaFree or any
+// allocating library routine. All calls on a device share the one array and it
+// keeps what the previous call left: the counters that must start at zero are
+// cleared on the stream before the kernels run, and two calls that overlap on the
+// GPU (different streams, or graphs replayed concurrently) would race on it.
+SGR_API int sgr_moe_layer_decode_static(const sgr_moe_layer* a, void* stream) {
+  if (a == nullptr) return kErrArg;
+  if (a->n <= 0) return kOk;
+  if (a->hidden <= 0 || a->hidden % kQK || a->n_ff <= 0 || a->n_ff % kQK || a->n_expert <= 0 ||
+      a->n_used <= 0 || a->n_max < a->n || a->n_max > kMaxRows)
+    return kErrGeometry;
+  const WsLayout lay = ws_layout(a->n_max, a->hidden, a->n_ff, a->n_expert, a->n_used);
+  if (lay.total > kStaticWsBytes) return kErrStaticLimit;   // the shape needs more scratch than the array holds
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) return kErrLaunch;
+  if (g_static_ws_addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_ws) != cudaSuccess || p == nullptr) return kErrLaunch;
+    g_static_ws_addr[dev] = static_cast<unsigned char*>(p);
+  }
+  unsigned char* ws = g_static_ws_addr[dev];
+  // counters of the route and expert kernels: [cnt, tile_cnt) is one contiguous span
+  if (cudaMemsetAsync(ws + lay.cnt, 0, lay.hbuf - lay.cnt, as_stream(stream)) != cudaSuccess)
+    return kErrLaunch;
+  sgr_moe_layer b = *a;
+  b.workspace = ws;
+  b.workspace_bytes = kStaticWsBytes;
+  return sgr_moe_layer_decode_stages(&b, 7, stream);
 }

@@ -29,6 +29,7 @@ enum : int {
   kErrUnsupported = 3,
   kErrLaunch = 4,     // the CUDA runtime refused the launch
   kErrGeometry = 5,   // a fused entry point was given a shape it was not built for
+  kErrStaticLimit = 6,  // the allocation-free entry point: shape exceeds the built-in scratch
 };
 
 __device__ __forceinline__ float h2f(uint16_t h) {
