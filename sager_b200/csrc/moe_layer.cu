@@ -44,13 +44,14 @@ namespace {
 constexpr int kMaxRows = 64;       // token rows per call (row masks are 64-bit)
 constexpr int kTokTile = 8;        // token rows per tile of the expert kernel (one MMA n-tile)
 constexpr int kRouteTok = 8;       // token rows per CTA of the route kernel
-constexpr int kRouteWarps = 4;
+constexpr int kRouteWarps = 8;
 
 constexpr int kTeams = 2;                         // consumer teams, items alternate between them
 constexpr int kTeamWarps = 8;
 constexpr int kTeamThreads = kTeamWarps * 32;
 constexpr int kConsumers = kTeams * kTeamThreads;
-constexpr int kStreamThreads = kConsumers + 32;   // + one producer warp
+constexpr int kProducerWarps = 4;
+constexpr int kStreamThreads = kConsumers + kProducerWarps * 32;
 constexpr int kStages = 4;
 constexpr unsigned kSpinLimit = 1u << 22;         // bounded waits: give up, raise the status word
 
@@ -88,6 +89,15 @@ struct LayerDev {
   long long* prof;   // SGR_PROFILE builds only: [grid][8] cycle totals
 };
 
+#ifdef SGR_PROFILE
+#define PROF_T0() long long _pt = clock64()
+#define PROF_ADD(slot) do { const long long _n = clock64(); if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == _pw) \
+    atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + blockIdx.x * 16 + (slot)), static_cast<unsigned long long>(_n - _pt)); _pt = _n; } while (0)
+#else
+#define PROF_T0() do {} while (0)
+#define PROF_ADD(slot) do {} while (0)
+#endif
+
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct WsLayout {
@@ -115,15 +125,15 @@ inline WsLayout ws_layout(int n_max, int H, int FF, int E, int K) {
 }
 
 // ---- plan ------------------------------------------------------------------------
-// One CTA (128 threads). Row sets per expert are 64-bit masks, so the slot of a
+// One CTA (at most 256 threads). Row sets per expert are 64-bit masks, so the slot of a
 // route inside its expert is a popcount: the plan is deterministic (ascending
 // row order) and needs no sort. Routes to experts outside [e_lo, e_hi) are left
 // to their owner (gslot = -1); ids outside [0, E) silence their row as in
 // moe_dispatch_scan (moe.cu:385-398 of the reference).
 __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   unsigned long long* mask = reinterpret_cast<unsigned long long*>(smem);       // [E]
-  int* scan_rows = reinterpret_cast<int*>(smem + static_cast<size_t>(L.E) * 8);   // [128]
-  int* scan_tiles = scan_rows + 128;                                              // [128]
+  int* scan_rows = reinterpret_cast<int*>(smem + static_cast<size_t>(L.E) * 8);   // [256]
+  int* scan_tiles = scan_rows + 256;                                              // [256]
   __shared__ int bad_sh;
   const int tid = threadIdx.x;
   const int total = L.n * L.K;
@@ -207,11 +217,11 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   }
 }
 
-constexpr size_t plan_smem(int E) { return static_cast<size_t>(E) * 8 + 2 * 128 * 4; }
+constexpr size_t plan_smem(int E) { return static_cast<size_t>(E) * 8 + 2 * 256 * 4; }   // CTAs of <= 256 threads
 
 // ---- launch 1: route ------------------------------------------------------------------
-// grid (ceil(E / 4), ceil(n / 8)), 128 threads. Dynamic smem: max(8 rows of fp16 x,
-// 4*E floats for the selection, plan scratch).
+// grid (ceil(E / 8), ceil(n / 8)), 256 threads. Dynamic smem: max(8 rows of fp16 x,
+// 8*E floats for the selection, plan scratch).
 __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev L) {
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ int last_sh;
@@ -230,6 +240,10 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
   }
   pdl_wait();
   pdl_launch_dependents();
+#ifdef SGR_PROFILE
+  const int _pw = 0;
+#endif
+  PROF_T0();
 
   for (int i = tid; i < nt * L.H / 8; i += blockDim.x)
     reinterpret_cast<uint4*>(xs)[i] =
@@ -260,6 +274,10 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
   __syncthreads();
   if (!last_sh) return;
   __threadfence();
+#ifdef SGR_PROFILE
+  if (tid == 0) atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + 11), static_cast<unsigned long long>(clock64() - _pt));
+  _pt = clock64();
+#endif
   float* prob = reinterpret_cast<float*>(smem) + static_cast<size_t>(warp) * L.E;
   for (int t = warp; t < nt; t += kRouteWarps) {
     for (int i = lane; i < L.E; i += 32) prob[i] = __ldcg(L.logits + static_cast<size_t>(tok0 + t) * L.E + i);
@@ -279,7 +297,15 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
   if (!last_sh) return;
   __threadfence();
   if (tid == 0) L.cnt[8] = 0u;
+#ifdef SGR_PROFILE
+  if (tid == 0) atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + 12), static_cast<unsigned long long>(clock64() - _pt));
+  _pt = clock64();
+#endif
   build_plan(L, smem);
+#ifdef SGR_PROFILE
+  __syncthreads();
+  if (tid == 0) atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + 13), static_cast<unsigned long long>(clock64() - _pt));
+#endif
 }
 
 // Routing supplied by the caller (expert-parallel owner side): plan only.
@@ -312,11 +338,11 @@ __host__ __device__ inline StreamGeom stream_geom(int H, int FF) {
   const int nbh = H / kQK, nbf = FF / kQK;
   g.rows_gu = tile_rows(nbh);
   g.rows_dn = tile_rows(nbf);
-  // Packed rows: one bulk copy brings a whole matrix tile. Issuing a copy per row
-  // (to pad the row stride) costs the producer warp more than the 8-way bank
-  // conflicts of the four weight ldmatrix per unit cost the consumers.
-  g.ws_gu = nbh * kW4;
-  g.ws_dn = nbf * kW4;
+  // Padded row strides where eight rows would otherwise share a bank group: those
+  // tiles arrive as one bulk copy per row. A warp issues its bulk copies one after
+  // another (about 60 cycles each), so the rows are spread over the producer warps.
+  g.ws_gu = tile_wstride(nbh);
+  g.ws_dn = tile_wstride(nbf);
   g.chunks_gu = (FF + g.rows_gu - 1) / g.rows_gu;
   g.chunks_dn = (H + g.rows_dn - 1) / g.rows_dn;
   const int a = 2 * g.rows_gu * g.ws_gu, b = g.rows_dn * g.ws_dn;
@@ -332,14 +358,6 @@ inline size_t stream_smem(int H, int FF) {
   return kStreamHdr + static_cast<size_t>(kStages) * g.stage_bytes + kTeams * (g.x_bytes + kTeamRed);
 }
 
-#ifdef SGR_PROFILE
-#define PROF_T0() long long _pt = clock64()
-#define PROF_ADD(slot) do { const long long _n = clock64(); if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == _pw) \
-    atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + blockIdx.x * 16 + (slot)), static_cast<unsigned long long>(_n - _pt)); _pt = _n; } while (0)
-#else
-#define PROF_T0() do {} while (0)
-#define PROF_ADD(slot) do {} while (0)
-#endif
 
 __device__ __forceinline__ void team_sync(int team) {
   asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "n"(kTeamThreads) : "memory");
@@ -387,7 +405,10 @@ __device__ __forceinline__ void stage_quantized_f32(const XTile& xt, int nt, con
                                          (static_cast<uint32_t>(q[3] & 0xFF) << 24);
     reinterpret_cast<uint32_t*>(qs)[1] = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) |
                                          (static_cast<uint32_t>(q[7] & 0xFF) << 24);
-    if ((lane & 3) == 0) xt.bs[(static_cast<size_t>(t) * xt.nb + blk) * 8 + (lane >> 2)] = static_cast<int16_t>(sum);
+    const int sum_next = __shfl_down_sync(0xFFFFFFFFu, sum, 4);      // the next sub-block's sum
+    if ((lane & 7) == 0)
+      xt.put_sum_pair(t, blk, lane >> 3,
+                      (static_cast<uint32_t>(sum) & 0xFFFFu) | (static_cast<uint32_t>(sum_next) << 16));
     if (lane == 0) xt.d[t * xt.nb + blk] = d;
   }
 }
@@ -458,6 +479,47 @@ __device__ __forceinline__ void item_compute(const LayerDev& L, const unsigned c
   PROF_ADD(10);
 }
 
+// The same item for tiles of one or two token rows: dp4a, one thread per
+// (row, matrix, super-block) task, shuffle reduction over the lanes of a row -
+// no shared-memory partials and no team barrier. Needs NMAT * lanes-per-row <= 32.
+template <int NMAT, typename Emit>
+__device__ __forceinline__ void item_compute_dp4a(const unsigned char* w, int wstride, int mat_stride,
+                                                  const XTile& xt, int nrows, int nb, int ntok,
+                                                  uint64_t* release, Emit emit) {
+  const int ttid = threadIdx.x & (kTeamThreads - 1), lane = threadIdx.x & 31;
+  const int lpr = next_pow2_cap32(nb);
+  const int tasks = nrows * NMAT * lpr;
+  for (int base = 0; base < tasks; base += kTeamThreads) {     // uniform trip count
+    const int t = base + ttid;
+    const int lr = t & (lpr - 1);
+    const int rm = t / lpr;
+    const int m = NMAT == 2 ? (rm & 1) : 0;
+    const int row = NMAT == 2 ? (rm >> 1) : rm;
+    float acc[1][2] = {{0.f, 0.f}};
+    if (t < tasks) {
+      for (int blk = lr; blk < nb; blk += lpr) {
+        const uint4* wb[1] = {reinterpret_cast<const uint4*>(w + m * mat_stride + row * wstride + blk * kW4)};
+        block_dot<1, 2>(wb, xt, blk, ntok, acc);
+      }
+    }
+    float v0 = reduce_lanes(acc[0][0], lpr), v1 = reduce_lanes(acc[0][1], lpr);
+    float u0 = 0.f, u1 = 0.f;
+    if (NMAT == 2) {                       // the up row's lanes follow the gate row's
+      u0 = __shfl_down_sync(0xFFFFFFFFu, v0, lpr);
+      u1 = __shfl_down_sync(0xFFFFFFFFu, v1, lpr);
+    }
+    if (t < tasks && lr == 0 && m == 0) {
+      float a[NMAT], b[NMAT];
+      a[0] = v0; b[0] = v1;
+      if (NMAT == 2) { a[NMAT - 1] = u0; b[NMAT - 1] = u1; }
+      emit(row, 0, a);
+      if (ntok > 1) emit(row, 1, b);
+    }
+  }
+  __syncwarp();
+  if (lane == 0) mbar_arrive(release);
+}
+
 // residual + sum_k w_k * y_k + shared expert for output rows [row0, row0+nrows), tokens [t_lo, t_hi)
 __device__ __forceinline__ void combine_rows(const LayerDev& L, int row0, int nrows, int t_lo, int t_hi,
                                              int tid, int nthr) {
@@ -511,8 +573,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
   const int n_items = gu_cnt + dn_cnt;
   const size_t rb_h = static_cast<size_t>(L.nbh) * kW4, rb_f = static_cast<size_t>(L.nbf) * kW4;
 
-  if (warp == kConsumers / 32) {
-    // ---------------- producer warp ----------------
+  if (warp >= kConsumers / 32) {
+    // ---------------- producer warps ----------------
+    // All of them walk the same item list; the first one also publishes the item
+    // descriptor and arms the stage's barrier, every one issues its share of the rows.
+    const int pw = warp - kConsumers / 32;
 #ifdef SGR_PROFILE
     const int _pw = kConsumers / 32;
 #endif
@@ -548,7 +613,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
       const int row0 = chunk * rows_per;
       const int nrows = min(rows_per, (kind == 0 ? L.FF : L.H) - row0);
       const int mode = absent ? 1 : (aligned ? 0 : 2);
-      if (lane == 0) {
+      if (lane == 0 && pw == 0) {
         ItemDesc d;
         d.kind = kind; d.mode = mode; d.tile = tile; d.chunk = chunk;
         d.e = rc.x; d.ntok = rc.y; d.hrow0 = rc.z; d.p0 = rc.w;
@@ -564,10 +629,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
         if (kind == 0) {
           const int ms = G.rows_gu * G.ws_gu;
           if (G.ws_gu == static_cast<int>(rb_h)) {
-            if (lane < 2) bulk_g2s(st + lane * ms, (lane == 0 ? w0 : w1) + row0 * rb_h,
-                                   static_cast<uint32_t>(nrows * rb_h), &full[s]);
+            if (pw == 0 && lane < 2) bulk_g2s(st + lane * ms, (lane == 0 ? w0 : w1) + row0 * rb_h,
+                                              static_cast<uint32_t>(nrows * rb_h), &full[s]);
           } else {
-            for (int j = lane; j < 2 * nrows; j += 32) {
+            // copy j of 2*nrows goes to warp j % kProducerWarps, lane j / kProducerWarps
+            for (int j = pw + kProducerWarps * lane; j < 2 * nrows; j += kProducerWarps * 32) {
               const int m = j / nrows, r = j - m * nrows;
               bulk_g2s(st + m * ms + r * G.ws_gu, (m == 0 ? w0 : w1) + (row0 + r) * rb_h,
                        static_cast<uint32_t>(rb_h), &full[s]);
@@ -575,9 +641,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
           }
         } else {
           if (G.ws_dn == static_cast<int>(rb_f)) {
-            if (lane == 0) bulk_g2s(st, w2 + row0 * rb_f, static_cast<uint32_t>(nrows * rb_f), &full[s]);
+            if (pw == 0 && lane == 0)
+              bulk_g2s(st, w2 + row0 * rb_f, static_cast<uint32_t>(nrows * rb_f), &full[s]);
           } else {
-            for (int r = lane; r < nrows; r += 32)
+            for (int r = pw + kProducerWarps * lane; r < nrows; r += kProducerWarps * 32)
               bulk_g2s(st + r * G.ws_dn, w2 + (row0 + r) * rb_f, static_cast<uint32_t>(rb_f), &full[s]);
           }
         }
@@ -681,6 +748,19 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
+    } else if (d.ntok <= 2 && 2 * next_pow2_cap32(L.nbh) <= 32) {
+      if (d.kind == 0)
+        item_compute_dp4a<2>(st, G.ws_gu, G.rows_gu * G.ws_gu, xt, d.nrows, L.nbh, d.ntok, &empty[s],
+                             [&](int r, int t, const float (&v)[2]) {
+                               const float g = v[0], u = v[1];
+                               L.hbuf[static_cast<size_t>(d.hrow0 + t) * L.FF + d.row0 + r] =
+                                   g / (1.f + expf(-g)) * u;
+                             });
+      else
+        item_compute_dp4a<1>(st, G.ws_dn, 0, xt, d.nrows, L.nbf, d.ntok, &empty[s],
+                             [&](int r, int t, const float (&v)[1]) {
+                               L.ybuf[static_cast<size_t>(d.hrow0 + t) * L.H + d.row0 + r] = v[0];
+                             });
     } else if (d.kind == 0) {
       // partial sums alternate between two buffers: a warp may start the next item
       // while another thread of the team still adds up this one

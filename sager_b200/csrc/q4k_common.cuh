@@ -99,6 +99,8 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 // One tile of up to TT Q8_K rows re-laid for 16-byte shared loads:
 //   qs   [TT][tok_stride]   int8 codes, 272 bytes per block (256 used)
 //   bs   [TT][nb][8]        int16 sub-block sums (one uint4 per block)
+//   bl   [TT][nb][16]       the same sums split as bsum = 128*hi + lo: eight lo bytes
+//                           (0..127) then eight hi bytes (-32..31), for the MMA path
 //   d    [TT][nb]           fp32 scales
 // Blocks are 68 words apart and token rows tok_stride/4 = 4 (mod 8) words apart,
 // so eight lanes that read the same 16 bytes of eight different blocks - or of
@@ -110,6 +112,7 @@ __host__ __device__ constexpr int xtile_tok_stride(int nb) {
 struct XTile {
   int8_t* qs;
   int16_t* bs;
+  int8_t* bl;
   float* d;
   int nb;
   int tok_stride;
@@ -123,10 +126,21 @@ struct XTile {
     return *reinterpret_cast<const uint4*>(bs + (static_cast<size_t>(t) * nb + blk) * 8);
   }
   __device__ __forceinline__ float scale(int t, int blk) const { return d[t * nb + blk]; }
+  __device__ __forceinline__ const int8_t* split_sums(int t, int blk) const {
+    return bl + (static_cast<size_t>(t) * nb + blk) * 16;
+  }
+  // store sub-block sums 2p and 2p+1 (packed in v as two int16) in both forms
+  __device__ __forceinline__ void put_sum_pair(int t, int blk, int p, uint32_t v) const {
+    reinterpret_cast<uint32_t*>(bs + (static_cast<size_t>(t) * nb + blk) * 8)[p] = v;
+    const int s0 = static_cast<int16_t>(v & 0xFFFFu), s1 = static_cast<int16_t>(v >> 16);
+    int8_t* q = bl + (static_cast<size_t>(t) * nb + blk) * 16;
+    reinterpret_cast<uint16_t*>(q)[p] = static_cast<uint16_t>((s0 & 127) | ((s1 & 127) << 8));
+    reinterpret_cast<uint16_t*>(q + 8)[p] = static_cast<uint16_t>(((s0 >> 7) & 0xFF) | (((s1 >> 7) & 0xFF) << 8));
+  }
 };
 
 __host__ __device__ constexpr size_t xtile_bytes(int tt, int nb) {
-  return static_cast<size_t>(tt) * (xtile_tok_stride(nb) + nb * (16 + 4));
+  return static_cast<size_t>(tt) * (xtile_tok_stride(nb) + nb * (16 + 16 + 4));
 }
 
 __device__ __forceinline__ XTile xtile_at(unsigned char* base, int tt, int nb) {
@@ -135,7 +149,8 @@ __device__ __forceinline__ XTile xtile_at(unsigned char* base, int tt, int nb) {
   x.tok_stride = xtile_tok_stride(nb);
   x.qs = reinterpret_cast<int8_t*>(base);
   x.bs = reinterpret_cast<int16_t*>(base + static_cast<size_t>(tt) * x.tok_stride);
-  x.d = reinterpret_cast<float*>(base + static_cast<size_t>(tt) * (x.tok_stride + nb * 16));
+  x.bl = reinterpret_cast<int8_t*>(base + static_cast<size_t>(tt) * (x.tok_stride + nb * 16));
+  x.d = reinterpret_cast<float*>(base + static_cast<size_t>(tt) * (x.tok_stride + nb * 32));
   return x;
 }
 
@@ -157,7 +172,7 @@ __device__ __forceinline__ void xtile_stage(const XTile& xt, int nt, RowOf row_o
     } else if (w <= 64) {
       reinterpret_cast<uint32_t*>(xt.qs + static_cast<size_t>(t) * xt.tok_stride + blk * kXqStride)[w - 1] = v;
     } else {
-      reinterpret_cast<uint32_t*>(xt.bs + (static_cast<size_t>(t) * xt.nb + blk) * 8)[w - 65] = v;
+      xt.put_sum_pair(t, blk, w - 65, v);
     }
   }
 }

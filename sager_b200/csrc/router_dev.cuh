@@ -17,7 +17,19 @@ __device__ __forceinline__ void router_row_dot(const float* __restrict__ wrow,
 #pragma unroll
   for (int t = 0; t < TT; ++t) acc[t] = 0.f;
   int i = lane;
-  // eight independent loads in flight, FMAs issued in ascending index order
+  // 32 independent loads in flight (a 2048-wide row is two round trips to memory),
+  // FMAs issued in ascending index order
+  for (; i + 31 * 32 < k; i += 32 * 32) {
+    float wv[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) wv[j] = __ldg(wrow + i + j * 32);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+#pragma unroll
+      for (int t = 0; t < TT; ++t)
+        if (t < nt) acc[t] = fmaf(wv[j], h2f(xs[t * k + i + j * 32]), acc[t]);
+    }
+  }
   for (; i + 7 * 32 < k; i += 8 * 32) {
     float wv[8];
 #pragma unroll
@@ -71,13 +83,32 @@ __device__ __forceinline__ void router_select_warp(float* prob, int n_expert, in
   for (int i = lane; i < n_expert; i += 32) prob[i] = prob[i] / z;
   __syncwarp();
 
+  // Every lane learns each pick (butterfly reduction); lane kk keeps pick kk in
+  // registers, so the results reach global memory once, in parallel, already
+  // renormalised. wsum is added in pick order in every lane (same rounding as the
+  // reference's serial sum).
   float wsum = 0.f;
+  float my_w = 0.f;
+  int my_i = 0;
+  // up to 256 experts: a lane keeps its eight probabilities in registers
+  const bool in_regs = n_expert <= 256;
+  float pr[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) pr[j] = (in_regs && lane + 32 * j < n_expert) ? prob[lane + 32 * j] : -1.f;
   for (int kk = 0; kk < k; ++kk) {
     float bv = -1.f;
     int bi = -1;
-    for (int i = lane; i < n_expert; i += 32) {
-      const float p = prob[i];
-      if (p == p && p > bv) { bv = p; bi = i; }    // ascending scan: first strict max
+    if (in_regs) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float p = pr[j];
+        if (p == p && p > bv) { bv = p; bi = lane + 32 * j; }
+      }
+    } else {
+      for (int i = lane; i < n_expert; i += 32) {
+        const float p = prob[i];
+        if (p == p && p > bv) { bv = p; bi = i; }    // ascending scan: first strict max
+      }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
@@ -87,19 +118,33 @@ __device__ __forceinline__ void router_select_warp(float* prob, int n_expert, in
       if (take) { bv = ov; bi = oi; }
     }
     if (bi < 0) bi = kk % n_expert;                // nothing valid: deterministic filler
-    if (lane == 0) {
+    if (in_regs) {
+      if ((bi & 31) == lane) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j == (bi >> 5)) pr[j] = -1.f;
+      }
+    } else if (lane == 0) {
       prob[bi] = -1.f;
+    }
+    wsum += bv;
+    if (k <= 32) {
+      if (lane == kk) { my_w = bv; my_i = bi; }
+    } else if (lane == 0) {
       out_idx[kk] = bi;
       out_w[kk] = bv;
-      wsum += bv;
     }
     __syncwarp();
   }
-  if (lane == 0) {
-    if (wsum > 0.f)
-      for (int kk = 0; kk < k; ++kk) out_w[kk] /= wsum;
-    if (write_shared) out_w[k] = shared_w;
+  if (k <= 32) {
+    if (lane < k) {
+      out_idx[lane] = my_i;
+      out_w[lane] = wsum > 0.f ? my_w / wsum : my_w;
+    }
+  } else if (lane == 0 && wsum > 0.f) {
+    for (int kk = 0; kk < k; ++kk) out_w[kk] /= wsum;
   }
+  if (lane == 0 && write_shared) out_w[k] = shared_w;
 }
 
 }  // namespace sgr

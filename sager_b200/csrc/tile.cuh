@@ -212,9 +212,10 @@ __device__ __forceinline__ void warp_mma_rows(const unsigned char* w, int wstrid
       const unsigned char* wm = w + m * mat_stride + blk * kW4;
       const uint4 h0 = *reinterpret_cast<const uint4*>(wm + row_lo * wstride);
       const uint4 h1 = *reinterpret_cast<const uint4*>(wm + row_hi * wstride);
-      d_lo[m] = __half2float(__ushort_as_half(static_cast<uint16_t>(h0.x & 0xFFFFu)));
+      // d enters as d/16 (exact): the integer sums below carry a factor 16
+      d_lo[m] = 0.0625f * __half2float(__ushort_as_half(static_cast<uint16_t>(h0.x & 0xFFFFu)));
       m_lo[m] = __half2float(__ushort_as_half(static_cast<uint16_t>(h0.x >> 16)));
-      d_hi[m] = __half2float(__ushort_as_half(static_cast<uint16_t>(h1.x & 0xFFFFu)));
+      d_hi[m] = 0.0625f * __half2float(__ushort_as_half(static_cast<uint16_t>(h1.x & 0xFFFFu)));
       m_hi[m] = __half2float(__ushort_as_half(static_cast<uint16_t>(h1.x >> 16)));
       s_lo[m] = unpack_scales6(h0.y, h0.z, h0.w);
       s_hi[m] = unpack_scales6(h1.y, h1.z, h1.w);
@@ -228,27 +229,22 @@ __device__ __forceinline__ void warp_mma_rows(const unsigned char* w, int wstrid
       uint32_t b[NT][4];
 #pragma unroll
       for (int n = 0; n < NT; ++n) ldmatrix_x4(b[n], xt.code_ptr(8 * n + b_tok, blk, 2 * g) + b_off);
-      const int sel = (g & 1) * 0x2222;            // byte 0/1 of the packed word for even g, 2/3 for odd
 #pragma unroll
       for (int m = 0; m < NMAT; ++m) {
         uint32_t raw[4];
         ldmatrix_x4(raw, w + m * mat_stride + a_row * wstride + blk * kW4 + 16 + g * 32 + a_koff);
+        // The high nibbles stay where they are: 16*q still fits u8, so the odd
+        // sub-block's dots come out 16-fold. The even sub-block's scale is taken
+        // 16-fold instead and the common factor leaves with the final fp32 multiply.
         uint32_t lo[4], hi[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           lo[j] = raw[j] & 0x0F0F0F0Fu;
-          hi[j] = (raw[j] >> 4) & 0x0F0F0F0Fu;
+          hi[j] = raw[j] & 0xF0F0F0F0u;
         }
         const int sh = 16 * (g & 1);
-        const int sc0_lo = (s_lo[m].sc[g >> 1] >> sh) & 0xFF, sc1_lo = (s_lo[m].sc[g >> 1] >> (sh + 8)) & 0xFF;
-        const int sc0_hi = (s_hi[m].sc[g >> 1] >> sh) & 0xFF, sc1_hi = (s_hi[m].sc[g >> 1] >> (sh + 8)) & 0xFF;
-        // min bytes of sub-blocks 2g and 2g+1, replicated over the four k positions
-        const uint32_t mn0_lo = __byte_perm(s_lo[m].mn[g >> 1], 0, 0x0000 + sel);
-        const uint32_t mn1_lo = __byte_perm(s_lo[m].mn[g >> 1], 0, 0x1111 + sel);
-        const uint32_t mn0_hi = __byte_perm(s_hi[m].mn[g >> 1], 0, 0x0000 + sel);
-        const uint32_t mn1_hi = __byte_perm(s_hi[m].mn[g >> 1], 0, 0x1111 + sel);
-        const uint32_t ma0[4] = {mn0_lo, mn0_hi, mn0_lo, mn0_hi};
-        const uint32_t ma1[4] = {mn1_lo, mn1_hi, mn1_lo, mn1_hi};
+        const int sc0_lo = ((s_lo[m].sc[g >> 1] >> sh) & 0xFF) << 4, sc1_lo = (s_lo[m].sc[g >> 1] >> (sh + 8)) & 0xFF;
+        const int sc0_hi = ((s_hi[m].sc[g >> 1] >> sh) & 0xFF) << 4, sc1_hi = (s_hi[m].sc[g >> 1] >> (sh + 8)) & 0xFF;
         const int zero[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
@@ -259,10 +255,31 @@ __device__ __forceinline__ void warp_mma_rows(const unsigned char* w, int wstrid
           isum[m][n][1] += sc0_lo * c0[1] + sc1_lo * c1[1];
           isum[m][n][2] += sc0_hi * c0[2] + sc1_hi * c1[2];
           isum[m][n][3] += sc0_hi * c0[3] + sc1_hi * c1[3];
-          // min term: the same activations against the replicated min bytes
-          mma_u8s8(msum[m][n], ma0, b[n][0], b[n][1], msum[m][n]);
-          mma_u8s8(msum[m][n], ma1, b[n][2], b[n][3], msum[m][n]);
         }
+      }
+    }
+    // Min term sum_s mn[s]*bsum[s] as one tiny contraction per block: the eight min
+    // bytes of a row are k = 0..7 of an A fragment, the sub-block sums split as
+    // bsum = 128*hi + lo are two B fragments (lo in 0..127 and hi in -32..31 fit s8).
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      uint32_t blo = 0u, bhi = 0u;
+      if (tig < 2) {
+        const int8_t* sp = xt.split_sums(8 * n + gid, blk);
+        blo = *reinterpret_cast<const uint32_t*>(sp + 4 * tig);
+        bhi = *reinterpret_cast<const uint32_t*>(sp + 8 + 4 * tig);
+      }
+#pragma unroll
+      for (int m = 0; m < NMAT; ++m) {
+        const uint32_t a_lo = tig == 0 ? s_lo[m].mn[0] : (tig == 1 ? s_lo[m].mn[1] : 0u);
+        const uint32_t a_hi = tig == 0 ? s_hi[m].mn[0] : (tig == 1 ? s_hi[m].mn[1] : 0u);
+        const uint32_t ma[4] = {a_lo, a_hi, 0u, 0u};
+        const int zero[4] = {0, 0, 0, 0};
+        int dl[4], dh[4];
+        mma_u8s8(dl, ma, blo, 0u, zero);
+        mma_u8s8(dh, ma, bhi, 0u, zero);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) msum[m][n][j] = dl[j] + 128 * dh[j];
       }
     }
 #pragma unroll
