@@ -106,12 +106,21 @@ def build_workload(device, rank, world, layers, tokens):
         ws.append(synth.MoeWeights(H, FF, E, device, seed=SEED + li))
     inputs = [synth.normal_fp16((tokens, H), SEED + 500 + li, device) for li in range(layers)]
     x0 = synth.normal_fp16((tokens, H), SEED + 499, device)
-    # Zipf bias: one alpha for the stack, found by bisection on layer 0 so that the
-    # top 20 % of the experts take ~70 % of the picks
+    alpha = calibrate_alpha(inputs[0], ws[0].router, device)
+    biases = [torch.from_numpy(synth.zipf_bias(E, SEED + 900 + li, alpha)).to(device)
+              for li in range(layers)]
+    return ws, inputs, x0, biases, alpha
+
+
+def calibrate_alpha(x0_rows, router, device):
+    """Zipf bias strength: one alpha for the stack, found by bisection on layer 0 so that
+    the top 20 % of the experts take ~70 % of the routed picks."""
+    import torch
+    from sager_b200 import synth
     ranks0 = synth.zipf_bias(E, SEED + 900, 1.0)
 
     def share(alpha):
-        lg = inputs[0].float() @ ws[0].router.t() + torch.from_numpy(ranks0 * alpha).to(device)
+        lg = x0_rows.float() @ router.t() + torch.from_numpy(ranks0 * alpha).to(device)
         idx = lg.topk(K, dim=1).indices.cpu().numpy()
         return synth.hot_share(idx, E)
 
@@ -122,10 +131,7 @@ def build_workload(device, rank, world, layers, tokens):
             lo = mid
         else:
             hi = mid
-    alpha = 0.5 * (lo + hi)
-    biases = [torch.from_numpy(synth.zipf_bias(E, SEED + 900 + li, alpha)).to(device)
-              for li in range(layers)]
-    return ws, inputs, x0, biases, alpha
+    return 0.5 * (lo + hi)
 
 
 def cpu_pool_sample(ws0, xn0, bias0, budget_s=12.0):

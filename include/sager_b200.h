@@ -221,14 +221,19 @@ typedef struct sgr_moe_layer {
   int* mail_n;           /* [1], reset by every call */
   void* workspace;
   size_t workspace_bytes;
+  /* row strides for records that travel between ranks; 0 = packed */
+  int route_stride;      /* elements between rows of route_idx / route_w (default n_used+1) */
+  int xq_stride;         /* bytes between Q8_K rows of xq_in / xq_out (default hidden/256*276) */
+  void* xq_out;          /* optional: the router's Q8_K rows are written here, not to the workspace */
 } sgr_moe_layer;
 
 size_t sgr_moe_layer_workspace_bytes(int n_max, int hidden, int n_ff, int n_expert, int n_used);
 int sgr_moe_layer_workspace_init(void* workspace, size_t bytes, void* stream);
 int sgr_moe_layer_decode(const sgr_moe_layer* args, void* stream);
 /* The same layer, only the launches named in `stages` (1 = route/plan, 2 or 4 or 6 =
- * the expert kernel), on a workspace that still holds what the earlier stage of a
- * previous call left there. For measuring one kernel at a time. */
+ * the expert kernel, 1|8 = route without building the plan), on a workspace that still
+ * holds what the earlier stage of a previous call left there. For measuring one kernel
+ * at a time and for the home side of an expert-parallel layer. */
 int sgr_moe_layer_decode_stages(const sgr_moe_layer* args, int stages, void* stream);
 
 /* No counterpart in the reference. sgr_moe_layer_decode for callers that cannot
@@ -243,6 +248,11 @@ int sgr_moe_layer_decode_stages(const sgr_moe_layer* args, int stages, void* str
  * call on each device looks up the array's device address and must be made outside
  * stream capture. Every call on a device uses the same array: calls that overlap on
  * the GPU race. */
+/* Expert parallelism, last step on the home rank (no counterpart in the reference, which is
+ * single-GPU): x[i] = f16(f32(x[i]) + sum_p parts[p*part_stride + i]), p ascending. */
+int sgr_ep_reduce_add_f16(uint16_t* x_f16, const float* parts, int n_parts, long long part_stride,
+                          long long count, void* stream);
+
 size_t sgr_moe_layer_static_limit(void);
 int sgr_moe_layer_decode_static(const sgr_moe_layer* args, void* stream);
 

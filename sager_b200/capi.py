@@ -97,6 +97,7 @@ class MoeLayerArgs(C.Structure):
         ("route_idx", C.c_void_p), ("route_w", C.c_void_p),
         ("mail", C.c_void_p), ("mail_n", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("route_stride", C.c_int), ("xq_stride", C.c_int), ("xq_out", C.c_void_p),
     ]
 
 

@@ -58,7 +58,9 @@ constexpr unsigned kSpinLimit = 1u << 22;         // bounded waits: give up, rai
 struct LayerDev {
   int n, H, FF, E, K, nbh, nbf;
   int e_lo, e_hi, sh_lo, sh_hi;
-  int add_residual, routing_given;
+  int add_residual, routing_given, skip_plan;
+  int rstride;     // elements between consecutive rows of idx / w (K+1 when packed)
+  int xq_stride;   // bytes between consecutive Q8_K rows
   float shared_w;
   const uint16_t* xn;
   const unsigned char* xq_in;
@@ -142,9 +144,9 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   __syncthreads();
   for (int i = tid; i < total; i += blockDim.x) {
     const int r = i / L.K, kk = i - r * L.K;
-    const int e = __ldcg(L.idx + static_cast<size_t>(r) * (L.K + 1) + kk);
+    const int e = __ldcg(L.idx + static_cast<size_t>(r) * L.rstride + kk);
     if (e < 0 || e >= L.E) {
-      for (int q = 0; q <= L.K; ++q) L.w[static_cast<size_t>(r) * (L.K + 1) + q] = 0.f;
+      for (int q = 0; q <= L.K; ++q) L.w[static_cast<size_t>(r) * L.rstride + q] = 0.f;
       atomicAdd(&bad_sh, 1);
     } else if (e >= L.e_lo && e < L.e_hi) {
       atomicOr(&mask[e], 1ull << r);
@@ -207,7 +209,7 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   __syncthreads();
   for (int i = tid; i < total; i += blockDim.x) {
     const int r = i / L.K, kk = i - r * L.K;
-    const int e = __ldcg(L.idx + static_cast<size_t>(r) * (L.K + 1) + kk);
+    const int e = __ldcg(L.idx + static_cast<size_t>(r) * L.rstride + kk);
     int pos = -1;
     if (e >= L.e_lo && e < L.e_hi && e >= 0 && e < L.E) {
       pos = L.off[e] + __popcll(mask[e] & ((1ull << r) - 1ull));
@@ -254,7 +256,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
     for (int b = blockIdx.x * kRouteWarps + warp; b < nt * L.nbh; b += gridDim.x * kRouteWarps) {
       const int t = b / L.nbh, blk = b - t * L.nbh;
       quantize_block_f16(xs + static_cast<size_t>(t) * L.H + blk * kQK,
-                         L.xq + (static_cast<size_t>(tok0 + t) * L.nbh + blk) * kX8, lane);
+                         L.xq + static_cast<size_t>(tok0 + t) * L.xq_stride + blk * kX8, lane);
     }
   }
   if (row < L.E) {
@@ -282,10 +284,11 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
   for (int t = warp; t < nt; t += kRouteWarps) {
     for (int i = lane; i < L.E; i += 32) prob[i] = __ldcg(L.logits + static_cast<size_t>(tok0 + t) * L.E + i);
     __syncwarp();
-    router_select_warp(prob, L.E, L.K, L.idx + static_cast<size_t>(tok0 + t) * (L.K + 1),
-                       L.w + static_cast<size_t>(tok0 + t) * (L.K + 1), L.shared_w, true, lane);
+    router_select_warp(prob, L.E, L.K, L.idx + static_cast<size_t>(tok0 + t) * L.rstride,
+                       L.w + static_cast<size_t>(tok0 + t) * L.rstride, L.shared_w, true, lane);
     __syncwarp();
   }
+  if (L.skip_plan) return;
   // last token tile plans
   __threadfence();
   __syncthreads();
@@ -528,7 +531,7 @@ __device__ __forceinline__ void combine_rows(const LayerDev& L, int row0, int nr
     const int tk = t_lo + i / nrows, r = row0 + i % nrows;
     const size_t o = static_cast<size_t>(tk) * L.H + r;
     float acc = (L.add_residual && L.x_f16 != nullptr) ? h2f(L.x_f16[o]) : 0.f;
-    const float* wr = L.w + static_cast<size_t>(tk) * (L.K + 1);
+    const float* wr = L.w + static_cast<size_t>(tk) * L.rstride;
     for (int kk = 0; kk < L.K; ++kk) {
       const int gs = __ldcg(L.gslot + tk * L.K + kk);
       if (gs >= 0) acc += __ldcg(wr + kk) * __ldcg(L.ybuf + static_cast<size_t>(gs) * L.H + r);
@@ -696,7 +699,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
         xtile_stage(xt, d.ntok,
                     [&](int t) {
                       const int r = shared ? d.p0 + t : __ldcg(L.grows + d.p0 + t);
-                      return xq + static_cast<size_t>(r) * L.nbh * kX8;
+                      return xq + static_cast<size_t>(r) * L.xq_stride;
                     },
                     ttid, kTeamThreads);
       } else {
@@ -823,6 +826,20 @@ __global__ void rearm_kernel(const LayerDev L) {
   if (threadIdx.x == 0) L.cnt[9] = 0u;
 }
 
+// x[i] = f16( f32(x[i]) + sum_p parts[p][i] ), p ascending: the home rank's last step of
+// an expert-parallel layer (partial sums of every owner rank, received row-aligned).
+__global__ void ep_reduce_add_kernel(uint16_t* __restrict__ x, const float* __restrict__ parts,
+                                     int n_parts, size_t part_stride, size_t count) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float acc = h2f(x[i]);
+    for (int p = 0; p < n_parts; ++p) acc += parts[p * part_stride + i];
+    x[i] = f2h(acc);
+  }
+}
+
 #ifdef SGR_PROFILE
 long long* g_prof_buf = nullptr;
 #endif
@@ -865,7 +882,7 @@ SGR_API int sgr_moe_layer_workspace_init(void* workspace, size_t bytes, void* st
 }
 
 SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void* stream) {
-  if (a == nullptr || (stages & 7) == 0) return kErrArg;
+  if (a == nullptr || (stages & 7) == 0) return kErrArg;   // bit 3 (8): route without the plan
   if (a->n <= 0) return kOk;
   if (a->hidden <= 0 || a->hidden % kQK || a->n_ff <= 0 || a->n_ff % kQK || a->n_expert <= 0 ||
       a->n_used <= 0 || a->n_used > a->n_expert || a->n_max < a->n || a->n_max > kMaxRows)
@@ -892,6 +909,10 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
     return kErrGeometry;
   L.add_residual = a->no_residual ? 0 : 1;
   L.routing_given = a->routing_given;
+  L.skip_plan = (stages & 8) ? 1 : 0;
+  L.rstride = a->route_stride > 0 ? a->route_stride : a->n_used + 1;
+  L.xq_stride = a->xq_stride > 0 ? a->xq_stride : (a->hidden / kQK) * kX8;
+  if (L.rstride < a->n_used + 1 || L.xq_stride < (a->hidden / kQK) * kX8 || (L.xq_stride & 3)) return kErrArg;
   L.shared_w = a->shared_w;
   L.xn = a->xn;
   L.xq_in = static_cast<const unsigned char*>(a->xq_in);
@@ -909,7 +930,8 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   L.mail = a->mail;
   L.mail_n = a->mail_n;
   unsigned char* ws = static_cast<unsigned char*>(a->workspace);
-  L.xq = ws + lay.xq;
+  L.xq = a->xq_out != nullptr ? static_cast<unsigned char*>(a->xq_out) : ws + lay.xq;
+  if (reinterpret_cast<uintptr_t>(L.xq) & 3u) return kErrAlign;
   L.logits = reinterpret_cast<float*>(ws + lay.logits);
   L.off = reinterpret_cast<int*>(ws + lay.off);
   L.rec = reinterpret_cast<int4*>(ws + lay.rec);
@@ -980,6 +1002,17 @@ extern "C" __attribute__((visibility("default"))) int sgr_prof_read(long long* h
 
 SGR_API int sgr_moe_layer_decode(const sgr_moe_layer* a, void* stream) {
   return sgr_moe_layer_decode_stages(a, 7, stream);
+}
+
+SGR_API int sgr_ep_reduce_add_f16(uint16_t* x_f16, const float* parts, int n_parts,
+                                  long long part_stride, long long count, void* stream) {
+  if (count <= 0 || n_parts <= 0) return kOk;
+  if (!x_f16 || !parts || part_stride < count) return kErrArg;
+  const int blocks = static_cast<int>(std::min<long long>((count + 255) / 256, 148 * 4));
+  ep_reduce_add_kernel<<<blocks, 256, 0, as_stream(stream)>>>(x_f16, parts, n_parts,
+                                                            static_cast<size_t>(part_stride),
+                                                            static_cast<size_t>(count));
+  return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
 SGR_API size_t sgr_moe_layer_static_limit(void) { return kStaticWsBytes; }

@@ -39,7 +39,7 @@ __device__ __forceinline__ uint16_t f2h(float f) {
   return __half_as_ushort(__float2half(f));   // round to nearest even
 }
 
-// ---- mbarrier + bulk copy (TMA, no tensor map, no multicast) -----------------
+// ---- mbarrier + bulk copy (TMA without a tensor map, one CTA per copy) --------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

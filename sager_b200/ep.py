@@ -1,0 +1,214 @@
+"""Expert parallelism over the ranks of one node.
+
+Every rank is home to `tokens / world` token rows and owns a contiguous range of
+`E / world` experts of every layer (router and shared expert are replicated).
+One layer is: route at home -> all-to-all dispatch of fixed-size token records
+(Q8_K row, top-k ids, weights) -> owner-side partial layer over all received
+rows (only the local experts; shared expert only for the home rows) ->
+all-to-all return of the fp32 partial sums -> residual add at home. Both
+exchanges are NCCL all-to-alls with fixed capacity (every rank's slot holds all
+of its home rows), so the step is static and can be captured in a CUDA graph.
+The reference has no multi-GPU path; the layer arithmetic is that of the
+single-GPU fused layer.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+Q8K_BYTES = 276
+
+
+def record_layout(hidden: int, k: int):
+    """Byte layout of one dispatched token record: Q8_K row, k+1 ids, k+1 weights,
+    padded to 16 bytes. -> (record_bytes, idx_offset, w_offset)."""
+    xq = hidden // 256 * Q8K_BYTES
+    idx_off = xq
+    w_off = xq + (k + 1) * 4
+    rec = (w_off + (k + 1) * 4 + 15) // 16 * 16
+    return rec, idx_off, w_off
+
+
+class EpExchange:
+    """The two fixed-capacity all-to-alls of a layer, on whatever device the buffers
+    live (NCCL on GPUs; gloo on CPU in the host-logic tests)."""
+
+    def __init__(self, world, rank, n_home, hidden, k, device):
+        self.world, self.rank, self.n_home, self.hidden, self.k = world, rank, n_home, hidden, k
+        self.rec, self.idx_off, self.w_off = record_layout(hidden, k)
+        self.send = torch.zeros(world, n_home, self.rec, dtype=torch.uint8, device=device)
+        self.recv = torch.zeros(world, n_home, self.rec, dtype=torch.uint8, device=device)
+        self.part = torch.zeros(world, n_home, hidden, dtype=torch.float32, device=device)
+        self.back = torch.zeros(world, n_home, hidden, dtype=torch.float32, device=device)
+
+    def dispatch(self):
+        """send[0] holds this rank's home records; afterwards recv[p] holds rank p's."""
+        if self.world > 1:
+            self.send[1:] = self.send[0]
+        dist.all_to_all_single(self.recv.view(-1), self.send.view(-1))
+
+    def combine(self):
+        """part[p] holds this rank's partial sums for rank p's home rows; afterwards
+        back[p] holds rank p's partial sums for this rank's home rows."""
+        dist.all_to_all_single(self.back.view(-1), self.part.view(-1))
+
+
+class EpStack:
+    def __init__(self, layers, tokens, n_used, device, rank, world, biases, inputs, x0):
+        from .layer import MoeLayerRunner
+        w0 = layers[0]
+        self.layers, self.device, self.rank, self.world = layers, device, rank, world
+        self.tokens, self.k = tokens, n_used
+        self.n_home = tokens // world
+        lo, hi = w0.lo, w0.hi
+        self.ex = EpExchange(world, rank, self.n_home, w0.hidden, n_used, device)
+        self.home = MoeLayerRunner(self.n_home, w0.hidden, w0.n_ff, w0.n_expert, n_used, device)
+        self.owner = MoeLayerRunner(tokens, w0.hidden, w0.n_ff, w0.n_expert, n_used, device,
+                                    expert_lo=lo, expert_hi=hi)
+        self.tables = [w.table() for w in layers]
+        self.biases = biases
+        h0 = rank * self.n_home
+        self.inputs = [x[h0:h0 + self.n_home].contiguous() for x in inputs]
+        self.x0 = x0[h0:h0 + self.n_home].contiguous()
+        self.x = self.x0.clone()
+        self.graph = None
+        self.launches_per_step = 4 * len(layers)     # route, plan, experts, reduce
+
+    def _ptr(self, t, off=0):
+        return C.c_void_p(t.data_ptr() + off)
+
+    def issue_layer(self, li):
+        from .capi import lib
+        from .ops import stream_ptr
+        w, ex = self.layers[li], self.ex
+        # 1. home: quantise + route straight into the dispatch record slot 0
+        a = self.home.args(self.n_home, self.inputs[li], w.router, self.tables[li], None, x_f16=self.x,
+                           bias=None if self.biases is None else self.biases[li])
+        a.xq_out = self._ptr(ex.send)
+        a.xq_stride = ex.rec
+        a.route_idx = self._ptr(ex.send, ex.idx_off)
+        a.route_w = self._ptr(ex.send, ex.w_off)
+        a.route_stride = ex.rec // 4
+        lib().call("sgr_moe_layer_decode_stages", C.byref(a), 1 | 8, stream_ptr())
+        ex.dispatch()
+        # 2. owner: the local experts over every received row, weighted, no residual
+        h0 = self.rank * self.n_home
+        b = self.owner.args(self.tokens, None, None, self.tables[li], w.shared_ptrs(), out_f32=ex.part,
+                            xq_in=ex.recv, routing_given=True, no_residual=True, shared_lo=h0,
+                            shared_hi=h0 + self.n_home)
+        b.xq_stride = ex.rec
+        b.route_idx = self._ptr(ex.recv, ex.idx_off)
+        b.route_w = self._ptr(ex.recv, ex.w_off)
+        b.route_stride = ex.rec // 4
+        lib().call("sgr_moe_layer_decode_stages", C.byref(b), 7, stream_ptr())
+        ex.combine()
+        # 3. home: residual += sum over owner ranks
+        n = self.n_home * w.hidden
+        lib().call("sgr_ep_reduce_add_f16", self._ptr(self.x), self._ptr(ex.back), self.world, n, n,
+                   stream_ptr())
+
+    def step_eager(self):
+        for li in range(len(self.layers)):
+            self.issue_layer(li)
+
+    def capture(self):
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self.step_eager()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.step_eager()
+
+    def replay(self):
+        self.graph.replay()
+
+
+def run_ep_bench(args, rank, world, device):
+    """N > 1 leg of bench.py: returns the JSON line (rank 0 prints it)."""
+    import bench
+    from . import synth
+    from .capi import lib
+    E, K, H, FF = bench.E, bench.K, bench.H, bench.FF
+    layers_n, tokens = bench.LAYERS, bench.TOKENS
+    assert E % world == 0 and tokens % world == 0
+    lo, hi = rank * (E // world), (rank + 1) * (E // world)
+    ws = [synth.MoeWeights(H, FF, E, device, seed=bench.SEED + li, expert_range=(lo, hi))
+          for li in range(layers_n)]
+    inputs = [synth.normal_fp16((tokens, H), bench.SEED + 500 + li, device) for li in range(layers_n)]
+    x0 = synth.normal_fp16((tokens, H), bench.SEED + 499, device)
+    alpha = bench.calibrate_alpha(inputs[0], ws[0].router, device)
+    biases = [torch.from_numpy(synth.zipf_bias(E, bench.SEED + 900 + li, alpha)).to(device)
+              for li in range(layers_n)]
+    st = EpStack(ws, tokens, K, device, rank, world, biases, inputs, x0)
+    st.capture()
+
+    def step():
+        st.x.copy_(st.x0, non_blocking=True)
+        st.replay()
+
+    def timed(fn, iters):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(args.warmup):
+        step()
+    sampler = bench.ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    ms_step = timed(step, args.steps)
+
+    h_in = torch.empty(layers_n + 1, st.n_home, H, dtype=torch.float16).pin_memory()
+    h_in[0].copy_(st.x0.cpu())
+    for li in range(layers_n):
+        h_in[li + 1].copy_(st.inputs[li].cpu())
+    d_in = torch.empty_like(h_in, device=device)
+    h_out = torch.empty(st.n_home, H, dtype=torch.float16).pin_memory()
+
+    def e2e_step():
+        d_in.copy_(h_in, non_blocking=True)
+        st.x.copy_(d_in[0], non_blocking=True)
+        for li in range(layers_n):
+            st.inputs[li].copy_(d_in[li + 1], non_blocking=True)
+        st.replay()
+        h_out.copy_(st.x, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    clocks = sampler.stop()
+    status = lib().raw("sgr_status")(0)
+    line = {
+        "metric": "q4k_moe_decode_tokens_per_s", "value": tokens / (ms_step * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8 dots, fp32 accumulate", "data": "synthetic",
+        "config": dict(bench.workload_config(world), zipf_alpha=alpha,
+                       exchange="2 NCCL all-to-alls per layer, fixed capacity, captured in the step graph"),
+        "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": int(h_in.numel() * 2) * world,
+                "d2h_bytes_per_step": int(h_out.numel() * 2) * world},
+        "gpu_launches": st.launches_per_step * args.steps, "clocks": clocks,
+        "roofline": {"kernel": "expert_stream_kernel", "bound": "hbm", "achieved": None, "peak": bench.load_peaks()[0],
+                     "unit": "GB/s", "frac": None, "traffic": None,
+                     "note": "per-kernel timing is taken at N=1; at N>1 the step is exchange-latency bound"},
+    }
+    if status != 0:
+        line["device_status"] = "a bounded device-side wait gave up"
+    return line

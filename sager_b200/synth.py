@@ -65,8 +65,13 @@ class MoeWeights:
     """One layer's weights: router [E][H] fp32 and a blob of E+1 experts, each
     [gate | up | down] contiguous (expert E is the always-on shared expert)."""
 
-    def __init__(self, hidden, n_ff, n_expert, device, seed, std=0.02, distinct=None):
+    def __init__(self, hidden, n_ff, n_expert, device, seed, std=0.02, distinct=None,
+                 expert_range=None):
+        """expert_range=(lo, hi): keep only the routed experts lo..hi-1 (and the shared
+        expert) - one rank's shard under expert parallelism. The bytes of an expert
+        are the same whichever shard holds it."""
         self.hidden, self.n_ff, self.n_expert = hidden, n_ff, n_expert
+        self.lo, self.hi = (0, n_expert) if expert_range is None else expert_range
         self.gu_bytes = n_ff * (hidden // QK_K) * Q4K_BYTES
         self.dn_bytes = hidden * (n_ff // QK_K) * Q4K_BYTES
         self.expert_bytes = 2 * self.gu_bytes + self.dn_bytes
@@ -74,39 +79,52 @@ class MoeWeights:
         self.router = (torch.randn(n_expert, hidden, generator=g, device=device) * std).float()
         n_all = n_expert + 1
         n_make = n_all if distinct is None else min(distinct, n_all)
-        self.blob = torch.empty(n_all, self.expert_bytes, dtype=torch.uint8, device=device)
+        # blob slot of expert e: e - lo for local routed experts, (hi - lo) for the shared one
+        self.n_slots = self.hi - self.lo + 1
+        self.blob = torch.empty(self.n_slots, self.expert_bytes, dtype=torch.uint8, device=device)
         step = 32
         for e0 in range(0, n_make, step):
             e1 = min(n_make, e0 + step)
             wg = torch.randn((e1 - e0) * 2 * n_ff, hidden, generator=g, device=device) * std
             wd = torch.randn((e1 - e0) * hidden, n_ff, generator=g, device=device) * std
+            keep = [e for e in range(e0, e1) if self.slot(e) is not None]
+            if not keep:
+                continue                      # same generator stream, another rank's experts
             qg = quantize_q4k(wg).reshape(e1 - e0, 2 * self.gu_bytes)
             qd = quantize_q4k(wd).reshape(e1 - e0, self.dn_bytes)
-            self.blob[e0:e1, :2 * self.gu_bytes] = qg
-            self.blob[e0:e1, 2 * self.gu_bytes:] = qd
+            for e in keep:
+                self.blob[self.slot(e), :2 * self.gu_bytes] = qg[e - e0]
+                self.blob[self.slot(e), 2 * self.gu_bytes:] = qd[e - e0]
         # remaining experts reuse the made ones' bytes at their own addresses
         # (distinct HBM lines; the arithmetic cost is the same)
         for e in range(n_make, n_all):
-            self.blob[e] = self.blob[e % n_make]
+            if self.slot(e) is not None and self.slot(e % n_make) is not None:
+                self.blob[self.slot(e)] = self.blob[self.slot(e % n_make)]
+
+    def slot(self, e):
+        if e == self.n_expert:
+            return self.hi - self.lo
+        return e - self.lo if self.lo <= e < self.hi else None
 
     def matrix(self, e, m):
         """uint8 view of matrix m (0 gate, 1 up, 2 down) of expert e."""
         o = [0, self.gu_bytes, 2 * self.gu_bytes, self.expert_bytes]
-        return self.blob[e, o[m]:o[m + 1]]
+        return self.blob[self.slot(e), o[m]:o[m + 1]]
 
     def table(self, absent=()):
-        """int64 [3][E] device pointer table; `absent` experts get null entries."""
+        """int64 [3][E] device pointer table; experts outside this shard and `absent`
+        ones get null entries."""
         base = self.blob.data_ptr()
         t = torch.zeros(3, self.n_expert, dtype=torch.int64)
         o = [0, self.gu_bytes, 2 * self.gu_bytes]
         for m in range(3):
-            t[m] = base + torch.arange(self.n_expert, dtype=torch.int64) * self.expert_bytes + o[m]
+            t[m, self.lo:self.hi] = base + torch.arange(self.hi - self.lo, dtype=torch.int64) * self.expert_bytes + o[m]
         for e in absent:
             t[:, e] = 0
         return t.to(self.blob.device)
 
     def shared_ptrs(self):
-        base = self.blob.data_ptr() + self.n_expert * self.expert_bytes
+        base = self.blob.data_ptr() + (self.hi - self.lo) * self.expert_bytes
         return [base, base + self.gu_bytes, base + 2 * self.gu_bytes]
 
 

@@ -191,3 +191,55 @@ def test_stack_graph_replay_is_deterministic(oracle):
     assert f16_close(eager.cpu().numpy(), x_np.astype(np.float32), tol=2e-3)
     from sager_b200 import lib
     assert lib().raw("sgr_status")(0) == 0
+
+
+def test_expert_parallel_record_path_on_one_device(full_w):
+    """The expert-parallel layer with its exchanges done by hand on one device: each
+    emulated rank routes its home rows straight into dispatch records (strided Q8_K
+    rows, ids, weights), every rank's owner call runs its expert range over all
+    records, partial sums are added at home. Must reproduce the single call."""
+    import ctypes as C
+    from sager_b200 import lib
+    from sager_b200.ep import record_layout
+    from sager_b200.ops import stream_ptr
+    w, k, world, tokens = full_w, 8, 4, 16
+    n_home = tokens // world
+    x16 = synth.normal_fp16((tokens, w.hidden), 91, DEV)
+    _, x_full, out_full = run_layer(w, tokens, k, x16, n_max=64)
+    rec, idx_off, w_off = record_layout(w.hidden, k)
+    records = torch.zeros(world, n_home, rec, dtype=torch.uint8, device=DEV)
+    for r in range(world):                                    # home side of every rank
+        home = MoeLayerRunner(n_home, w.hidden, w.n_ff, w.n_expert, k, DEV)
+        a = home.args(n_home, x16[r * n_home:(r + 1) * n_home].contiguous(), w.router, w.table(), None,
+                      x_f16=torch.zeros(n_home, w.hidden, dtype=torch.float16, device=DEV))
+        base = records[r].data_ptr()
+        a.xq_out, a.xq_stride = C.c_void_p(base), rec
+        a.route_idx, a.route_w = C.c_void_p(base + idx_off), C.c_void_p(base + w_off)
+        a.route_stride = rec // 4
+        lib().call("sgr_moe_layer_decode_stages", C.byref(a), 1 | 8, stream_ptr())
+    torch.cuda.synchronize()
+    total = x16.float().clone()
+    per = w.n_expert // world
+    for r in range(world):                                    # owner side of every rank
+        owner = MoeLayerRunner(64, w.hidden, w.n_ff, w.n_expert, k, DEV, expert_lo=r * per,
+                               expert_hi=(r + 1) * per)
+        part = torch.zeros(tokens, w.hidden, dtype=torch.float32, device=DEV)
+        b = owner.args(tokens, None, None, w.table(), w.shared_ptrs(), out_f32=part, xq_in=records,
+                       routing_given=True, no_residual=True, shared_lo=r * n_home,
+                       shared_hi=(r + 1) * n_home)
+        b.xq_stride, b.route_stride = rec, rec // 4
+        b.route_idx = C.c_void_p(records.data_ptr() + idx_off)
+        b.route_w = C.c_void_p(records.data_ptr() + w_off)
+        lib().call("sgr_moe_layer_decode_stages", C.byref(b), 7, stream_ptr())
+        torch.cuda.synchronize()
+        total += part
+    assert rel(total.cpu().numpy(), out_full.cpu().numpy()) < 1e-6
+    # and the home-side reduction kernel
+    xh = x16[:n_home].clone()
+    parts = torch.randn(world, n_home, w.hidden, device=DEV)
+    lib().call("sgr_ep_reduce_add_f16", C.c_void_p(xh.data_ptr()), C.c_void_p(parts.data_ptr()), world,
+               n_home * w.hidden, n_home * w.hidden, stream_ptr())
+    want = x16[:n_home].float()
+    for p_ in range(world):
+        want = want + parts[p_]
+    assert torch.equal(xh, want.half())
