@@ -248,6 +248,15 @@ int sgr_moe_layer_decode_stages(const sgr_moe_layer* args, int stages, void* str
  * call on each device looks up the array's device address and must be made outside
  * stream capture. Every call on a device uses the same array: calls that overlap on
  * the GPU race. */
+/* Prefill grouped GEMM on int8 tensor cores (tcgen05, accumulators in tensor memory).
+ * Replaces dequant_experts_q4_k_f16 + tc_gemm_f16_raw (cuda_ops.hpp:125-131, one cuBLAS GEMM per
+ * expert and matrix) with the contract of gemv_grouped_tab_q4_k_q8_f16out_mtok (cuda_ops.hpp:247):
+ * xq is the expert-major slab of Q8_K rows, off[n_expert+1] the row prefix of the device plan,
+ * y[off[e]+t][r] = W_e[r] . xq[off[e]+t] in fp16; a null table entry gives zero rows. The integer
+ * arithmetic is that of the Q4_K x Q8_K path (exact sub-block dots), not of the fp16 GEMM. */
+int sgr_moe_grouped_gemm_i8(const void* const* w_tab, const int* off, const void* xq, uint16_t* y,
+                            int n_rows, int k, int n_expert, void* stream);
+
 /* Expert parallelism, last step on the home rank (no counterpart in the reference, which is
  * single-GPU): x[i] = f16(f32(x[i]) + sum_p parts[p*part_stride + i]), p ascending. */
 int sgr_ep_reduce_add_f16(uint16_t* x_f16, const float* parts, int n_parts, long long part_stride,
