@@ -140,3 +140,73 @@ class MoeStack:
 
     def replay(self):
         self.graph.replay()
+
+
+class PrefillLayer:
+    """One MoE layer over a chunk of many token rows, as the reference's
+    `Session::moe_dispatch_device` drives it for prefill (src/core/session.cpp:2482-3030),
+    call for call through the library's launchers - with the expert math on the int8
+    tensor-core grouped GEMM instead of the reference's fp16 cuBLAS path. Buffers follow
+    the session's scratch (src/core/session.cpp:207-257)."""
+
+    TOK_PER = 16
+
+    def __init__(self, n_max, hidden, n_ff, n_expert, n_used, device):
+        from . import ops
+        self.ops = ops
+        self.n_max, self.H, self.F, self.E, self.K = n_max, hidden, n_ff, n_expert, n_used
+        d, u8, f16, i32, f32 = device, torch.uint8, torch.float16, torch.int32, torch.float32
+        R = n_max * n_used
+        self.R = R
+        self.xq = torch.empty(n_max, hidden // 256 * 276, dtype=u8, device=d)
+        self.logits = torch.empty(n_max, n_expert, dtype=f32, device=d)
+        self.idx = torch.zeros(n_max, n_used + 1, dtype=i32, device=d)
+        self.w = torch.zeros(n_max, n_used + 1, dtype=f32, device=d)
+        self.gslot = torch.zeros(R, dtype=i32, device=d)
+        self.grows = torch.zeros(R, dtype=i32, device=d)
+        self.off = torch.zeros(n_expert + 1, dtype=i32, device=d)
+        self.toff = torch.zeros(n_expert + 1, dtype=i32, device=d)
+        self.meta = torch.zeros(4, dtype=i32, device=d)
+        self.mail = torch.zeros(n_expert, dtype=i32, device=d)
+        self.mail_n = torch.zeros(1, dtype=i32, device=d)
+        self.xqg = torch.empty(R, hidden // 256 * 276, dtype=u8, device=d)
+        self.g = torch.empty(R, n_ff, dtype=f16, device=d)
+        self.u = torch.empty(R, n_ff, dtype=f16, device=d)
+        self.hq = torch.empty(R, n_ff // 256 * 276, dtype=u8, device=d)
+        self.yg = torch.empty(R, hidden, dtype=f16, device=d)
+        self.expert_y = torch.zeros(n_max, n_used + 1, hidden, dtype=f16, device=d)
+        self.sh_g = torch.empty(n_max, n_ff, dtype=f16, device=d)
+        self.sh_u = torch.empty(n_max, n_ff, dtype=f16, device=d)
+        self.sh_q = torch.empty(n_max, n_ff // 256 * 276, dtype=u8, device=d)
+        self.sh_y = torch.empty(n_max, hidden, dtype=f16, device=d)
+
+    def run(self, n, xn, x, weights, table, logits=None, shared=True, experts_only=False):
+        """x [n][H] fp16 residual, combined in place. `logits` replaces the router GEMV
+        (the prefill benchmark draws them directly). experts_only stops after the three
+        grouped GEMMs (timing)."""
+        o, H, F, E, K = self.ops, self.H, self.F, self.E, self.K
+        if not experts_only:
+            o.quantize_q8_k(xn, self.xq, n * H)
+            if logits is None:
+                o.gemv_f32_out_f16x_mtok(weights.router, xn, self.logits, E, H, n)
+                logits = self.logits
+            o.router_topk_batched(logits, self.idx, self.w, E, K, K + 1, n, 1.0 if shared else 0.0)
+            o.moe_dispatch_scan(self.idx, self.w, self.gslot, self.grows, self.off, self.toff, self.meta,
+                                self.mail, self.mail_n, n, K, E, self.TOK_PER)
+            o.gather_rows_q8_n(self.xqg, self.xq, self.grows, self.meta, n * K, H // 256)
+        o.moe_grouped_gemm_i8(table[0], self.off, self.xqg, self.g, F, H, E)
+        o.moe_grouped_gemm_i8(table[1], self.off, self.xqg, self.u, F, H, E)
+        o.silu_mul_f16_n(self.g, self.g, self.u, self.meta, n * K, F)
+        o.quantize_q8_k_n(self.g, self.hq, self.meta, F, n * K * (F // 256))
+        o.moe_grouped_gemm_i8(table[2], self.off, self.hq, self.yg, H, F, E)
+        if experts_only:
+            return
+        o.scatter_routed_f16(self.expert_y, self.yg, self.gslot, n, K, H)
+        if shared:
+            sg, su, sd = weights.shared_ptrs()
+            o.gemv2_q4_k_q8_f16out_mtok(sg, su, self.xq, self.sh_g, self.sh_u, F, H, n)
+            o.silu_mul_f16(self.sh_g, self.sh_g, self.sh_u, n, F)
+            o.quantize_q8_k(self.sh_g, self.sh_q, n * F)
+            o.gemv_q4_k_q8_f16out_mtok(sd, self.sh_q, self.sh_y, H, F, n)
+            self.expert_y[:n, K, :].copy_(self.sh_y[:n])
+        o.moe_combine_batched_f16(x, self.expert_y, self.w, K, H, n)

@@ -19,6 +19,8 @@ def _conv(a):
         return None
     if isinstance(a, torch.Tensor):
         return C.c_void_p(a.data_ptr())
+    if isinstance(a, int) and a > 0x7FFFFFFF:
+        return C.c_void_p(a)                 # a raw device address
     return a
 
 

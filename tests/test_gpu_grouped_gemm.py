@@ -88,3 +88,48 @@ def test_prefill_sized_plan(oracle):
     xq_np = xq.cpu().numpy()
     for r in rng.integers(0, R, 12).tolist():
         assert f16_close(y[r].cpu().numpy(), oracle.gemv(w_np, xq_np[r], n_rows, k))
+
+
+def test_prefill_layer_against_oracle(oracle):
+    """The whole prefill call sequence (router, plan, gather, three tensor-core grouped GEMMs,
+    SwiGLU, requantisation, scatter, shared expert, combine). The launchers keep the reference's
+    fp16 staging (g, u, h, y and the combine slab are fp16: their signatures say so), so the check
+    is made twice: against the oracle's restatement of that staged device path (a few fp16 steps)
+    and against the fp32 CPU layer. The second gap is not a kernel property: rounding h to fp16
+    before it is requantised moves Q8 codes, so the staged path and the fp32 path differ at the
+    level of the Q8 grid (measured 3.6e-3 of the largest output here, with weights 2.5x the
+    benchmark's scale); it is asserted below 1e-2 and printed. The fused decode layer, which keeps
+    fp32 intermediates, meets the 1e-3 bound at 1e-7."""
+    from sager_b200 import synth
+    from sager_b200.layer import PrefillLayer
+    from tests.test_gpu_moe_layer import oracle_layer
+    H, F, E, K, n = 512, 256, 16, 4, 300
+    w = synth.MoeWeights(H, F, E, DEV, seed=61, std=0.05)
+    x16 = synth.normal_fp16((n, H), 62, DEV)
+    layer = PrefillLayer(n, H, F, E, K, DEV)
+    x = x16.clone()
+    layer.run(n, x16, x, w, w.table())
+    torch.cuda.synchronize()
+    x_np = x16.cpu().numpy()
+    got = x.cpu().numpy()
+    want = oracle_layer(oracle, w, x_np, x_np.astype(np.float32), K)
+    assert np.array_equal(layer.idx.cpu().numpy()[:n, :K], want["idx"][:, :K])
+    assert int(layer.meta[0].item()) == n * K
+    gap = np.abs(got.astype(np.float32) - want["out"]).max() / np.abs(want["out"]).max()
+    print(f"prefill layer (fp16 staging) vs fp32 CPU layer: max relative error {gap:.2e}")
+    assert gap < 1e-2
+    # the staged device path, restated with the oracle's pieces, for a few rows
+    mats = {e: [w.matrix(e, m).cpu().numpy() for m in range(3)] for e in range(E + 1)}
+    for r in (0, 17, 299):
+        xq = oracle.quantize_q8k_f16(x_np[r][None])[0]
+        slab = np.zeros((K + 1, H), dtype=np.float16)
+        for kk in range(K + 1):
+            e = int(want["idx"][r, kk]) if kk < K else E
+            g16 = oracle.gemv(mats[e][0], xq, F, H).astype(np.float16)
+            u16 = oracle.gemv(mats[e][1], xq, F, H).astype(np.float16)
+            h16 = oracle.silu_mul_f16(g16, u16).view(np.float16)
+            hq = oracle.quantize_q8k_f16(h16[None])[0]
+            slab[kk] = oracle.gemv(mats[e][2], hq, H, F).astype(np.float16)
+        ref = oracle.combine_batched_f16(x_np[r][None], slab[None], want["w"][r][None], K, H, 1)
+        # one Q8 code of h may flip where the device's expf differs by an ulp: allow a few fp16 steps
+        assert f16_ulp_diff(got[r], ref.view(np.float16).reshape(H)) <= 4
