@@ -42,7 +42,9 @@ namespace sgr {
 namespace {
 
 constexpr int kMaxRows = 64;       // token rows per call (row masks are 64-bit)
-constexpr int kTokTile = 8;        // token rows per tile of the expert kernel (one MMA n-tile)
+constexpr int kTokTile = 8;        // token rows per tile of the item kernel (one MMA n-tile)
+constexpr int kMaxGrid = 1024;           // most CTAs the expert kernels are launched with
+constexpr int kRowsKernelMinRows = 16;   // layers of at least this many token rows run the row-streaming kernel
 constexpr int kRouteTok = 8;       // token rows per CTA of the route kernel
 constexpr int kRouteWarps = 8;
 
@@ -84,6 +86,13 @@ struct LayerDev {
   int* grows;      // [n*K] source row of a grouped slot
   unsigned* cnt;   // [0..7] route tiles, [8] route tiles done, [9] expert kernel grid barrier
   unsigned* tile_cnt;  // [max_tiles] finished gate/up items per tile
+  unsigned* blk_cnt;   // [max_tiles][nbf] row-streaming kernel: warps done with a 256-wide block of h
+  unsigned* ready;     // [max_tiles] row-streaming kernel: quantised blocks of h published
+  unsigned char* hq;   // [(n_max*K + n_max)][nbf] Q8_K rows of h, 288-byte blocks (row-streaming kernel)
+  int tok_tile;        // token rows per tile: 8 (item kernel) or 16 (row-streaming kernel)
+  unsigned char* xq16; // [n_max][nbh] the quantised rows once more in 288-byte blocks (row-streaming kernel)
+  int* cta_lo;         // [2][grid + 1] row-streaming kernel: first gate/up and first down group of every CTA
+  int grid;            // CTAs of the expert kernel
   float* hbuf;     // [(n_max*K + n_max)][FF]
   float* ybuf;     // [(n_max*K + n_max)][H]
   int n_max;
@@ -103,7 +112,7 @@ struct LayerDev {
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct WsLayout {
-  size_t xq, logits, off, rec, meta, gslot, grows, cnt, tile_cnt, hbuf, ybuf, total;
+  size_t xq, logits, off, rec, meta, gslot, grows, cnt, tile_cnt, blk_cnt, ready, hbuf, ybuf, hq, xq16, cta_lo, total;
 };
 inline WsLayout ws_layout(int n_max, int H, int FF, int E, int K) {
   WsLayout l{};
@@ -120,8 +129,13 @@ inline WsLayout ws_layout(int n_max, int H, int FF, int E, int K) {
   l.grows = take(static_cast<size_t>(n_max) * K * 4);
   l.cnt = take((16 + static_cast<size_t>(H) / 16 + 1) * 4);
   l.tile_cnt = take(tiles * 4);
+  l.blk_cnt = take(tiles * (FF / kQK) * 4);
+  l.ready = take(tiles * 4);
   l.hbuf = take(rows * FF * 4);
   l.ybuf = take(rows * H * 4);
+  l.hq = take(rows * (FF / kQK) * 288);     // padded Q8_K blocks (rs::kHq)
+  l.xq16 = take(static_cast<size_t>(n_max) * (H / kQK) * 288);
+  l.cta_lo = take(2 * (kMaxGrid + 1) * 4);
   l.total = p;
   return l;
 }
@@ -132,6 +146,73 @@ inline WsLayout ws_layout(int n_max, int H, int FF, int E, int K) {
 // row order) and needs no sort. Routes to experts outside [e_lo, e_hi) are left
 // to their owner (gslot = -1); ids outside [0, E) silence their row as in
 // moe_dispatch_scan (moe.cu:385-398 of the reference).
+__device__ __forceinline__ void reset_tile_counters(const LayerDev& L, int tid, int nthr) {
+  const int tiles = L.n_max * L.K + L.n_max;
+  for (int i = tid; i < tiles; i += nthr) {
+    L.tile_cnt[i] = 0u;
+    L.ready[i] = 0u;
+  }
+  for (int i = tid; i < tiles * L.nbf; i += nthr) L.blk_cnt[i] = 0u;
+}
+
+// Rows [t0, t0 + nt) of caller-provided packed Q8_K rows, once more in 288-byte blocks.
+__device__ __forceinline__ void pad_xq_rows(const LayerDev& L, int t0, int nt, int tid, int nthr) {
+  const int words = kX8 / 4;
+  for (int i = tid; i < nt * L.nbh * words; i += nthr) {
+    const int tb = i / words, w = i - tb * words;
+    const int t = tb / L.nbh, blk = tb - t * L.nbh;
+    const uint32_t v = reinterpret_cast<const uint32_t*>(L.xq_in + static_cast<size_t>(t0 + t) * L.xq_stride + blk * kX8)[w];
+    uint32_t* o = reinterpret_cast<uint32_t*>(L.xq16 + (static_cast<size_t>(t0 + t) * L.nbh + blk) * 288);
+    o[w == 0 ? 0 : w + 3] = v;
+  }
+}
+
+// Relative time of one stage of the row-streaming kernel for a tile of `ntok` rows
+// (memory-bound below nine rows, bound by the two MMA token groups above).
+#ifndef SGR_RS_COST_SMALL
+#define SGR_RS_COST_SMALL 10
+#define SGR_RS_COST_MID 10
+#define SGR_RS_COST_BIG 13
+#endif
+__device__ __forceinline__ int tile_cost(int ntok) {
+  return ntok <= 2 ? SGR_RS_COST_SMALL : (ntok <= 8 ? SGR_RS_COST_MID : SGR_RS_COST_BIG);
+}
+
+// Row-streaming kernel: cut the tile sequence into L.grid runs of equal cost and store
+// every CTA's first gate/up group and first down group (the same cut for both phases).
+// One CTA, after the tile records are written; scratch: (tiles + 1) ints.
+__device__ void plan_cta_ranges(const LayerDev& L, int* wsum, int n_tiles, int gpt_gu, int gpt_dn) {
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  for (int i = tid; i < n_tiles; i += nthr) wsum[i + 1] = tile_cost(L.rec[i].y);
+  __syncthreads();
+  if (tid == 0) {
+    wsum[0] = 0;
+    for (int i = 0; i < n_tiles; ++i) wsum[i + 1] += wsum[i];
+  }
+  __syncthreads();
+  const long long total = wsum[n_tiles];
+  for (int c = tid; c <= L.grid; c += nthr) {
+    int gu = 0, dn = 0;
+    if (c == L.grid || total == 0) {
+      gu = n_tiles * gpt_gu;
+      dn = n_tiles * gpt_dn;
+      if (c != L.grid) gu = dn = 0;
+    } else {
+      const long long target = total * c / L.grid;
+      int lo = 0, hi = n_tiles;                  // last tile with wsum[tile] <= target
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (wsum[mid] <= target) lo = mid; else hi = mid;
+      }
+      const long long rem = target - wsum[lo], ct = wsum[lo + 1] - wsum[lo];
+      gu = lo * gpt_gu + static_cast<int>((rem * gpt_gu + ct / 2) / ct);
+      dn = lo * gpt_dn + static_cast<int>((rem * gpt_dn + ct / 2) / ct);
+    }
+    L.cta_lo[c] = gu;
+    L.cta_lo[kMaxGrid + 1 + c] = dn;
+  }
+}
+
 __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   unsigned long long* mask = reinterpret_cast<unsigned long long*>(smem);       // [E]
   int* scan_rows = reinterpret_cast<int*>(smem + static_cast<size_t>(L.E) * 8);   // [256]
@@ -139,6 +220,7 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   __shared__ int bad_sh;
   const int tid = threadIdx.x;
   const int total = L.n * L.K;
+  const int TT = L.tok_tile;
   if (tid == 0) bad_sh = 0;
   for (int e = tid; e < L.E; e += blockDim.x) mask[e] = 0ull;
   __syncthreads();
@@ -160,7 +242,7 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   for (int e = e0; e < e1; ++e) {
     const int c = __popcll(mask[e]);
     rows += c;
-    tiles += (c + kTokTile - 1) / kTokTile;
+    tiles += (c + TT - 1) / TT;
   }
   scan_rows[tid] = rows;
   scan_tiles[tid] = tiles;
@@ -177,10 +259,10 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
     // shared expert: tiles over the rows [sh_lo, sh_hi), appended after the routed ones
     int sh_tiles = 0;
     if (L.sh[0] != nullptr && L.sh_hi > L.sh_lo) {
-      sh_tiles = (L.sh_hi - L.sh_lo + kTokTile - 1) / kTokTile;
+      sh_tiles = (L.sh_hi - L.sh_lo + TT - 1) / TT;
       for (int i = 0; i < sh_tiles; ++i) {
-        const int t0 = i * kTokTile;
-        L.rec[at + i] = make_int4(L.E, min(kTokTile, L.sh_hi - L.sh_lo - t0),
+        const int t0 = i * TT;
+        L.rec[at + i] = make_int4(L.E, min(TT, L.sh_hi - L.sh_lo - t0),
                                   L.n_max * L.K + L.sh_lo + t0, L.sh_lo + t0);
       }
     }
@@ -192,15 +274,15 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
     if (L.mail_n != nullptr) *L.mail_n = 0;
     L.cnt[9] = 0u;                        // grid barrier of the expert kernel
   }
-  for (int i = tid; i < L.n_max * L.K + L.n_max; i += blockDim.x) L.tile_cnt[i] = 0u;
+  reset_tile_counters(L, tid, blockDim.x);
   __syncthreads();
   {
     int ar = scan_rows[tid], at = scan_tiles[tid];
     for (int e = e0; e < e1; ++e) {
       const int c = __popcll(mask[e]);
       L.off[e] = ar;
-      for (int t0 = 0; t0 < c; t0 += kTokTile) {
-        L.rec[at] = make_int4(e, min(kTokTile, c - t0), ar + t0, ar + t0);
+      for (int t0 = 0; t0 < c; t0 += TT) {
+        L.rec[at] = make_int4(e, min(TT, c - t0), ar + t0, ar + t0);
         ++at;
       }
       ar += c;
@@ -217,9 +299,16 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
     }
     L.gslot[i] = pos;
   }
+  if (L.tok_tile != kTokTile) {
+    __syncthreads();                          // tile records and meta written (same CTA)
+    plan_cta_ranges(L, reinterpret_cast<int*>(smem), L.meta[1], L.FF / 128, L.H / 256);
+  }
 }
 
-constexpr size_t plan_smem(int E) { return static_cast<size_t>(E) * 8 + 2 * 256 * 4; }   // CTAs of <= 256 threads
+// CTAs of <= 256 threads; the second term is the cost prefix of the row-streaming kernel's partition
+inline size_t plan_smem(int E, int n_max, int K) {
+  return std::max(static_cast<size_t>(E) * 8 + 2 * 256 * 4, (static_cast<size_t>(n_max) * K + n_max + 2) * 4);
+}
 
 // ---- launch 1: route ------------------------------------------------------------------
 // grid (ceil(E / 8), ceil(n / 8)), 256 threads. Dynamic smem: max(8 rows of fp16 x,
@@ -252,11 +341,15 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
         reinterpret_cast<const uint4*>(L.xn + static_cast<size_t>(tok0) * L.H)[i];
   __syncthreads();
 
-  if (L.xq_in == nullptr) {
+  if (L.xq_in != nullptr) {
+    if (blockIdx.x == 0 && L.tok_tile != kTokTile) pad_xq_rows(L, tok0, nt, tid, blockDim.x);
+  } else {
     for (int b = blockIdx.x * kRouteWarps + warp; b < nt * L.nbh; b += gridDim.x * kRouteWarps) {
       const int t = b / L.nbh, blk = b - t * L.nbh;
       quantize_block_f16(xs + static_cast<size_t>(t) * L.H + blk * kQK,
-                         L.xq + static_cast<size_t>(tok0 + t) * L.xq_stride + blk * kX8, lane);
+                         L.xq + static_cast<size_t>(tok0 + t) * L.xq_stride + blk * kX8, lane,
+                         L.tok_tile == kTokTile ? nullptr
+                                                : L.xq16 + (static_cast<size_t>(tok0 + t) * L.nbh + blk) * 288);
     }
   }
   if (row < L.E) {
@@ -316,6 +409,7 @@ __global__ void __launch_bounds__(128) plan_kernel(const LayerDev L) {
   extern __shared__ __align__(16) unsigned char smem[];
   pdl_wait();
   pdl_launch_dependents();
+  if (L.tok_tile != kTokTile) pad_xq_rows(L, 0, L.n, threadIdx.x, blockDim.x);
   build_plan(L, smem);
 }
 
@@ -542,6 +636,8 @@ __device__ __forceinline__ void combine_rows(const LayerDev& L, int row0, int nr
     if (L.x_f16 != nullptr && L.add_residual) L.x_f16[o] = f2h(acc);
   }
 }
+
+#include "expert_rows.cuh"
 
 __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const LayerDev L) {
   extern __shared__ __align__(16) unsigned char smem[];
@@ -822,7 +918,7 @@ unsigned char* g_static_ws_addr[kStaticMaxDevices];     // per-device address of
 __global__ void rearm_kernel(const LayerDev L) {
   pdl_wait();
   pdl_launch_dependents();
-  for (int i = threadIdx.x; i < L.n_max * L.K + L.n_max; i += blockDim.x) L.tile_cnt[i] = 0u;
+  reset_tile_counters(L, threadIdx.x, blockDim.x);
   if (threadIdx.x == 0) L.cnt[9] = 0u;
 }
 
@@ -882,7 +978,7 @@ SGR_API int sgr_moe_layer_workspace_init(void* workspace, size_t bytes, void* st
 }
 
 SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void* stream) {
-  if (a == nullptr || (stages & 7) == 0) return kErrArg;   // bit 3 (8): route without the plan
+  if (a == nullptr || (stages & 7) == 0) return kErrArg;   // bit 3 (8): route without the plan; bits 4, 5: kernel choice
   if (a->n <= 0) return kOk;
   if (a->hidden <= 0 || a->hidden % kQK || a->n_ff <= 0 || a->n_ff % kQK || a->n_expert <= 0 ||
       a->n_used <= 0 || a->n_used > a->n_expert || a->n_max < a->n || a->n_max > kMaxRows)
@@ -936,6 +1032,11 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   L.off = reinterpret_cast<int*>(ws + lay.off);
   L.rec = reinterpret_cast<int4*>(ws + lay.rec);
   L.tile_cnt = reinterpret_cast<unsigned*>(ws + lay.tile_cnt);
+  L.blk_cnt = reinterpret_cast<unsigned*>(ws + lay.blk_cnt);
+  L.ready = reinterpret_cast<unsigned*>(ws + lay.ready);
+  L.hq = ws + lay.hq;
+  L.xq16 = ws + lay.xq16;
+  L.cta_lo = reinterpret_cast<int*>(ws + lay.cta_lo);
   L.meta = reinterpret_cast<int*>(ws + lay.meta);
   L.gslot = reinterpret_cast<int*>(ws + lay.gslot);
   L.grows = reinterpret_cast<int*>(ws + lay.grows);
@@ -944,10 +1045,22 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   L.ybuf = reinterpret_cast<float*>(ws + lay.ybuf);
   L.n_max = a->n_max;
   L.status = status_word();
+  // Which expert kernel: the row-streaming one pays once a layer has enough tiles to
+  // give every SM whole groups (bit 4 of `stages` forces it, bit 5 forces the item
+  // kernel; both stages of a split call must be given the same bits).
+  const bool use_rows = (stages & 32) ? false : ((stages & 16) ? true : a->n >= kRowsKernelMinRows);
+  L.tok_tile = use_rows ? rs::kTok : kTokTile;
+  {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      return kErrLaunch;
+    L.grid = std::min(sms, kMaxGrid);
+  }
 #ifdef SGR_PROFILE
   if (g_prof_buf == nullptr) {
-    cudaMalloc(&g_prof_buf, 1024 * 16 * sizeof(long long));
-    cudaMemset(g_prof_buf, 0, 1024 * 16 * sizeof(long long));
+    cudaMalloc(&g_prof_buf, (1024 * 16 + 160 * 512) * sizeof(long long));
+    cudaMemset(g_prof_buf, 0, (1024 * 16 + 160 * 512) * sizeof(long long));
   }
   L.prof = g_prof_buf;
 #endif
@@ -959,16 +1072,23 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   } else if (!a->routing_given) {
     const size_t smem = std::max<size_t>(
         std::max<size_t>(static_cast<size_t>(kRouteTok) * L.H * 2, static_cast<size_t>(kRouteWarps) * L.E * 4),
-        plan_smem(L.E));
+        plan_smem(L.E, L.n_max, L.K));
     rc = launch_pdl(route_kernel, dim3((L.E + kRouteWarps - 1) / kRouteWarps, (L.n + kRouteTok - 1) / kRouteTok),
                     kRouteWarps * 32, smem, s, L);
   } else {
     if (!a->xq_in) return kErrArg;
-    rc = launch_pdl(plan_kernel, dim3(1), 128, plan_smem(L.E), s, L);
+    rc = launch_pdl(plan_kernel, dim3(1), 128, plan_smem(L.E, L.n_max, L.K), s, L);
   }
   if (rc != kOk) return rc;
 
-  if (stages & 6) {
+  if ((stages & 6) && use_rows) {
+    const int sms = L.grid;
+    if (!(stages & 1)) {
+      rc = launch_pdl(rearm_kernel, dim3(1), 256, 0, s, L);
+      if (rc != kOk) return rc;
+    }
+    rc = launch_pdl(rs::expert_rows_kernel, dim3(sms), rs::kThreads, rs::kSmem, s, L);
+  } else if (stages & 6) {
     // geometry the consumer mapping was written for: a tile of rows is one 16-row
     // group, or at most eight (group, super-block) units
     const StreamGeom g = stream_geom(L.H, L.FF);
@@ -991,6 +1111,13 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
 
 #ifdef SGR_PROFILE
 // profiling builds: copy out (and clear) the per-CTA cycle totals [grid][8]
+// the per-stage trace of the last expert_rows_kernel launch: [grid][512] (see expert_rows.cuh)
+extern "C" __attribute__((visibility("default"))) int sgr_trace_read(long long* host_out, int n) {
+  if (g_prof_buf == nullptr) return -1;
+  cudaDeviceSynchronize();
+  cudaMemcpy(host_out, g_prof_buf + 1024 * 16, static_cast<size_t>(n) * sizeof(long long), cudaMemcpyDeviceToHost);
+  return 0;
+}
 extern "C" __attribute__((visibility("default"))) int sgr_prof_read(long long* host_out, int n) {
   if (g_prof_buf == nullptr) return -1;
   cudaDeviceSynchronize();

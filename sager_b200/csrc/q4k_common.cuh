@@ -116,6 +116,7 @@ struct XTile {
   float* d;
   int nb;
   int tok_stride;
+  int d_step;          // floats between the scales of consecutive token rows (nb when packed)
   __device__ __forceinline__ const int8_t* code_ptr(int t, int blk, int sb) const {
     return qs + static_cast<size_t>(t) * tok_stride + blk * kXqStride + sb * 32;
   }
@@ -125,7 +126,7 @@ struct XTile {
   __device__ __forceinline__ uint4 sums(int t, int blk) const {
     return *reinterpret_cast<const uint4*>(bs + (static_cast<size_t>(t) * nb + blk) * 8);
   }
-  __device__ __forceinline__ float scale(int t, int blk) const { return d[t * nb + blk]; }
+  __device__ __forceinline__ float scale(int t, int blk) const { return d[t * d_step + blk]; }
   __device__ __forceinline__ const int8_t* split_sums(int t, int blk) const {
     return bl + (static_cast<size_t>(t) * nb + blk) * 16;
   }
@@ -146,6 +147,7 @@ __host__ __device__ constexpr size_t xtile_bytes(int tt, int nb) {
 __device__ __forceinline__ XTile xtile_at(unsigned char* base, int tt, int nb) {
   XTile x;
   x.nb = nb;
+  x.d_step = nb;
   x.tok_stride = xtile_tok_stride(nb);
   x.qs = reinterpret_cast<int8_t*>(base);
   x.bs = reinterpret_cast<int16_t*>(base + static_cast<size_t>(tt) * x.tok_stride);

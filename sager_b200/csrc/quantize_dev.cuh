@@ -6,8 +6,11 @@
 
 namespace sgr {
 
+// out16 (optional): the same block once more in the padded 288-byte form
+// [d | 12 bytes | 256 codes | 8 int16 sums], every part 16-byte aligned.
 __device__ __forceinline__ void quantize_block_f16(const uint16_t* __restrict__ x,
-                                               unsigned char* __restrict__ out, int lane) {
+                                               unsigned char* __restrict__ out, int lane,
+                                               unsigned char* __restrict__ out16 = nullptr) {
   float v[8];
   if ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
     const uint4 raw = reinterpret_cast<const uint4*>(x)[lane];
@@ -49,6 +52,13 @@ __device__ __forceinline__ void quantize_block_f16(const uint16_t* __restrict__ 
   if ((lane & 7) == 0) {                                      // lanes 0, 8, 16, 24
     o32[65 + (lane >> 3)] = (static_cast<uint32_t>(sum) & 0xFFFFu) |
                             (static_cast<uint32_t>(sum_hi) << 16);
+  }
+  if (out16 != nullptr) {
+    uint32_t* p32 = reinterpret_cast<uint32_t*>(out16);
+    if (lane == 0) p32[0] = __float_as_uint(d);
+    p32[4 + 2 * lane] = o32[1 + 2 * lane];
+    p32[5 + 2 * lane] = o32[2 + 2 * lane];
+    if ((lane & 7) == 0) p32[68 + (lane >> 3)] = o32[65 + (lane >> 3)];
   }
 }
 

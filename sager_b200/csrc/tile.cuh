@@ -296,6 +296,135 @@ __device__ __forceinline__ void warp_mma_rows(const unsigned char* w, int wstrid
   }
 }
 
+// One super-block of sixteen weight rows that need not be adjacent: `a_ptr` is this
+// lane's ldmatrix row address (start of the row's block + 16 + 16 * (lane >> 4)),
+// `h_lo` / `h_hi` the blocks of the rows whose results this lane owns (fragment
+// rows gid and gid + 8). Activations: block 0 of a tile staged with nb == 1 (codes, int16
+// sums and scales; the split sums of the staged layout are not used).
+// Accumulates into acc (same ownership as warp_mma_rows).
+template <int NT>
+__device__ __forceinline__ void warp_mma_block(const unsigned char* a_ptr, const unsigned char* h_lo,
+                                               const unsigned char* h_hi, const XTile& xt,
+                                               float (&acc)[NT][4]) {
+  const int lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int b_tok = lane & 7;
+  const int b_off = (lane >> 3) * 16;
+  const uint4 h0 = *reinterpret_cast<const uint4*>(h_lo);
+  const uint4 h1 = *reinterpret_cast<const uint4*>(h_hi);
+  const float d_lo = 0.0625f * __half2float(__ushort_as_half(static_cast<uint16_t>(h0.x & 0xFFFFu)));
+  const float m_lo = __half2float(__ushort_as_half(static_cast<uint16_t>(h0.x >> 16)));
+  const float d_hi = 0.0625f * __half2float(__ushort_as_half(static_cast<uint16_t>(h1.x & 0xFFFFu)));
+  const float m_hi = __half2float(__ushort_as_half(static_cast<uint16_t>(h1.x >> 16)));
+  const Scales6 s_lo = unpack_scales6(h0.y, h0.z, h0.w);
+  const Scales6 s_hi = unpack_scales6(h1.y, h1.z, h1.w);
+  int isum[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) isum[n][j] = 0;
+  const int zero[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint32_t b[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) ldmatrix_x4(b[n], xt.code_ptr(8 * n + b_tok, 0, 2 * g) + b_off);
+    uint32_t raw[4];
+    ldmatrix_x4(raw, a_ptr + g * 32);
+    uint32_t lo[4], hi[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      lo[j] = raw[j] & 0x0F0F0F0Fu;
+      hi[j] = raw[j] & 0xF0F0F0F0u;               // 16 * q: see warp_mma_rows
+    }
+    const int sh = 16 * (g & 1);
+    const int sc0_lo = ((s_lo.sc[g >> 1] >> sh) & 0xFF) << 4, sc1_lo = (s_lo.sc[g >> 1] >> (sh + 8)) & 0xFF;
+    const int sc0_hi = ((s_hi.sc[g >> 1] >> sh) & 0xFF) << 4, sc1_hi = (s_hi.sc[g >> 1] >> (sh + 8)) & 0xFF;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      int c0[4], c1[4];
+      mma_u8s8(c0, lo, b[n][0], b[n][1], zero);
+      mma_u8s8(c1, hi, b[n][2], b[n][3], zero);
+      isum[n][0] += sc0_lo * c0[0] + sc1_lo * c1[0];
+      isum[n][1] += sc0_lo * c0[1] + sc1_lo * c1[1];
+      isum[n][2] += sc0_hi * c0[2] + sc1_hi * c1[2];
+      isum[n][3] += sc0_hi * c0[3] + sc1_hi * c1[3];
+    }
+  }
+  const uint32_t a_lo = tig == 0 ? s_lo.mn[0] : (tig == 1 ? s_lo.mn[1] : 0u);
+  const uint32_t a_hi = tig == 0 ? s_hi.mn[0] : (tig == 1 ? s_hi.mn[1] : 0u);
+  const uint32_t ma[4] = {a_lo, a_hi, 0u, 0u};
+#pragma unroll
+  for (int n = 0; n < NT; ++n) {
+    // sub-block sums 4*tig .. 4*tig+3 of token 8n+gid, split as bsum = 128*hi + lo
+    // (lo in 0..127, hi in -32..31) straight from the int16 sums
+    uint32_t blo = 0u, bhi = 0u;
+    if (tig < 2) {
+      const uint2 sv = *reinterpret_cast<const uint2*>(xt.bs + static_cast<size_t>(8 * n + gid) * 8 + 4 * tig);
+      blo = __byte_perm(sv.x & 0x007F007Fu, sv.y & 0x007F007Fu, 0x6420);
+      bhi = __byte_perm((sv.x >> 7) & 0x00FF00FFu, (sv.y >> 7) & 0x00FF00FFu, 0x6420);
+    }
+    int dl[4], dh[4];
+    mma_u8s8(dl, ma, blo, 0u, zero);
+    mma_u8s8(dh, ma, bhi, 0u, zero);
+    const float xd0 = xt.scale(8 * n + 2 * tig, 0), xd1 = xt.scale(8 * n + 2 * tig + 1, 0);
+    acc[n][0] += xd0 * (d_lo * static_cast<float>(isum[n][0]) - m_lo * static_cast<float>(dl[0] + 128 * dh[0]));
+    acc[n][1] += xd1 * (d_lo * static_cast<float>(isum[n][1]) - m_lo * static_cast<float>(dl[1] + 128 * dh[1]));
+    acc[n][2] += xd0 * (d_hi * static_cast<float>(isum[n][2]) - m_hi * static_cast<float>(dl[2] + 128 * dh[2]));
+    acc[n][3] += xd1 * (d_hi * static_cast<float>(isum[n][3]) - m_hi * static_cast<float>(dl[3] + 128 * dh[3]));
+  }
+}
+
+// Half a super-block (sub-blocks 4*half .. 4*half+3) of one weight row against up to
+// TT staged tokens (block 0 of a tile staged with nb == 1), for a pair of adjacent
+// lanes that share the row: the integer sums of the two halves are added across
+// the pair before the one fp32 rounding, so the result equals block_dot's.
+template <int TT>
+__device__ __forceinline__ void half_block_dot(const uint4* wrow, int half, const XTile& xt, int nt,
+                                               float (&acc)[TT]) {
+  const uint4 hdr = wrow[0];
+  const float d = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x & 0xFFFFu)));
+  const float dmin = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x >> 16)));
+  const Scales6 s6 = unpack_scales6(hdr.y, hdr.z, hdr.w);
+  const uint32_t scw = half ? s6.sc[1] : s6.sc[0];
+  const uint32_t mnw = half ? s6.mn[1] : s6.mn[0];
+  int isum[TT];
+#pragma unroll
+  for (int t = 0; t < TT; ++t) isum[t] = 0;
+#pragma unroll
+  for (int gg = 0; gg < 2; ++gg) {
+    const int g = 2 * half + gg;
+    const uint4 q0 = wrow[1 + 2 * g], q1 = wrow[2 + 2 * g];
+    const uint32_t raw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    uint32_t lo[8], hi[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      lo[i] = raw[i] & 0x0F0F0F0Fu;
+      hi[i] = (raw[i] >> 4) & 0x0F0F0F0Fu;
+    }
+    const int sc_lo = (scw >> (16 * gg)) & 0xFF, sc_hi = (scw >> (16 * gg + 8)) & 0xFF;
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+      if (t < nt) {
+        const uint4* xa = xt.codes(t, 0, 2 * g);
+        const uint4 x0 = xa[0], x1 = xa[1], x2 = xa[2], x3 = xa[3];
+        isum[t] += sc_lo * dot8(lo, x0, x1) + sc_hi * dot8(hi, x2, x3);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < TT; ++t) {
+    if (t < nt) {                               // nt is warp-uniform: the shuffles stay converged
+      const uint4 bs = xt.sums(t, 0);
+      int msum = __dp2a_lo(static_cast<int>(half ? bs.z : bs.x), static_cast<int>(mnw), 0);
+      msum = __dp2a_hi(static_cast<int>(half ? bs.w : bs.y), static_cast<int>(mnw), msum);
+      const int is = isum[t] + __shfl_xor_sync(0xFFFFFFFFu, isum[t], 1);
+      const int ms = msum + __shfl_xor_sync(0xFFFFFFFFu, msum, 1);
+      acc[t] += xt.scale(t, 0) * (d * static_cast<float>(is) - dmin * static_cast<float>(ms));
+    }
+  }
+}
+
 // Four warps cover the tile: with at least four 16-row groups each warp takes
 // groups w, w+4, ...; with fewer, the warps of a group split the super-blocks and
 // their partial sums meet in shared memory (fixed order, so results are

@@ -21,6 +21,9 @@ def _p(t):
     return None if t is None else C.c_void_p(t.data_ptr())
 
 
+KERNEL_BITS = {None: 0, "rows": 16, "items": 32}
+
+
 class MoeLayerRunner:
     def __init__(self, n_max, hidden, n_ff, n_expert, n_used, device, expert_lo=0, expert_hi=0):
         self.n_max, self.hidden, self.n_ff = n_max, hidden, n_ff
@@ -62,8 +65,10 @@ class MoeLayerRunner:
         a.workspace, a.workspace_bytes = _p(self.ws), self.ws.numel()
         return a
 
-    def run(self, a: MoeLayerArgs):
-        lib().call("sgr_moe_layer_decode", C.byref(a), stream_ptr())
+    def run(self, a: MoeLayerArgs, kernel=None):
+        """kernel: None = the library's choice by row count, "rows" / "items" force the
+        row-streaming or the item expert kernel."""
+        lib().call("sgr_moe_layer_decode_stages", C.byref(a), 7 | KERNEL_BITS[kernel], stream_ptr())
 
 
 class MoeStack:
@@ -76,8 +81,9 @@ class MoeStack:
     activations are still there and single stages can be re-launched (timing)."""
 
     def __init__(self, layers, n_max, n_used, device, biases=None, inputs=None,
-                 per_layer_ws=False):
+                 per_layer_ws=False, kernel=None):
         self.layers = layers
+        self.kernel_bits = KERNEL_BITS[kernel]
         w0 = layers[0]
         self.device = device
         n_ws = len(layers) if per_layer_ws else 1
@@ -106,7 +112,7 @@ class MoeStack:
     def _issue(self, n, stages=7):
         for li in range(len(self.layers)):
             r, a = self.layer_args(li, n)
-            lib().call("sgr_moe_layer_decode_stages", C.byref(a), stages, stream_ptr())
+            lib().call("sgr_moe_layer_decode_stages", C.byref(a), stages | self.kernel_bits, stream_ptr())
 
     def step_eager(self, n):
         self._issue(n)
