@@ -13,12 +13,20 @@
 // in shared memory, no barrier between the warps; the only synchronisation is
 // the full/empty mbarrier pair of each stage.
 //
-// Four weight warps fill a stage with 16-byte asynchronous copies (cp.async; a
-// 144-byte piece per row is too small for a bulk copy to pay: one warp issues
-// roughly one bulk copy per 60 cycles). A fifth producer warp copies the stage's
-// block of the tile's activation rows, also asynchronously. The two roles walk
-// the same list of stages independently, so the weight stream never waits for
-// an activation row that is not ready yet.
+// The weight part of a stage arrives by TMA: two tiled copies per stage (boxes of
+// 144 bytes x 128 rows) through 2-D tensor maps over [rows][row bytes]. The maps
+// are made on the host for a placeholder address; when the weight warp enters a
+// tile it patches the expert's base addresses into shared-memory copies
+// (tensormap.replace), publishes them to a per-CTA ring of descriptors in global
+// memory (tensormap.cp_fenceproxy) and acquires them before use. (16-byte cp.async
+// copies reach the same HBM rate on their own, but every one of them passes through
+// the load/store pipe that the consumers' shared-memory loads need; bulk copies of
+// 144 bytes are issue-bound at roughly one per 60 cycles and warp.) Three more
+// producer warps copy the stage's block of the tile's activation rows with
+// cp.async. The two roles walk the same list of stages independently, so the
+// weight stream never waits for an activation row that is not ready yet. Experts
+// whose pointers are not 16-byte aligned cannot go through TMA: the weight warp
+// copies them with plain loads.
 //
 // Gate/up groups write fp32 h. The last warp of a CTA to finish a group counts
 // the CTA in at the group's 256-wide block of h (global counter); the CTA that
@@ -38,9 +46,13 @@ namespace rs {
 constexpr int kTok = 16;                        // token rows per tile
 constexpr int kConsumerWarps = 16;
 constexpr int kConsumers = kConsumerWarps * 32;
-constexpr int kWeightWarps = 4;
-constexpr int kWeightThreads = kWeightWarps * 32;
-constexpr int kThreads = kConsumers + kWeightThreads + 64;      // + the activation warp and the finisher warp
+constexpr int kXWarps = 3;                      // activation-row producers
+constexpr int kXThreads = kXWarps * 32;
+#ifdef SGR_PROFILE
+constexpr int kThreads = kConsumers + 32 + kXThreads + 32 + 64; // + two observer warps (profiling builds)
+#else
+constexpr int kThreads = kConsumers + 32 + kXThreads + 32;      // consumers, weight warp, activation warps, finisher warp
+#endif
 constexpr int kStageCount = 5;
 constexpr int kHalfRows = 128;                  // a stage is two halves of 128 rows
 constexpr int kHalfBytes = kHalfRows * kW4;     // 18432
@@ -49,27 +61,31 @@ constexpr int kWBytes = 2 * kHalfBytes;
 constexpr int kXCodes = kTok * kXqStride;
 constexpr int kXBytes = kXCodes + kTok * 16 + kTok * 16;
 constexpr int kStageBytes = (kWBytes + kXBytes + 127) & ~127;
-constexpr int kPieces = kHalfBytes / 16 / kWeightThreads;       // 16-byte copies per thread and half: 9
 constexpr int kHq = 288;                        // padded Q8_K block of h: d | 12 bytes | 256 codes | 8 sums
-constexpr int kHdr = 1024;
+constexpr int kHdr = 2048;
 constexpr size_t kSmem = kHdr + static_cast<size_t>(kStageCount) * kStageBytes;
 constexpr int kGateUpPairs = 128;               // pairs per gate/up group
 constexpr int kDownRows = 256;                  // rows per down group
 constexpr int kCombineRows = 64;
-constexpr int kFullArrivals = 2 * (kWeightThreads + 32);        // per producer thread: copies landed + plain stores done
+constexpr int kFullArrivals = 32 + kXThreads;     // weight warp: one arrival per lane; activation warps: copies landed
+constexpr int kMapRing = 4;                      // descriptor slots per CTA and matrix
 
-static_assert(kPieces * kWeightThreads * 16 == kHalfBytes, "pieces must tile a half stage");
 static_assert(kSmem <= 227 * 1024, "ring exceeds shared memory");
 
-struct Desc {
-  int kind;      // 0 gate/up, 1 down
-  int mode;      // 0 weights streamed, 1 expert absent
-  int tile, ntok;
+struct Desc {     // one 16-byte shared-memory load per stage and warp
+  int flags;     // bit 0 kind (0 gate/up, 1 down), bit 1 expert absent, bits 2-7 token rows,
+                 // bits 8-15 block column, bit 16 last column of the group, bit 17 end of this CTA's list,
+                 // bits 20-31 group number in this CTA
+  int tile;
   int hrow0;     // first h / y row of the tile
   int row0;      // first pair (gate/up) or first row (down) of the group
-  int blk, nb;   // block column of this stage, columns per group
-  int e, seq;    // expert id; running number of the group inside this CTA
-  int pad[2];
+  __device__ __forceinline__ int kind() const { return flags & 1; }
+  __device__ __forceinline__ int absent() const { return (flags >> 1) & 1; }
+  __device__ __forceinline__ int ntok() const { return (flags >> 2) & 63; }
+  __device__ __forceinline__ int blk() const { return (flags >> 8) & 255; }
+  __device__ __forceinline__ int last() const { return (flags >> 16) & 1; }
+  __device__ __forceinline__ int end() const { return (flags >> 17) & 1; }     // no more stages for this CTA
+  __device__ __forceinline__ int seq() const { return (flags >> 20) & 4095; }
 };
 
 // A finished gate/up group, handed from the consumers to the finisher warp.
@@ -84,6 +100,22 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 // arrive on `bar` once every cp.async this thread has issued so far has landed
 __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmap_replace_addr(void* smem_map, const void* gaddr) {
+  asm volatile("tensormap.replace.tile.global_address.shared::cta.b1024.b64 [%0], %1;" ::"r"(smem_u32(smem_map)), "l"(gaddr) : "memory");
+}
+// whole warp: copy the patched 128-byte descriptor to global memory for the TMA unit
+__device__ __forceinline__ void tmap_publish(void* gmem_map, void* smem_map) {
+  asm volatile("tensormap.cp_fenceproxy.global.shared::cta.tensormap::generic.release.gpu.sync.aligned [%0], [%1], 128;"
+               ::"l"(gmem_map), "r"(smem_u32(smem_map)) : "memory");
+}
+__device__ __forceinline__ void tmap_acquire(const void* gmem_map) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(gmem_map) : "memory");
+}
+// box (144 bytes x 128 rows) at byte column x, row y; dst 128-byte aligned, x a multiple of 16
+__device__ __forceinline__ void tma_load_box(void* dst, const void* gmem_map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(smem_u32(dst)), "l"(gmem_map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void rs_consumers_sync() {
   asm volatile("bar.sync 5, %0;" ::"n"(kConsumers) : "memory");
@@ -105,25 +137,31 @@ __device__ __forceinline__ void copy16_any(unsigned char* dst, const unsigned ch
   *reinterpret_cast<uint4*>(dst) = make_uint4(v[0], v[1], v[2], v[3]);
 }
 
-// The list of stages of one CTA, walked identically by every role: gate/up groups
-// [gu_lo, gu_lo + gu_cnt) with nbh columns each, then down groups with nbf columns.
-struct Walk {
-  int kind, gid, blk, nb, gpt, tile, gi, seq;
-  int gu_end, dn_lo, nbf, gpt_dn;
-  __device__ __forceinline__ void start(int gu_lo, int gu_cnt, int dn_lo_, int nbh, int nbf_, int gpt_gu, int gpt_dn_) {
-    gu_end = gu_lo + gu_cnt; dn_lo = dn_lo_; nbf = nbf_; gpt_dn = gpt_dn_;
-    seq = 0; blk = 0;
-    if (gu_cnt > 0) { kind = 0; gid = gu_lo; nb = nbh; gpt = gpt_gu; }
-    else { kind = 1; gid = dn_lo; nb = nbf; gpt = gpt_dn; }
-    tile = gid / gpt; gi = gid - tile * gpt;
-  }
-  __device__ __forceinline__ void next() {
-    if (++blk < nb) return;
-    blk = 0; ++gid; ++seq;
-    if (kind == 0 && gid == gu_end) { kind = 1; gid = dn_lo; nb = nbf; gpt = gpt_dn; }
-    tile = gid / gpt; gi = gid - tile * gpt;
+// Groups are handed out dynamically, in one global order: every gate/up group of the
+// layer (tile-major), then every down group. A CTA starts with group blockIdx.x and takes
+// further ones from a global counter; its weight warp draws the next number while it
+// streams the current group and publishes the CTA's list in shared memory for the other
+// roles. Equal finishing times need no cost model this way, and a tile's down groups are
+// drawn long after its gate/up groups were (the whole gate/up list lies between).
+struct Group {
+  int kind, tile, gi, nb;        // 0 gate/up / 1 down, tile, group inside the tile, block columns
+  bool valid;
+};
+struct Sched {
+  int n_gu, total, nbh, nbf, gpt_gu, gpt_dn;
+  __device__ __forceinline__ Group decode(int g) const {
+    Group r;
+    r.valid = g >= 0 && g < total;
+    r.kind = g >= n_gu ? 1 : 0;
+    const int local = r.kind ? g - n_gu : g;
+    const int gpt = r.kind ? gpt_dn : gpt_gu;
+    r.tile = r.valid ? local / gpt : 0;
+    r.gi = local - r.tile * gpt;
+    r.nb = r.kind ? nbf : nbh;
+    return r;
   }
 };
+constexpr int kListSlots = 16;
 
 // One warp: Q8_K-quantise block `hb` of the fp32 h rows [hrow0, hrow0 + ntok) into the
 // padded rows of L.hq (arithmetic of src/kernels/cpu/q4_avx2.cpp:77-94 in the reference,
@@ -193,117 +231,192 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     for (int i = 0; i < 8; ++i) grp_cnt[i] = 0u;
     *done_tail = 0u;
     *done_head = 0u;
+    *reinterpret_cast<volatile unsigned*>(smem + 144) = 0u;
     fence_barrier_init();
   }
   __syncthreads();
   pdl_wait();                       // plan, routing and quantised rows come from the route kernel
   pdl_launch_dependents();
 
-  const int gpt_gu = L.FF / kGateUpPairs, gpt_dn = L.H / kDownRows;      // groups per tile
-  // this CTA's run of gate/up groups and of down groups: equal-cost cuts made by the plan
-  const int gu_lo = L.cta_lo[blockIdx.x], gu_cnt = L.cta_lo[blockIdx.x + 1] - gu_lo;
-  const int dn_lo = L.cta_lo[kMaxGrid + 1 + blockIdx.x], dn_cnt = L.cta_lo[kMaxGrid + 2 + blockIdx.x] - dn_lo;
-  const int n_stage = gu_cnt * L.nbh + dn_cnt * L.nbf;
+  Sched sc;
+  sc.gpt_gu = L.FF / kGateUpPairs; sc.gpt_dn = L.H / kDownRows;      // groups per tile
+  sc.nbh = L.nbh; sc.nbf = L.nbf;
+  sc.n_gu = L.meta[1] * sc.gpt_gu;
+  sc.total = sc.n_gu + L.meta[1] * sc.gpt_dn;
   const int rb_h = L.nbh * kW4, rb_f = L.nbf * kW4;
-  Walk wk;
-  wk.start(gu_lo, gu_cnt, dn_lo, L.nbh, L.nbf, gpt_gu, gpt_dn);
+  volatile int* glist = reinterpret_cast<volatile int*>(smem + 768);           // [kListSlots] this CTA's groups, -1 = end
+  volatile unsigned* g_pub = reinterpret_cast<volatile unsigned*>(smem + 144);  // entries of glist published
+  // a follower role's k-th group (bounded wait for the weight warp to publish it)
+  auto follow = [&](int k, bool& ok) {
+    unsigned it = 0;
+    if (lane == 0)
+      while (*g_pub <= static_cast<unsigned>(k) && ++it < kSpinLimit) __nanosleep(40);
+    it = __shfl_sync(0xFFFFFFFFu, it, 0);
+    ok = it < kSpinLimit;
+    __threadfence_block();
+    return ok ? static_cast<int>(glist[k % kListSlots]) : -1;
+  };
 
-  if (warp >= kConsumerWarps && warp < kConsumerWarps + kWeightWarps) {
-    // ---------------- weight warps ----------------
-    const int ptid = tid - kConsumers;
-    int so_h[kPieces], so_f[kPieces];           // source offsets of this thread's pieces, per row pitch
-#pragma unroll
-    for (int j = 0; j < kPieces; ++j) {
-      const int p = ptid + kWeightThreads * j;
-      const int r = p / 9, c = (p - r * 9) * 16;
-      so_h[j] = r * rb_h + c;
-      so_f[j] = r * rb_f + c;
-    }
-    int cur_tile = -1, cur_gid = -1;
+  if (warp == kConsumerWarps) {
+    // ---------------- weight warp ----------------
+    unsigned char* smaps = smem + 1024;                                 // three 128-byte descriptors being patched
+    unsigned char* gmaps = L.tmaps + static_cast<size_t>(blockIdx.x) * kMapRing * 3 * 128;
+    int cur_tile = -1, tile_seq = 0;
+    int4 rc = make_int4(0, 0, 0, 0);
     const unsigned char *w0 = nullptr, *w1 = nullptr, *w2 = nullptr;
+    const unsigned char* maps = nullptr;                                // this tile's descriptors: gate, up, down
     bool absent = false, aligned = true;
-    for (int q = 0; q < n_stage; ++q, wk.next()) {
-      const int s = q % kStageCount;
-      const unsigned ph = (q / kStageCount) & 1;
+    int drawn = blockIdx.x;                     // the first group is this CTA's own number
+    int q = 0;
+    for (int k = 0;; ++k) {
+      // publish group k of this CTA (or the end of the list) and draw the one after it;
+      // the drawn number is only looked at when this group has been issued
+      const int cur = __shfl_sync(0xFFFFFFFFu, drawn, 0);
+      const Group wk = sc.decode(cur);
+      if (lane == 0) {
+        glist[k % kListSlots] = wk.valid ? cur : -1;
+        __threadfence_block();
+        *g_pub = static_cast<unsigned>(k) + 1u;
+      }
+      if (!wk.valid) {                           // end of the list: one last stage that only says so
+        const int s = q % kStageCount;
+        const unsigned ph = (q / kStageCount) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1u)) {
+          if (lane == 0) atomicExch(L.status, 2);
+          return;
+        }
+        if (lane == 0) {
+          Desc d;
+          d.flags = 1 << 17; d.tile = 0; d.hrow0 = 0; d.row0 = 0;
+          desc[s] = d;
+        }
+        mbar_arrive(&full[s]);
+        return;
+      }
+      if (lane == 0) drawn = static_cast<int>(atomicAdd(&L.cnt[10], 1u));
       if (wk.tile != cur_tile) {
         cur_tile = wk.tile;
-        const int e = __ldcg(&L.rec[wk.tile].x);
-        const bool shared = e == L.E;
-        w0 = shared ? L.sh[0] : L.tab[e];
-        w1 = shared ? L.sh[1] : L.tab[L.E + e];
-        w2 = shared ? L.sh[2] : L.tab[2 * L.E + e];
+        rc = __ldcg(L.rec + wk.tile);
+        const bool shared = rc.x == L.E;
+        w0 = shared ? L.sh[0] : L.tab[rc.x];
+        w1 = shared ? L.sh[1] : L.tab[L.E + rc.x];
+        w2 = shared ? L.sh[2] : L.tab[2 * L.E + rc.x];
         absent = w0 == nullptr || w1 == nullptr || w2 == nullptr;
         aligned = ((reinterpret_cast<uintptr_t>(w0) | reinterpret_cast<uintptr_t>(w1) |
                     reinterpret_cast<uintptr_t>(w2)) & 15u) == 0;
-      }
-      if (SGR_RS_PREFETCH != 0 && wk.gid != cur_gid && !absent && aligned) {
-        // announce the group to L2 as long sequential reads
-        if (wk.kind == 0) {
-          const int bytes = kGateUpPairs * rb_h;
-          const size_t at = static_cast<size_t>(wk.gi) * bytes;
-          for (int o = ptid * 8192; o < 2 * bytes; o += kWeightThreads * 8192) {
-            const int m = o >= bytes ? 1 : 0, oo = o - m * bytes;
-            bulk_prefetch_l2((m ? w1 : w0) + at + oo, static_cast<uint32_t>(min(8192, bytes - oo)));
+        if (!absent && aligned) {
+          // descriptors of this expert's three matrices (the ring keeps the previous
+          // tiles' descriptors intact while their copies are in flight)
+          unsigned char* slot = gmaps + static_cast<size_t>(tile_seq % kMapRing) * 3 * 128;
+          ++tile_seq;
+          if (lane == 0) {
+            uint32_t* m = reinterpret_cast<uint32_t*>(smaps);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {       // constant indices only (see LayerDev)
+              m[i] = L.tmap_gu[i];
+              m[32 + i] = L.tmap_gu[i];
+              m[64 + i] = L.tmap_dn[i];
+            }
+            tmap_replace_addr(smaps, w0);
+            tmap_replace_addr(smaps + 128, w1);
+            tmap_replace_addr(smaps + 256, w2);
           }
-        } else {
-          const int bytes = kDownRows * rb_f;
-          const size_t at = static_cast<size_t>(wk.gi) * bytes;
-          for (int o = ptid * 8192; o < bytes; o += kWeightThreads * 8192)
-            bulk_prefetch_l2(w2 + at + o, static_cast<uint32_t>(min(8192, bytes - o)));
+          __syncwarp();
+          tmap_publish(slot, smaps);
+          tmap_publish(slot + 128, smaps + 128);
+          tmap_publish(slot + 256, smaps + 256);
+          if (lane == 0) {
+            tmap_acquire(slot);
+            tmap_acquire(slot + 128);
+            tmap_acquire(slot + 256);
+          }
+          __syncwarp();
+          maps = slot;
         }
       }
-      cur_gid = wk.gid;
+      for (int blk = 0; blk < wk.nb; ++blk, ++q) {
+      const int s = q % kStageCount;
+      const unsigned ph = (q / kStageCount) & 1;
       if (!mbar_wait(&empty[s], ph ^ 1u)) {
         if (lane == 0) atomicExch(L.status, 2);
         return;
       }
-      if (!absent) {
-        unsigned char* dst = stages + static_cast<size_t>(s) * kStageBytes + ptid * 16;
-        const unsigned char *b0, *b1;
-        if (wk.kind == 0) {
-          b0 = w0 + static_cast<size_t>(wk.gi) * kGateUpPairs * rb_h + wk.blk * kW4;
-          b1 = w1 + static_cast<size_t>(wk.gi) * kGateUpPairs * rb_h + wk.blk * kW4;
-        } else {
-          b0 = w2 + static_cast<size_t>(wk.gi) * kDownRows * rb_f + wk.blk * kW4;
-          b1 = b0 + static_cast<size_t>(kHalfRows) * rb_f;
-        }
-        if (aligned) {
-#pragma unroll
-          for (int j = 0; j < kPieces; ++j) {
-            const int so = wk.kind == 0 ? so_h[j] : so_f[j];
-            cp_async16(dst + j * (kWeightThreads * 16), b0 + so);
-            cp_async16(dst + j * (kWeightThreads * 16) + kHalfBytes, b1 + so);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < kPieces; ++j) {
-            const int so = wk.kind == 0 ? so_h[j] : so_f[j];
-            copy16_any(dst + j * (kWeightThreads * 16), b0 + so);
-            copy16_any(dst + j * (kWeightThreads * 16) + kHalfBytes, b1 + so);
-          }
-        }
+      unsigned char* st = stages + static_cast<size_t>(s) * kStageBytes;
+      if (lane == 0) {
+        Desc d;
+        d.flags = wk.kind | (absent ? 2 : 0) | (rc.y << 2) | (blk << 8) | (blk == wk.nb - 1 ? 1 << 16 : 0) |
+                  ((k & 4095) << 20);
+        d.tile = wk.tile; d.hrow0 = rc.z;
+        d.row0 = wk.gi * (wk.kind == 0 ? kGateUpPairs : kDownRows);
+        desc[s] = d;
       }
-      cp_async_arrive(&full[s]);
-      mbar_arrive(&full[s]);
+      if (!absent && aligned) {
+        if (lane == 0) {
+          mbar_expect_tx(&full[s], kWBytes);      // this lane's arrival, with the bytes to come
+          if (wk.kind == 0) {
+            tma_load_box(st, maps, blk * kW4, wk.gi * kGateUpPairs, &full[s]);
+            tma_load_box(st + kHalfBytes, maps + 128, blk * kW4, wk.gi * kGateUpPairs, &full[s]);
+          } else {
+            tma_load_box(st, maps + 256, blk * kW4, wk.gi * kDownRows, &full[s]);
+            tma_load_box(st + kHalfBytes, maps + 256, blk * kW4, wk.gi * kDownRows + kHalfRows, &full[s]);
+          }
 #ifdef SGR_PROFILE
-      if (ptid == 0 && q < 120) {
-        long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        (L.prof + 1024 * 16 + blockIdx.x * 512)[7 + 4 * q] = t;
-      }
+          if (q < 120) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); (L.prof + 1024 * 16 + blockIdx.x * 512)[7 + 4 * q] = t; }
 #endif
+        } else {
+          mbar_arrive(&full[s]);
+        }
+      } else {
+        if (!absent) {                           // sources without 16-byte alignment: plain loads
+          const unsigned char *b0, *b1;
+          int rb;
+          if (wk.kind == 0) {
+            rb = rb_h;
+            b0 = w0 + static_cast<size_t>(wk.gi) * kGateUpPairs * rb_h + blk * kW4;
+            b1 = w1 + static_cast<size_t>(wk.gi) * kGateUpPairs * rb_h + blk * kW4;
+          } else {
+            rb = rb_f;
+            b0 = w2 + static_cast<size_t>(wk.gi) * kDownRows * rb_f + blk * kW4;
+            b1 = b0 + static_cast<size_t>(kHalfRows) * rb_f;
+          }
+          for (int p = lane; p < kHalfBytes / 16; p += 32) {
+            const int r = p / 9, c = (p - r * 9) * 16;
+            copy16_any(st + p * 16, b0 + static_cast<size_t>(r) * rb + c);
+            copy16_any(st + kHalfBytes + p * 16, b1 + static_cast<size_t>(r) * rb + c);
+          }
+          fence_proxy_async();                   // the next fill of this stage may come from the TMA unit
+        }
+        mbar_arrive(&full[s]);
+      }
+      }   // block columns of the group
     }
-    return;
   }
 
-  if (warp == kConsumerWarps + kWeightWarps) {
-    // ---------------- activation warp ----------------
+  if (warp > kConsumerWarps && warp <= kConsumerWarps + kXWarps) {
+    // ---------------- activation warps ----------------
+    const int xtid = tid - kConsumers - 32;
     int cur_tile = -1, cur_kind = -1;
     int4 rc = make_int4(0, 0, 0, 0);
     bool absent = false;
     int myoff = 0;                              // lane t < 16: byte offset of token slot t's row
-    for (int q = 0; q < n_stage; ++q, wk.next()) {
-      const int s = q % kStageCount;
-      const unsigned ph = (q / kStageCount) & 1;
+    int q = 0;
+    for (int k = 0;; ++k) {
+      bool got;
+      const Group wk = sc.decode(follow(k, got));
+      if (!got) {
+        if (lane == 0) atomicExch(L.status, 7);
+        return;
+      }
+      if (!wk.valid) {                           // end of the list: count in at the last stage and leave
+        const int s = q % kStageCount;
+        const unsigned ph = (q / kStageCount) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1u)) {
+          if (lane == 0) atomicExch(L.status, 2);
+          return;
+        }
+        cp_async_arrive(&full[s]);
+        return;
+      }
       if (wk.tile != cur_tile || wk.kind != cur_kind) {
         if (wk.tile != cur_tile) {
           rc = __ldcg(L.rec + wk.tile);
@@ -335,6 +448,9 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
           }
         }
       }
+      for (int blk = 0; blk < wk.nb; ++blk, ++q) {
+      const int s = q % kStageCount;
+      const unsigned ph = (q / kStageCount) & 1;
       if (!mbar_wait(&empty[s], ph ^ 1u)) {
         if (lane == 0) atomicExch(L.status, 2);
         return;
@@ -342,40 +458,41 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
       unsigned char* xs = stages + static_cast<size_t>(s) * kStageBytes + kWBytes;
       if (!absent) {
         // 288-byte blocks (quantised inputs for gate/up, quantised h for down): 16-byte copies
-        const unsigned char* xsrc = (wk.kind == 0 ? L.xq16 : L.hq) + wk.blk * kHq;
+        const unsigned char* xsrc = (wk.kind == 0 ? L.xq16 : L.hq) + blk * kHq;
         const int total = rc.y * (kHq / 16);
-        for (int base = 0; base < total; base += 32) {
-          const int i = base + lane;
+        for (int base = 0; base < total; base += kXThreads) {      // warp-uniform trip count
+          const int i = base + xtid;
           const bool valid = i < total;
           const int t = valid ? i / (kHq / 16) : 0;
           const int c = i - t * (kHq / 16);
           const int off = __shfl_sync(0xFFFFFFFFu, myoff, t);
           if (valid) {
+            // scale | codes (second half of the block 16 bytes further on: see XTile::mid_pad) | sums
             unsigned char* dst = c == 0 ? xs + kXCodes + kTok * 16 + t * 16
-                                        : (c <= 16 ? xs + t * kXqStride + (c - 1) * 16 : xs + kXCodes + t * 16);
+                                        : (c <= 16 ? xs + t * kXqStride + (c - 1) * 16 + (c > 8 ? 16 : 0)
+                                                   : xs + kXCodes + t * 16);
             cp_async16(dst, xsrc + off + c * 16);
           }
         }
       }
-      if (lane == 0) {
-        Desc d;
-        d.kind = wk.kind; d.mode = absent ? 1 : 0; d.tile = wk.tile; d.ntok = rc.y; d.hrow0 = rc.z;
-        d.row0 = wk.gi * (wk.kind == 0 ? kGateUpPairs : kDownRows); d.blk = wk.blk; d.nb = wk.nb;
-        d.e = rc.x; d.seq = wk.seq; d.pad[0] = d.pad[1] = 0;
-        desc[s] = d;
-      }
       cp_async_arrive(&full[s]);
-      mbar_arrive(&full[s]);
+      }   // block columns of the group
     }
-    return;
   }
 
-  if (warp == kConsumerWarps + kWeightWarps + 1) {
+  if (warp == kConsumerWarps + 1 + kXWarps) {
     // ---------------- finisher warp ----------------
     // Takes the finished gate/up groups of this CTA in order: counts the CTA in at the
     // group's block of h, and if that completes the block, quantises it for the tile's
     // rows and publishes it. The consumers never wait for any of this.
-    for (int g = 0; g < gu_cnt; ++g) {
+    for (int g = 0;; ++g) {
+      bool got;
+      const Group wk = sc.decode(follow(g, got));
+      if (!got) {
+        if (lane == 0) atomicExch(L.status, 7);
+        return;
+      }
+      if (!wk.valid || wk.kind == 1) return;     // a CTA's gate/up groups all come before its down groups
       unsigned it = 0;
       if (lane == 0)
         while (*done_tail <= static_cast<unsigned>(g) && ++it < kSpinLimit) __nanosleep(100);
@@ -404,17 +521,40 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     return;
   }
 
+#ifdef SGR_PROFILE
+  if (warp >= kConsumerWarps + 2 + kXWarps) {
+    // observers: when does each stage become full / free again
+    const bool obs_full = warp == kConsumerWarps + 2 + kXWarps;
+    if (lane == 0) {
+      long long* tr2 = L.prof + 1024 * 16 + 160 * 512 + blockIdx.x * 256;
+      for (int q = 0; q < 120; ++q) {
+        const int s = q % kStageCount;
+        const unsigned ph = (q / kStageCount) & 1;
+        if (!mbar_wait(obs_full ? &full[s] : &empty[s], ph)) break;
+        long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        tr2[2 * q + (obs_full ? 0 : 1)] = t;
+      }
+    }
+    return;
+  }
+#endif
   // ---------------- consumers ----------------
   float acc[2][4];
   bool ok = true;
+#ifdef SGR_TRACE
+  auto gt = []() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
+  long long tl[8] = {0, 0, 0, 0, 0, 0, 0, 0};     // start, first full, gu end, dn start, last done, barrier, end
+  int ncls[3] = {0, 0, 0}, last_kind = 0;
+  if (tid == 0) tl[0] = gt();
+#endif
 #ifdef SGR_PROFILE
   const int _pw = 0;
   long long* trace = L.prof + 1024 * 16 + blockIdx.x * 512;
   auto gtime = []() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
-  if (tid == 0) { trace[0] = gtime(); trace[1] = n_stage; }
+  if (tid == 0) { trace[0] = gtime(); trace[1] = 0; }
 #endif
   PROF_T0();
-  for (int q = 0; q < n_stage; ++q) {
+  for (int q = 0;; ++q) {
     const int s = q % kStageCount;
     const unsigned ph = (q / kStageCount) & 1;
     PROF_ADD(2);
@@ -425,18 +565,28 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     }
     PROF_ADD(0);
     const Desc d = desc[s];
+    if (d.end()) break;
+    const int d_kind = d.kind(), d_mode = d.absent(), d_ntok = d.ntok(), d_blk = d.blk(), d_last = d.last(), d_seq = d.seq();
+#ifdef SGR_TRACE
+    if (tid == 0) {
+      if (q == 0) tl[1] = gt();
+      if (d_kind == 1 && last_kind == 0) tl[3] = gt();
+      last_kind = d_kind;
+      ++ncls[d_ntok <= 2 ? 0 : (d_ntok <= 8 ? 1 : 2)];
+    }
+#endif
 #ifdef SGR_PROFILE
-    if (tid == 0 && q < 120) { trace[4 + 4 * q] = gtime(); trace[6 + 4 * q] = d.kind * 1000 + d.ntok * 10 + (d.blk == 0 ? 1 : 0); }
+    if (tid == 0 && q < 120) { trace[4 + 4 * q] = gtime(); trace[6 + 4 * q] = d_kind * 1000 + d_ntok * 10 + (d_blk == 0 ? 1 : 0); }
 #endif
     unsigned char* st = stages + static_cast<size_t>(s) * kStageBytes;
-    if (d.blk == 0) {
+    if (d_blk == 0) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[0][j] = acc[1][j] = 0.f;
     }
 #ifdef SGR_RS_NOCOMPUTE
     if (false) {
 #else
-    if (d.mode == 0) {
+    if (d_mode == 0) {
 #endif
       XTile xt;
       xt.qs = reinterpret_cast<int8_t*>(st + kWBytes);
@@ -446,64 +596,102 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
       xt.nb = 1;
       xt.tok_stride = kXqStride;
       xt.d_step = 4;
+      xt.mid_pad = 16;
       // unit row u of this warp -> byte offset of its block in the stage
       auto row_at = [&](int u) {
-        return d.kind == 0 ? ((u & 7) + 8 * warp) * kW4 + (u >> 3) * kHalfBytes : (16 * warp + u) * kW4;
+        return d_kind == 0 ? ((u & 7) + 8 * warp) * kW4 + (u >> 3) * kHalfBytes : (16 * warp + u) * kW4;
       };
-      if (d.ntok <= 2) {
+#if defined(SGR_RS_EXP) && SGR_RS_EXP == 1
+      if (true) {                                // experiment: the shared-memory loads of the dp4a path, no math
+        const uint4* wrow = reinterpret_cast<const uint4*>(st + row_at(lane >> 1));
+        const int half = lane & 1;
+        uint4 v = wrow[0];
+        for (int gg = 0; gg < 2; ++gg) {
+          const int g = 2 * half + gg;
+          const uint4 q0 = wrow[1 + 2 * g], q1 = wrow[2 + 2 * g];
+          v.x ^= q0.x ^ q1.y; v.y ^= q0.z ^ q1.w;
+          for (int t = 0; t < 2; ++t) if (t < d_ntok) {
+            const uint4* xa = xt.codes(t, 0, 2 * g);
+            v.z ^= xa[0].x ^ xa[1].y ^ xa[2].z ^ xa[3].w;
+          }
+        }
+        const uint4 bs = xt.sums(0, 0);
+        acc[0][0] += __uint_as_float((v.x ^ v.y ^ v.z ^ v.w ^ bs.x) & 0x3FFFFFFFu);
+      } else if (false) {
+#elif defined(SGR_RS_EXP) && SGR_RS_EXP == 2
+      if (true) {                                // experiment: the math of the dp4a path on register data, no loads
+        uint32_t w = lane * 0x01010101u + q, x = lane * 0x00010203u + s;
+        int i0 = 0, i1 = 0;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          i0 = __dp4a(static_cast<int>(w & 0x0F0F0F0Fu), static_cast<int>(x), i0);
+          i1 = __dp4a(static_cast<int>((w >> 4) & 0x0F0F0F0Fu), static_cast<int>(x ^ 0x55u), i1);
+          w = w * 5u + 1u; x = x * 3u + 7u;
+        }
+        acc[0][0] += static_cast<float>(i0 * 3 + i1 * 5);
+      } else if (false) {
+#else
+      if (d_ntok <= 2) {
+#endif
         float a2[2] = {acc[0][0], acc[0][1]};
-        half_block_dot<2>(reinterpret_cast<const uint4*>(st + row_at(lane >> 1)), lane & 1, xt, d.ntok, a2);
+        half_block_dot<2>(reinterpret_cast<const uint4*>(st + row_at(lane >> 1)), lane & 1, xt, d_ntok, a2);
         acc[0][0] = a2[0];
         acc[0][1] = a2[1];
       } else {
         const unsigned char* a_ptr = st + row_at((lane & 7) + ((lane >> 3) & 1) * 8) + 16 + (lane >> 4) * 16;
         const unsigned char* h_lo = st + row_at(lane >> 2);
         const unsigned char* h_hi = st + row_at((lane >> 2) + 8);
-        if (d.ntok <= 8) warp_mma_block<1>(a_ptr, h_lo, h_hi, xt, reinterpret_cast<float(&)[1][4]>(acc));
+        if (d_ntok <= 8) warp_mma_block<1>(a_ptr, h_lo, h_hi, xt, acc);
         else warp_mma_block<2>(a_ptr, h_lo, h_hi, xt, acc);
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[s]);       // this warp no longer reads the stage
+#ifdef SGR_TRACE
+    if (tid == 0 && d_last && true) { if (d_kind == 0) tl[2] = gt(); else tl[4] = gt(); }
+#endif
 #ifdef SGR_PROFILE
     if (tid == 0 && q < 120) trace[5 + 4 * q] = gtime();
     if (lane == 0 && warp == 0) {
-      const int cls = d.ntok <= 2 ? 0 : (d.ntok <= 8 ? 1 : 2);
+      const int cls = d_ntok <= 2 ? 0 : (d_ntok <= 8 ? 1 : 2);
       atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + blockIdx.x * 16 + 8 + cls), static_cast<unsigned long long>(clock64() - _pt));
       atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + blockIdx.x * 16 + 11 + cls), 1ull);
     }
 #endif
     PROF_ADD(1);
-    if (d.blk != d.nb - 1) continue;
+    if (!d_last) continue;
 
     // ---- the group is complete for this warp's rows ----
     const int gid = lane >> 2, tig = lane & 3;
-    if (d.kind == 0) {
-      if (d.mode == 1) {
-        if (d.row0 == 0 && warp == 0 && lane == 0 && L.mail != nullptr && d.e != L.E) {
-          const int mi = atomicAdd(L.mail_n, 1);
-          if (mi < L.E) L.mail[mi] = d.e;
+    if (d_kind == 0) {
+      if (d_mode == 1) {
+        if (d.row0 == 0 && warp == 0 && lane == 0 && L.mail != nullptr) {
+          const int e = __ldcg(&L.rec[d.tile].x);
+          if (e != L.E) {
+            const int mi = atomicAdd(L.mail_n, 1);
+            if (mi < L.E) L.mail[mi] = e;
+          }
         }
       } else
-      if (d.ntok <= 2) {
+      if (d_ntok <= 2) {
         const float u0 = __shfl_down_sync(0xFFFFFFFFu, acc[0][0], 16);
         const float u1 = __shfl_down_sync(0xFFFFFFFFu, acc[0][1], 16);
         if (lane < 16 && (lane & 1) == 0) {
           const int col = d.row0 + 8 * warp + (lane >> 1);
           const float g0 = acc[0][0], g1 = acc[0][1];
           L.hbuf[static_cast<size_t>(d.hrow0) * L.FF + col] = g0 / (1.f + expf(-g0)) * u0;
-          if (d.ntok > 1) L.hbuf[static_cast<size_t>(d.hrow0 + 1) * L.FF + col] = g1 / (1.f + expf(-g1)) * u1;
+          if (d_ntok > 1) L.hbuf[static_cast<size_t>(d.hrow0 + 1) * L.FF + col] = g1 / (1.f + expf(-g1)) * u1;
         }
       } else {
         const int col = d.row0 + 8 * warp + gid;
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
           const int t0 = 8 * n + 2 * tig;
-          if (t0 < d.ntok) {
+          if (t0 < d_ntok) {
             const float g = acc[n][0], u = acc[n][2];
             L.hbuf[static_cast<size_t>(d.hrow0 + t0) * L.FF + col] = g / (1.f + expf(-g)) * u;
           }
-          if (t0 + 1 < d.ntok) {
+          if (t0 + 1 < d_ntok) {
             const float g = acc[n][1], u = acc[n][3];
             L.hbuf[static_cast<size_t>(d.hrow0 + t0 + 1) * L.FF + col] = g / (1.f + expf(-g)) * u;
           }
@@ -516,43 +704,43 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
       __threadfence_block();
       __syncwarp();
       if (lane == 0) {
-        if (atomicAdd(&grp_cnt[d.seq & 7], 1u) == kConsumerWarps - 1) {
-          grp_cnt[d.seq & 7] = 0u;
+        if (atomicAdd(&grp_cnt[d_seq & 7], 1u) == kConsumerWarps - 1) {
+          grp_cnt[d_seq & 7] = 0u;
           unsigned it = 0;                       // queue full: wait (bounded) for the finisher
-          while (static_cast<unsigned>(d.seq) - *done_head >= static_cast<unsigned>(kDoneSlots) && ++it < kSpinLimit)
+          while (static_cast<unsigned>(d_seq) - *done_head >= static_cast<unsigned>(kDoneSlots) && ++it < kSpinLimit)
             __nanosleep(100);
           if (it >= kSpinLimit) atomicExch(L.status, 6);
           Done r;
-          r.tile = d.tile; r.hb = d.row0 / kQK; r.hrow0 = d.hrow0; r.ntok = d.mode == 1 ? 0 : d.ntok;
-          done_q[d.seq % kDoneSlots] = r;
+          r.tile = d.tile; r.hb = d.row0 / kQK; r.hrow0 = d.hrow0; r.ntok = d_mode == 1 ? 0 : d_ntok;
+          done_q[d_seq % kDoneSlots] = r;
           __threadfence_block();
-          *done_tail = static_cast<unsigned>(d.seq) + 1u;
+          *done_tail = static_cast<unsigned>(d_seq) + 1u;
         }
       }
       PROF_ADD(6);
       PROF_ADD(7);
     } else {
-      if (d.mode == 1) {
-        for (int j = lane; j < 16 * d.ntok; j += 32)
+      if (d_mode == 1) {
+        for (int j = lane; j < 16 * d_ntok; j += 32)
           L.ybuf[static_cast<size_t>(d.hrow0 + j / 16) * L.H + d.row0 + 16 * warp + (j & 15)] = 0.f;
         continue;
       }
-      if (d.ntok <= 2) {
+      if (d_ntok <= 2) {
         if ((lane & 1) == 0) {
           const int col = d.row0 + 16 * warp + (lane >> 1);
           L.ybuf[static_cast<size_t>(d.hrow0) * L.H + col] = acc[0][0];
-          if (d.ntok > 1) L.ybuf[static_cast<size_t>(d.hrow0 + 1) * L.H + col] = acc[0][1];
+          if (d_ntok > 1) L.ybuf[static_cast<size_t>(d.hrow0 + 1) * L.H + col] = acc[0][1];
         }
       } else {
         const int col = d.row0 + 16 * warp + gid;
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
           const int t0 = 8 * n + 2 * tig;
-          if (t0 < d.ntok) {
+          if (t0 < d_ntok) {
             L.ybuf[static_cast<size_t>(d.hrow0 + t0) * L.H + col] = acc[n][0];
             L.ybuf[static_cast<size_t>(d.hrow0 + t0) * L.H + col + 8] = acc[n][2];
           }
-          if (t0 + 1 < d.ntok) {
+          if (t0 + 1 < d_ntok) {
             L.ybuf[static_cast<size_t>(d.hrow0 + t0 + 1) * L.H + col] = acc[n][1];
             L.ybuf[static_cast<size_t>(d.hrow0 + t0 + 1) * L.H + col + 8] = acc[n][3];
           }
@@ -573,6 +761,9 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     flag[0] = (it < kSpinLimit && ok) ? 1 : 0;
   }
   rs_consumers_sync();
+#ifdef SGR_TRACE
+  if (tid == 0) tl[5] = gt();
+#endif
   PROF_ADD(3);
 #ifdef SGR_PROFILE
   if (tid == 0) trace[2] = gtime();
@@ -591,6 +782,14 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
   PROF_ADD(4);
 #ifdef SGR_PROFILE
   if (tid == 0) trace[3] = gtime();
+#endif
+#ifdef SGR_TRACE
+  if (tid == 0) {
+    tl[6] = gt();
+    long long* o = L.prof + blockIdx.x * 16;
+    for (int i = 0; i < 7; ++i) o[i] = tl[i];
+    o[8] = ncls[0]; o[9] = ncls[1]; o[10] = ncls[2]; o[11] = ncls[0] + ncls[1] + ncls[2];
+  }
 #endif
 }
 

@@ -30,7 +30,11 @@
 // Every weight byte is read once, and the weight stream never stops at the
 // gate/up -> down dependency. The route kernel prefetches the router matrix into
 // L2 before it waits for the previous layer.
+#include <cuda.h>
+
 #include <algorithm>
+#include <cstring>
+#include <mutex>
 
 #include "api_util.cuh"
 #include "quantize_dev.cuh"
@@ -43,7 +47,7 @@ namespace {
 
 constexpr int kMaxRows = 64;       // token rows per call (row masks are 64-bit)
 constexpr int kTokTile = 8;        // token rows per tile of the item kernel (one MMA n-tile)
-constexpr int kMaxGrid = 1024;           // most CTAs the expert kernels are launched with
+constexpr int kMaxGrid = 192;            // most CTAs the expert kernels are launched with
 constexpr int kRowsKernelMinRows = 16;   // layers of at least this many token rows run the row-streaming kernel
 constexpr int kRouteTok = 8;       // token rows per CTA of the route kernel
 constexpr int kRouteWarps = 8;
@@ -84,15 +88,20 @@ struct LayerDev {
   int* meta;       // {routed rows, tiles incl. shared, bad ids, routed tiles}
   int* gslot;      // [n*K] grouped slot of a route, -1 = not computed here
   int* grows;      // [n*K] source row of a grouped slot
-  unsigned* cnt;   // [0..7] route tiles, [8] route tiles done, [9] expert kernel grid barrier
+  unsigned* cnt;   // [0..7] route tiles, [8] route tiles done, [9] expert kernel grid barrier, [10] next group
   unsigned* tile_cnt;  // [max_tiles] finished gate/up items per tile
   unsigned* blk_cnt;   // [max_tiles][nbf] row-streaming kernel: warps done with a 256-wide block of h
   unsigned* ready;     // [max_tiles] row-streaming kernel: quantised blocks of h published
   unsigned char* hq;   // [(n_max*K + n_max)][nbf] Q8_K rows of h, 288-byte blocks (row-streaming kernel)
   int tok_tile;        // token rows per tile: 8 (item kernel) or 16 (row-streaming kernel)
   unsigned char* xq16; // [n_max][nbh] the quantised rows once more in 288-byte blocks (row-streaming kernel)
-  int* cta_lo;         // [2][grid + 1] row-streaming kernel: first gate/up and first down group of every CTA
   int grid;            // CTAs of the expert kernel
+  unsigned char* tmaps;   // [grid][4][3][128] row-streaming kernel: patched TMA descriptors
+  // TMA descriptors (placeholder address) of a gate / up matrix and of a down matrix. Only ever
+  // read with constant indices: a dynamic index would make every thread keep a local-memory
+  // copy of the whole argument block.
+  alignas(64) uint32_t tmap_gu[32];
+  alignas(64) uint32_t tmap_dn[32];
   float* hbuf;     // [(n_max*K + n_max)][FF]
   float* ybuf;     // [(n_max*K + n_max)][H]
   int n_max;
@@ -112,7 +121,7 @@ struct LayerDev {
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct WsLayout {
-  size_t xq, logits, off, rec, meta, gslot, grows, cnt, tile_cnt, blk_cnt, ready, hbuf, ybuf, hq, xq16, cta_lo, total;
+  size_t xq, logits, off, rec, meta, gslot, grows, cnt, tile_cnt, blk_cnt, ready, hbuf, ybuf, hq, xq16, tmaps, total;
 };
 inline WsLayout ws_layout(int n_max, int H, int FF, int E, int K) {
   WsLayout l{};
@@ -135,7 +144,7 @@ inline WsLayout ws_layout(int n_max, int H, int FF, int E, int K) {
   l.ybuf = take(rows * H * 4);
   l.hq = take(rows * (FF / kQK) * 288);     // padded Q8_K blocks (rs::kHq)
   l.xq16 = take(static_cast<size_t>(n_max) * (H / kQK) * 288);
-  l.cta_lo = take(2 * (kMaxGrid + 1) * 4);
+  l.tmaps = take(static_cast<size_t>(kMaxGrid) * 4 * 3 * 128);
   l.total = p;
   return l;
 }
@@ -164,52 +173,6 @@ __device__ __forceinline__ void pad_xq_rows(const LayerDev& L, int t0, int nt, i
     const uint32_t v = reinterpret_cast<const uint32_t*>(L.xq_in + static_cast<size_t>(t0 + t) * L.xq_stride + blk * kX8)[w];
     uint32_t* o = reinterpret_cast<uint32_t*>(L.xq16 + (static_cast<size_t>(t0 + t) * L.nbh + blk) * 288);
     o[w == 0 ? 0 : w + 3] = v;
-  }
-}
-
-// Relative time of one stage of the row-streaming kernel for a tile of `ntok` rows
-// (memory-bound below nine rows, bound by the two MMA token groups above).
-#ifndef SGR_RS_COST_SMALL
-#define SGR_RS_COST_SMALL 10
-#define SGR_RS_COST_MID 10
-#define SGR_RS_COST_BIG 13
-#endif
-__device__ __forceinline__ int tile_cost(int ntok) {
-  return ntok <= 2 ? SGR_RS_COST_SMALL : (ntok <= 8 ? SGR_RS_COST_MID : SGR_RS_COST_BIG);
-}
-
-// Row-streaming kernel: cut the tile sequence into L.grid runs of equal cost and store
-// every CTA's first gate/up group and first down group (the same cut for both phases).
-// One CTA, after the tile records are written; scratch: (tiles + 1) ints.
-__device__ void plan_cta_ranges(const LayerDev& L, int* wsum, int n_tiles, int gpt_gu, int gpt_dn) {
-  const int tid = threadIdx.x, nthr = blockDim.x;
-  for (int i = tid; i < n_tiles; i += nthr) wsum[i + 1] = tile_cost(L.rec[i].y);
-  __syncthreads();
-  if (tid == 0) {
-    wsum[0] = 0;
-    for (int i = 0; i < n_tiles; ++i) wsum[i + 1] += wsum[i];
-  }
-  __syncthreads();
-  const long long total = wsum[n_tiles];
-  for (int c = tid; c <= L.grid; c += nthr) {
-    int gu = 0, dn = 0;
-    if (c == L.grid || total == 0) {
-      gu = n_tiles * gpt_gu;
-      dn = n_tiles * gpt_dn;
-      if (c != L.grid) gu = dn = 0;
-    } else {
-      const long long target = total * c / L.grid;
-      int lo = 0, hi = n_tiles;                  // last tile with wsum[tile] <= target
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (wsum[mid] <= target) lo = mid; else hi = mid;
-      }
-      const long long rem = target - wsum[lo], ct = wsum[lo + 1] - wsum[lo];
-      gu = lo * gpt_gu + static_cast<int>((rem * gpt_gu + ct / 2) / ct);
-      dn = lo * gpt_dn + static_cast<int>((rem * gpt_dn + ct / 2) / ct);
-    }
-    L.cta_lo[c] = gu;
-    L.cta_lo[kMaxGrid + 1 + c] = dn;
   }
 }
 
@@ -273,6 +236,7 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
     L.meta[3] = at;
     if (L.mail_n != nullptr) *L.mail_n = 0;
     L.cnt[9] = 0u;                        // grid barrier of the expert kernel
+    L.cnt[10] = static_cast<unsigned>(L.grid);   // row-streaming kernel: next group to hand out
   }
   reset_tile_counters(L, tid, blockDim.x);
   __syncthreads();
@@ -299,16 +263,10 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
     }
     L.gslot[i] = pos;
   }
-  if (L.tok_tile != kTokTile) {
-    __syncthreads();                          // tile records and meta written (same CTA)
-    plan_cta_ranges(L, reinterpret_cast<int*>(smem), L.meta[1], L.FF / 128, L.H / 256);
-  }
 }
 
-// CTAs of <= 256 threads; the second term is the cost prefix of the row-streaming kernel's partition
-inline size_t plan_smem(int E, int n_max, int K) {
-  return std::max(static_cast<size_t>(E) * 8 + 2 * 256 * 4, (static_cast<size_t>(n_max) * K + n_max + 2) * 4);
-}
+// CTAs of <= 256 threads
+inline size_t plan_smem(int E, int, int) { return static_cast<size_t>(E) * 8 + 2 * 256 * 4; }
 
 // ---- launch 1: route ------------------------------------------------------------------
 // grid (ceil(E / 8), ceil(n / 8)), 256 threads. Dynamic smem: max(8 rows of fp16 x,
@@ -919,7 +877,10 @@ __global__ void rearm_kernel(const LayerDev L) {
   pdl_wait();
   pdl_launch_dependents();
   reset_tile_counters(L, threadIdx.x, blockDim.x);
-  if (threadIdx.x == 0) L.cnt[9] = 0u;
+  if (threadIdx.x == 0) {
+    L.cnt[9] = 0u;
+    L.cnt[10] = static_cast<unsigned>(L.grid);
+  }
 }
 
 // x[i] = f16( f32(x[i]) + sum_p parts[p][i] ), p ascending: the home rank's last step of
@@ -936,9 +897,56 @@ __global__ void ep_reduce_add_kernel(uint16_t* __restrict__ x, const float* __re
   }
 }
 
-#ifdef SGR_PROFILE
+#if defined(SGR_PROFILE) || defined(SGR_TRACE)
 long long* g_prof_buf = nullptr;
 #endif
+
+// A 2-D TMA descriptor over a Q4_K matrix seen as bytes, [rows][row_bytes], with boxes of
+// one super-block column (144 bytes) x 128 rows, encoded for a placeholder address: the
+// expert kernel patches the real base address in on the device. Encoded once per
+// geometry (cuTensorMapEncodeTiled, reached through the runtime's driver entry point).
+bool matrix_tmap(int row_bytes, int rows, const void* placeholder, uint32_t* out128) {
+  struct Entry { int row_bytes, rows; unsigned char bytes[128]; };
+  static std::mutex mu;
+  static Entry cache[16];
+  static int n_cache = 0;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < n_cache; ++i)
+    if (cache[i].row_bytes == row_bytes && cache[i].rows == rows) {
+      std::memcpy(out128, cache[i].bytes, 128);
+      return true;
+    }
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  if (encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        fn == nullptr || qres != cudaDriverEntryPointSuccess)
+      return false;
+    encode = reinterpret_cast<EncodeFn>(fn);
+  }
+  CUtensorMap tm;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kW4), 128u};
+  const cuuint32_t estr[2] = {1u, 1u};
+  if (encode(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(placeholder), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  static_assert(sizeof(CUtensorMap) == 128, "descriptor size");
+  std::memcpy(out128, &tm, 128);
+  if (n_cache < 16) {
+    cache[n_cache].row_bytes = row_bytes;
+    cache[n_cache].rows = rows;
+    std::memcpy(cache[n_cache].bytes, &tm, 128);
+    ++n_cache;
+  }
+  return true;
+}
 
 template <typename Kern>
 int launch_pdl(Kern kern, dim3 grid, int threads, size_t smem, cudaStream_t stream,
@@ -1036,7 +1044,7 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   L.ready = reinterpret_cast<unsigned*>(ws + lay.ready);
   L.hq = ws + lay.hq;
   L.xq16 = ws + lay.xq16;
-  L.cta_lo = reinterpret_cast<int*>(ws + lay.cta_lo);
+  L.tmaps = ws + lay.tmaps;
   L.meta = reinterpret_cast<int*>(ws + lay.meta);
   L.gslot = reinterpret_cast<int*>(ws + lay.gslot);
   L.grows = reinterpret_cast<int*>(ws + lay.grows);
@@ -1050,6 +1058,9 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   // kernel; both stages of a split call must be given the same bits).
   const bool use_rows = (stages & 32) ? false : ((stages & 16) ? true : a->n >= kRowsKernelMinRows);
   L.tok_tile = use_rows ? rs::kTok : kTokTile;
+  if (use_rows && (!matrix_tmap(L.nbh * kW4, L.FF, a->workspace, L.tmap_gu) ||
+                   !matrix_tmap(L.nbf * kW4, L.H, a->workspace, L.tmap_dn)))
+    return kErrUnsupported;
   {
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
@@ -1057,10 +1068,10 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
       return kErrLaunch;
     L.grid = std::min(sms, kMaxGrid);
   }
-#ifdef SGR_PROFILE
+#if defined(SGR_PROFILE) || defined(SGR_TRACE)
   if (g_prof_buf == nullptr) {
-    cudaMalloc(&g_prof_buf, (1024 * 16 + 160 * 512) * sizeof(long long));
-    cudaMemset(g_prof_buf, 0, (1024 * 16 + 160 * 512) * sizeof(long long));
+    cudaMalloc(&g_prof_buf, (1024 * 16 + 160 * 512 + 160 * 256) * sizeof(long long));
+    cudaMemset(g_prof_buf, 0, (1024 * 16 + 160 * 512 + 160 * 256) * sizeof(long long));
   }
   L.prof = g_prof_buf;
 #endif
@@ -1109,9 +1120,15 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   return rc;
 }
 
-#ifdef SGR_PROFILE
+#if defined(SGR_PROFILE) || defined(SGR_TRACE)
 // profiling builds: copy out (and clear) the per-CTA cycle totals [grid][8]
 // the per-stage trace of the last expert_rows_kernel launch: [grid][512] (see expert_rows.cuh)
+extern "C" __attribute__((visibility("default"))) int sgr_trace2_read(long long* host_out, int n) {
+  if (g_prof_buf == nullptr) return -1;
+  cudaDeviceSynchronize();
+  cudaMemcpy(host_out, g_prof_buf + 1024 * 16 + 160 * 512, static_cast<size_t>(n) * sizeof(long long), cudaMemcpyDeviceToHost);
+  return 0;
+}
 extern "C" __attribute__((visibility("default"))) int sgr_trace_read(long long* host_out, int n) {
   if (g_prof_buf == nullptr) return -1;
   cudaDeviceSynchronize();

@@ -117,8 +117,11 @@ struct XTile {
   int nb;
   int tok_stride;
   int d_step;          // floats between the scales of consecutive token rows (nb when packed)
+  int mid_pad;         // bytes between the codes of sub-blocks 3 and 4 of a block (0, or 16 when the
+                       // block's own padding sits in the middle: lanes that read sub-blocks s and
+                       // s + 4 of one row at once then hit different banks)
   __device__ __forceinline__ const int8_t* code_ptr(int t, int blk, int sb) const {
-    return qs + static_cast<size_t>(t) * tok_stride + blk * kXqStride + sb * 32;
+    return qs + static_cast<size_t>(t) * tok_stride + blk * kXqStride + sb * 32 + (sb >> 2) * mid_pad;
   }
   __device__ __forceinline__ const uint4* codes(int t, int blk, int sb) const {
     return reinterpret_cast<const uint4*>(code_ptr(t, blk, sb));
@@ -148,6 +151,7 @@ __device__ __forceinline__ XTile xtile_at(unsigned char* base, int tt, int nb) {
   XTile x;
   x.nb = nb;
   x.d_step = nb;
+  x.mid_pad = 0;
   x.tok_stride = xtile_tok_stride(nb);
   x.qs = reinterpret_cast<int8_t*>(base);
   x.bs = reinterpret_cast<int16_t*>(base + static_cast<size_t>(tt) * x.tok_stride);

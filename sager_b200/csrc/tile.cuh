@@ -302,10 +302,11 @@ __device__ __forceinline__ void warp_mma_rows(const unsigned char* w, int wstrid
 // rows gid and gid + 8). Activations: block 0 of a tile staged with nb == 1 (codes, int16
 // sums and scales; the split sums of the staged layout are not used).
 // Accumulates into acc (same ownership as warp_mma_rows).
-template <int NT>
+template <int NT, int NACC>
 __device__ __forceinline__ void warp_mma_block(const unsigned char* a_ptr, const unsigned char* h_lo,
                                                const unsigned char* h_hi, const XTile& xt,
-                                               float (&acc)[NT][4]) {
+                                               float (&acc)[NACC][4]) {
+  static_assert(NT <= NACC, "accumulator rows");
   const int lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
   const int b_tok = lane & 7;
