@@ -50,7 +50,7 @@ constexpr int kTokTile = 8;        // token rows per tile of the item kernel (on
 constexpr int kMaxGrid = 192;            // most CTAs the expert kernels are launched with
 constexpr int kRowsKernelMinRows = 16;   // layers of at least this many token rows run the row-streaming kernel
 constexpr int kRouteTok = 8;       // token rows per CTA of the route kernel
-constexpr int kRouteWarps = 8;
+constexpr int kRouteWarps = 16;
 
 constexpr int kTeams = 2;                         // consumer teams, items alternate between them
 constexpr int kTeamWarps = 8;
@@ -150,11 +150,17 @@ inline WsLayout ws_layout(int n_max, int H, int FF, int E, int K) {
 }
 
 // ---- plan ------------------------------------------------------------------------
-// One CTA (at most 256 threads). Row sets per expert are 64-bit masks, so the slot of a
+// One CTA. Row sets per expert are 64-bit masks, so the slot of a
 // route inside its expert is a popcount: the plan is deterministic (ascending
 // row order) and needs no sort. Routes to experts outside [e_lo, e_hi) are left
 // to their owner (gslot = -1); ids outside [0, E) silence their row as in
 // moe_dispatch_scan (moe.cu:385-398 of the reference).
+__device__ __forceinline__ unsigned atom_add_acq_rel(unsigned* p, unsigned v) {
+  unsigned old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+
 __device__ __forceinline__ void reset_tile_counters(const LayerDev& L, int tid, int nthr) {
   const int tiles = L.n_max * L.K + L.n_max;
   for (int i = tid; i < tiles; i += nthr) {
@@ -178,8 +184,9 @@ __device__ __forceinline__ void pad_xq_rows(const LayerDev& L, int t0, int nt, i
 
 __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   unsigned long long* mask = reinterpret_cast<unsigned long long*>(smem);       // [E]
-  int* scan_rows = reinterpret_cast<int*>(smem + static_cast<size_t>(L.E) * 8);   // [256]
-  int* scan_tiles = scan_rows + 256;                                              // [256]
+  int* scan_rows = reinterpret_cast<int*>(smem + static_cast<size_t>(L.E) * 8);   // [65] warp totals, prefixes, total
+  int* scan_tiles = scan_rows + 128;                                              // [65]
+  int* off_sh = scan_rows + 256;                                                  // [E] copy of L.off for the last pass
   __shared__ int bad_sh;
   const int tid = threadIdx.x;
   const int total = L.n * L.K;
@@ -187,9 +194,11 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   if (tid == 0) bad_sh = 0;
   for (int e = tid; e < L.E; e += blockDim.x) mask[e] = 0ull;
   __syncthreads();
+  int my_e = 0;                               // this thread's first route, kept for the last pass
   for (int i = tid; i < total; i += blockDim.x) {
     const int r = i / L.K, kk = i - r * L.K;
     const int e = __ldcg(L.idx + static_cast<size_t>(r) * L.rstride + kk);
+    if (i == tid) my_e = e;
     if (e < 0 || e >= L.E) {
       for (int q = 0; q <= L.K; ++q) L.w[static_cast<size_t>(r) * L.rstride + q] = 0.f;
       atomicAdd(&bad_sh, 1);
@@ -207,18 +216,35 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
     rows += c;
     tiles += (c + TT - 1) / TT;
   }
-  scan_rows[tid] = rows;
-  scan_tiles[tid] = tiles;
-  __syncthreads();
-  if (tid == 0) {
-    int ar = 0, at = 0;
-    for (int i = 0; i < static_cast<int>(blockDim.x); ++i) {
-      const int r = scan_rows[i], t = scan_tiles[i];
-      scan_rows[i] = ar;
-      scan_tiles[i] = at;
-      ar += r;
-      at += t;
+  // exclusive scan over the threads: inside the warps with shuffles, across the warps by warp 0
+  {
+    const int lane = tid & 31, wp = tid >> 5, nw = (blockDim.x + 31) >> 5;
+    int ir = rows, it = tiles;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int ur = __shfl_up_sync(0xFFFFFFFFu, ir, off), ut = __shfl_up_sync(0xFFFFFFFFu, it, off);
+      if (lane >= off) { ir += ur; it += ut; }
     }
+    if (lane == 31) { scan_rows[wp] = ir; scan_tiles[wp] = it; }
+    __syncthreads();
+    if (wp == 0) {
+      int wr = lane < nw ? scan_rows[lane] : 0, wt = lane < nw ? scan_tiles[lane] : 0;
+      const int own_r = wr, own_t = wt;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int ur = __shfl_up_sync(0xFFFFFFFFu, wr, off), ut = __shfl_up_sync(0xFFFFFFFFu, wt, off);
+        if (lane >= off) { wr += ur; wt += ut; }
+      }
+      scan_rows[32 + lane] = wr - own_r;          // exclusive prefix of the warps
+      scan_tiles[32 + lane] = wt - own_t;
+      if (lane == 31) { scan_rows[64] = wr; scan_tiles[64] = wt; }
+    }
+    __syncthreads();
+    rows = scan_rows[32 + wp] + ir - rows;        // this thread's exclusive prefixes
+    tiles = scan_tiles[32 + wp] + it - tiles;
+  }
+  if (tid == 0) {
+    const int ar = scan_rows[64], at = scan_tiles[64];
     // shared expert: tiles over the rows [sh_lo, sh_hi), appended after the routed ones
     int sh_tiles = 0;
     if (L.sh[0] != nullptr && L.sh_hi > L.sh_lo) {
@@ -241,10 +267,11 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   reset_tile_counters(L, tid, blockDim.x);
   __syncthreads();
   {
-    int ar = scan_rows[tid], at = scan_tiles[tid];
+    int ar = rows, at = tiles;
     for (int e = e0; e < e1; ++e) {
       const int c = __popcll(mask[e]);
       L.off[e] = ar;
+      off_sh[e] = ar;
       for (int t0 = 0; t0 < c; t0 += TT) {
         L.rec[at] = make_int4(e, min(TT, c - t0), ar + t0, ar + t0);
         ++at;
@@ -255,22 +282,63 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   __syncthreads();
   for (int i = tid; i < total; i += blockDim.x) {
     const int r = i / L.K, kk = i - r * L.K;
-    const int e = __ldcg(L.idx + static_cast<size_t>(r) * L.rstride + kk);
+    const int e = i == tid ? my_e : __ldcg(L.idx + static_cast<size_t>(r) * L.rstride + kk);
     int pos = -1;
     if (e >= L.e_lo && e < L.e_hi && e >= 0 && e < L.E) {
-      pos = L.off[e] + __popcll(mask[e] & ((1ull << r) - 1ull));
+      pos = off_sh[e] + __popcll(mask[e] & ((1ull << r) - 1ull));
       L.grows[pos] = r;
     }
     L.gslot[i] = pos;
   }
 }
 
-// CTAs of <= 256 threads
-inline size_t plan_smem(int E, int, int) { return static_cast<size_t>(E) * 8 + 2 * 256 * 4; }
+inline size_t plan_smem(int E, int, int) { return static_cast<size_t>(E) * 12 + 2 * 128 * 4; }
 
 // ---- launch 1: route ------------------------------------------------------------------
-// grid (ceil(E / 8), ceil(n / 8)), 256 threads. Dynamic smem: max(8 rows of fp16 x,
-// 8*E floats for the selection, plan scratch).
+// grid (ceil(E / 16), ceil(n / 8)), 512 threads: a CTA computes the logits of sixteen
+// experts (one per warp) for a tile of up to eight token rows. The tile's activations are
+// staged in shared memory k-major (fp16), so that a lane's values of one k for all rows
+// of the tile are one vector load. Dynamic smem: max(H * 8 halves, the selection's 8 * E
+// floats, plan scratch).
+template <int NT>
+__device__ __forceinline__ void route_tile_logits(const LayerDev& L, uint16_t* xs, int tok0, int nt, int row,
+                                                   int warp, int lane, const float (&pre)[kRouterPre]) {
+  // stage: lane = one k of a 32-wide chunk, all rows of the tile (rows beyond nt read as
+  // zero); four chunks per pass, so that all loads of a pass are in flight together
+  for (int c0 = warp; c0 < L.H / 32; c0 += 4 * kRouteWarps) {
+    uint16_t raw[4][NT];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int k = (c0 + u * kRouteWarps) * 32 + lane;
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+        raw[u][t] = (t < nt && k < L.H) ? L.xn[static_cast<size_t>(tok0 + t) * L.H + k] : static_cast<uint16_t>(0);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int k = (c0 + u * kRouteWarps) * 32 + lane;
+      if (k >= L.H) continue;
+      uint16_t* xp = xs + static_cast<size_t>(k) * NT;
+      auto pack = [&](int t) { return static_cast<uint32_t>(raw[u][t % NT]) | (static_cast<uint32_t>(raw[u][(t + 1) % NT]) << 16); };
+      if (NT == 8) *reinterpret_cast<uint4*>(xp) = make_uint4(pack(0), pack(2), pack(4), pack(6));
+      else if (NT == 4) *reinterpret_cast<uint2*>(xp) = make_uint2(pack(0), pack(2));
+      else if (NT == 2) *reinterpret_cast<uint32_t*>(xp) = pack(0);
+      else xp[0] = raw[u][0];
+    }
+  }
+  __syncthreads();
+  if (row < L.E) {
+    float out[NT];
+    router_row_dot_kmajor<NT>(L.router_w + static_cast<size_t>(row) * L.H, pre, xs, L.H, lane, out);
+    if (lane == 0) {
+      const float b = L.bias != nullptr ? L.bias[row] : 0.f;
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+        if (t < nt) L.logits[static_cast<size_t>(tok0 + t) * L.E + row] = out[t] + b;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev L) {
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ int last_sh;
@@ -280,12 +348,13 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
   const int nt = min(kRouteTok, L.n - tok0);
   const int row = blockIdx.x * kRouteWarps + warp;
 
-  // The router matrix does not depend on the previous layer: pull this warp's row
-  // towards L2 while the previous kernel drains.
-  if (row < L.E && blockIdx.y == 0) {
-    const char* wr = reinterpret_cast<const char*>(L.router_w + static_cast<size_t>(row) * L.H);
-    for (int b = lane * 128; b < L.H * 4; b += 32 * 128)
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(wr + b));
+  // this warp's router row does not depend on the previous layer: its first 2048 weights
+  // are in registers before the wait for that layer ends
+  float pre[kRouterPre];
+  {
+    const float* wrow = L.router_w + static_cast<size_t>(min(row, L.E - 1)) * L.H;
+#pragma unroll
+    for (int j = 0; j < kRouterPre; ++j) pre[j] = lane + j * 32 < L.H ? __ldg(wrow + lane + j * 32) : 0.f;
   }
   pdl_wait();
   pdl_launch_dependents();
@@ -293,72 +362,105 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
   const int _pw = 0;
 #endif
   PROF_T0();
+#ifdef SGR_TRACE
+  auto gt = []() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
+  long long* rt = L.prof + 4096 + (blockIdx.y * gridDim.x + blockIdx.x) * 8;
+  if (tid == 0) rt[0] = gt();
+#endif
 
-  for (int i = tid; i < nt * L.H / 8; i += blockDim.x)
-    reinterpret_cast<uint4*>(xs)[i] =
-        reinterpret_cast<const uint4*>(L.xn + static_cast<size_t>(tok0) * L.H)[i];
-  __syncthreads();
-
+  // Q8_K rows of the tile (packed, and padded for the row-streaming kernel): block
+  // b of the tile goes to warp b / gridDim.x of CTA b % gridDim.x
   if (L.xq_in != nullptr) {
     if (blockIdx.x == 0 && L.tok_tile != kTokTile) pad_xq_rows(L, tok0, nt, tid, blockDim.x);
   } else {
-    for (int b = blockIdx.x * kRouteWarps + warp; b < nt * L.nbh; b += gridDim.x * kRouteWarps) {
+    const int b = warp * gridDim.x + blockIdx.x;
+    if (b < nt * L.nbh) {
       const int t = b / L.nbh, blk = b - t * L.nbh;
-      quantize_block_f16(xs + static_cast<size_t>(t) * L.H + blk * kQK,
+      quantize_block_f16(L.xn + static_cast<size_t>(tok0 + t) * L.H + blk * kQK,
+                         L.xq + static_cast<size_t>(tok0 + t) * L.xq_stride + blk * kX8, lane,
+                         L.tok_tile == kTokTile ? nullptr
+                                                : L.xq16 + (static_cast<size_t>(tok0 + t) * L.nbh + blk) * 288);
+    }
+    // more blocks than warps in the tile's CTAs (small expert counts): the rest in a loop
+    for (int b2 = b + kRouteWarps * gridDim.x; b2 < nt * L.nbh; b2 += kRouteWarps * gridDim.x) {
+      const int t = b2 / L.nbh, blk = b2 - t * L.nbh;
+      quantize_block_f16(L.xn + static_cast<size_t>(tok0 + t) * L.H + blk * kQK,
                          L.xq + static_cast<size_t>(tok0 + t) * L.xq_stride + blk * kX8, lane,
                          L.tok_tile == kTokTile ? nullptr
                                                 : L.xq16 + (static_cast<size_t>(tok0 + t) * L.nbh + blk) * 288);
     }
   }
-  if (row < L.E) {
-    float out[kRouteTok];
-    router_row_dot<kRouteTok>(L.router_w + static_cast<size_t>(row) * L.H, xs, L.H, nt, lane, out);
-    if (lane == 0) {
-      const float b = L.bias != nullptr ? L.bias[row] : 0.f;
-#pragma unroll
-      for (int t = 0; t < kRouteTok; ++t)
-        if (t < nt) L.logits[static_cast<size_t>(tok0 + t) * L.E + row] = out[t] + b;
-    }
-  }
-  // last CTA of this token tile selects
-  __threadfence();
+  if (nt > 4) route_tile_logits<8>(L, xs, tok0, nt, row, warp, lane, pre);
+  else if (nt > 2) route_tile_logits<4>(L, xs, tok0, nt, row, warp, lane, pre);
+  else if (nt > 1) route_tile_logits<2>(L, xs, tok0, nt, row, warp, lane, pre);
+  else route_tile_logits<1>(L, xs, tok0, nt, row, warp, lane, pre);
+#ifdef SGR_TRACE
+  if (tid == 0) rt[1] = gt();
+#endif
+  // last CTA of this token tile selects (the counter's release covers the logits of all
+  // warps, which the barrier ordered before it; its acquire covers the reads that follow)
   __syncthreads();
-  if (tid == 0) last_sh = atomicAdd(&L.cnt[blockIdx.y], 1u) == gridDim.x - 1 ? 1 : 0;
+#ifdef SGR_TRACE
+  if (tid == 0) rt[2] = gt();
+#endif
+  if (tid == 0) last_sh = atom_add_acq_rel(&L.cnt[blockIdx.y], 1u) == gridDim.x - 1 ? 1 : 0;
   __syncthreads();
   if (!last_sh) return;
-  __threadfence();
+#ifdef SGR_TRACE
+  if (tid == 0) rt[3] = gt();
+#endif
 #ifdef SGR_PROFILE
   if (tid == 0) atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + 11), static_cast<unsigned long long>(clock64() - _pt));
   _pt = clock64();
 #endif
-  float* prob = reinterpret_cast<float*>(smem) + static_cast<size_t>(warp) * L.E;
+  float* prob = reinterpret_cast<float*>(smem) + static_cast<size_t>(warp % kRouteTok) * L.E;
+#ifdef SGR_TRACE
+  if (tid == 0) (L.prof + 8192 + blockIdx.y * 8)[6] = clock64();
+#endif
   for (int t = warp; t < nt; t += kRouteWarps) {
     for (int i = lane; i < L.E; i += 32) prob[i] = __ldcg(L.logits + static_cast<size_t>(tok0 + t) * L.E + i);
     __syncwarp();
+#ifdef SGR_TRACE
+    long long* stamps = warp == 0 ? L.prof + 8192 + blockIdx.y * 8 : nullptr;
+    if (warp == 0 && lane == 0) stamps[7] = clock64();
+    router_select_warp(prob, L.E, L.K, L.idx + static_cast<size_t>(tok0 + t) * L.rstride,
+                       L.w + static_cast<size_t>(tok0 + t) * L.rstride, L.shared_w, true, lane, stamps);
+    if (warp == 0 && lane == 0) stamps[5] = clock64();
+#else
     router_select_warp(prob, L.E, L.K, L.idx + static_cast<size_t>(tok0 + t) * L.rstride,
                        L.w + static_cast<size_t>(tok0 + t) * L.rstride, L.shared_w, true, lane);
+#endif
     __syncwarp();
   }
+#ifdef SGR_TRACE
+  __syncthreads();
+  if (tid == 0) rt[4] = gt();
+#endif
   if (L.skip_plan) return;
   // last token tile plans
-  __threadfence();
   __syncthreads();
   if (tid == 0) {
     L.cnt[blockIdx.y] = 0u;
-    last_sh = atomicAdd(&L.cnt[8], 1u) == gridDim.y - 1 ? 1 : 0;
+    last_sh = atom_add_acq_rel(&L.cnt[8], 1u) == gridDim.y - 1 ? 1 : 0;
   }
   __syncthreads();
   if (!last_sh) return;
-  __threadfence();
   if (tid == 0) L.cnt[8] = 0u;
 #ifdef SGR_PROFILE
   if (tid == 0) atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + 12), static_cast<unsigned long long>(clock64() - _pt));
   _pt = clock64();
 #endif
+#ifdef SGR_TRACE
+  if (tid == 0) rt[5] = gt();
+#endif
   build_plan(L, smem);
 #ifdef SGR_PROFILE
   __syncthreads();
   if (tid == 0) atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + 13), static_cast<unsigned long long>(clock64() - _pt));
+#endif
+#ifdef SGR_TRACE
+  __syncthreads();
+  if (tid == 0) rt[6] = gt();
 #endif
 }
 
@@ -1082,8 +1184,9 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
     // plan, xq and routing are taken from the workspace as a previous call left them
   } else if (!a->routing_given) {
     const size_t smem = std::max<size_t>(
-        std::max<size_t>(static_cast<size_t>(kRouteTok) * L.H * 2, static_cast<size_t>(kRouteWarps) * L.E * 4),
+        std::max<size_t>(static_cast<size_t>(kRouteTok) * L.H * 2, static_cast<size_t>(kRouteTok) * L.E * 4),
         plan_smem(L.E, L.n_max, L.K));
+    if (smem > 200 * 1024) return kErrUnsupported;
     rc = launch_pdl(route_kernel, dim3((L.E + kRouteWarps - 1) / kRouteWarps, (L.n + kRouteTok - 1) / kRouteTok),
                     kRouteWarps * 32, smem, s, L);
   } else {

@@ -56,17 +56,151 @@ __device__ __forceinline__ void router_row_dot(const float* __restrict__ wrow,
   }
 }
 
+// One k of the dot below: NT activations (fp16, k-major: xs[k * NT + t]) against one weight.
+template <int NT>
+__device__ __forceinline__ void router_fma_k(float wv, const uint16_t* __restrict__ xp, float (&acc)[NT]) {
+  auto lo = [](uint32_t w) { return __half2float(__ushort_as_half(static_cast<uint16_t>(w & 0xFFFFu))); };
+  auto hi = [](uint32_t w) { return __half2float(__ushort_as_half(static_cast<uint16_t>(w >> 16))); };
+  if (NT == 8) {
+    const uint4 a = *reinterpret_cast<const uint4*>(xp);
+    acc[0] = fmaf(wv, lo(a.x), acc[0]); acc[1 % NT] = fmaf(wv, hi(a.x), acc[1 % NT]);
+    acc[2 % NT] = fmaf(wv, lo(a.y), acc[2 % NT]); acc[3 % NT] = fmaf(wv, hi(a.y), acc[3 % NT]);
+    acc[4 % NT] = fmaf(wv, lo(a.z), acc[4 % NT]); acc[5 % NT] = fmaf(wv, hi(a.z), acc[5 % NT]);
+    acc[6 % NT] = fmaf(wv, lo(a.w), acc[6 % NT]); acc[7 % NT] = fmaf(wv, hi(a.w), acc[7 % NT]);
+  } else if (NT == 4) {
+    const uint2 a = *reinterpret_cast<const uint2*>(xp);
+    acc[0] = fmaf(wv, lo(a.x), acc[0]); acc[1 % NT] = fmaf(wv, hi(a.x), acc[1 % NT]);
+    acc[2 % NT] = fmaf(wv, lo(a.y), acc[2 % NT]); acc[3 % NT] = fmaf(wv, hi(a.y), acc[3 % NT]);
+  } else if (NT == 2) {
+    const uint32_t a = *reinterpret_cast<const uint32_t*>(xp);
+    acc[0] = fmaf(wv, lo(a), acc[0]); acc[1 % NT] = fmaf(wv, hi(a), acc[1 % NT]);
+  } else {
+    acc[0] = fmaf(wv, __half2float(__ushort_as_half(xp[0])), acc[0]);
+  }
+}
+
+// The router dot for NT token rows whose activations sit in shared memory as fp16,
+// k-major. The first `kPre` weights of the lane (k = lane, lane + 32, ...) were loaded
+// by the caller - before it had to wait for the activations - the rest is loaded here.
+// The FMAs of a (lane, token) chain run in the same order as in router_row_dot, so the
+// logits are bit-identical.
+constexpr int kRouterPre = 64;
+template <int NT>
+__device__ __forceinline__ void router_row_dot_kmajor(const float* __restrict__ wrow, const float (&pre)[kRouterPre],
+                                                      const uint16_t* __restrict__ xs, int k, int lane,
+                                                      float (&out)[NT]) {
+  float acc[NT];
+#pragma unroll
+  for (int t = 0; t < NT; ++t) acc[t] = 0.f;
+#pragma unroll
+  for (int j = 0; j < kRouterPre; ++j)
+    if (lane + j * 32 < k) router_fma_k<NT>(pre[j], xs + static_cast<size_t>(lane + j * 32) * NT, acc);
+  int i = lane + kRouterPre * 32;
+  for (; i + 7 * 32 < k; i += 8 * 32) {
+    float wv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wv[j] = __ldg(wrow + i + j * 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) router_fma_k<NT>(wv[j], xs + static_cast<size_t>(i + j * 32) * NT, acc);
+  }
+  for (; i < k; i += 32) router_fma_k<NT>(__ldg(wrow + i), xs + static_cast<size_t>(i) * NT, acc);
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    float a = acc[t];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) a += __shfl_down_sync(0xFFFFFFFFu, a, off);
+    out[t] = a;
+  }
+}
+
 // Softmax + top-k of one row by one warp. `prob` is n_expert floats of shared
 // memory that already hold the logits; it is overwritten.
 __device__ __forceinline__ void router_select_warp(float* prob, int n_expert, int k, int* out_idx,
                                                    float* out_w, float shared_w, bool write_shared,
-                                                   int lane) {
+                                                   int lane, long long* stamps = nullptr) {
+#ifdef SGR_TRACE
+#define SEL_STAMP(i) do { if (stamps != nullptr && lane == 0) stamps[i] = clock64(); } while (0)
+#else
+#define SEL_STAMP(i) do {} while (0)
+#endif
+  SEL_STAMP(0);
+  if (n_expert <= 256 && k <= 32) {
+    // Up to 256 experts: a lane keeps its eight values (experts lane, lane + 32, ...) in
+    // registers from the logits to the picks. Same arithmetic as the general path below.
+    float pr[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) pr[j] = lane + 32 * j < n_expert ? prob[lane + 32 * j] : -1e30f;
+    float mx = -1e30f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, pr[j]);
+    {                                            // warp maximum through an order-preserving integer key
+      const int b = __float_as_int(mx);
+      const int key = b ^ ((b >> 31) & 0x7FFFFFFF);
+      const int mk = __reduce_max_sync(0xFFFFFFFFu, key);
+      mx = __int_as_float(mk ^ ((mk >> 31) & 0x7FFFFFFF));
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      pr[j] = expf(pr[j] - mx);
+      if (lane + 32 * j < n_expert) prob[lane + 32 * j] = pr[j];
+    }
+    __syncwarp();
+    SEL_STAMP(1);
+    float z = 0.f;
+    if (lane == 0) {                             // strictly in index order, loads ahead of the adds
+      int i = 0;
+#pragma unroll 4
+      for (; i + 8 <= n_expert; i += 8) {
+        const float4 a = *reinterpret_cast<const float4*>(prob + i), b = *reinterpret_cast<const float4*>(prob + i + 4);
+        z += a.x; z += a.y; z += a.z; z += a.w; z += b.x; z += b.y; z += b.z; z += b.w;
+      }
+      for (; i < n_expert; ++i) z += prob[i];
+    }
+    z = __shfl_sync(0xFFFFFFFFu, z, 0);
+    SEL_STAMP(2);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float p = pr[j] / z;
+      pr[j] = (lane + 32 * j < n_expert && p == p) ? p : -1.f;     // absent or NaN: never picked
+    }
+    SEL_STAMP(3);
+    float wsum = 0.f, my_w = 0.f;
+    int my_i = 0;
+    for (int kk = 0; kk < k; ++kk) {
+      // this lane's best (lowest j on ties), then the warp's: largest value, lowest index
+      float bv = pr[0];
+      int bj = 0;
+#pragma unroll
+      for (int j = 1; j < 8; ++j)
+        if (pr[j] > bv) { bv = pr[j]; bj = j; }
+      const int vmax = __reduce_max_sync(0xFFFFFFFFu, __float_as_int(bv));      // values are >= 0 or -1
+      const int cand = __float_as_int(bv) == vmax ? lane + 32 * bj : 0x7FFFFFFF;
+      int bi = __reduce_min_sync(0xFFFFFFFFu, cand);
+      float best = __int_as_float(vmax);
+      if (best < 0.f) bi = kk % n_expert;          // nothing valid: deterministic filler
+      if ((bi & 31) == lane && best >= 0.f) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j == (bi >> 5)) pr[j] = -1.f;
+      }
+      wsum += best;
+      if (lane == kk) { my_w = best; my_i = bi; }
+    }
+    SEL_STAMP(4);
+    if (lane < k) {
+      out_idx[lane] = my_i;
+      out_w[lane] = wsum > 0.f ? my_w / wsum : my_w;
+    }
+    if (lane == 0 && write_shared) out_w[k] = shared_w;
+    return;
+  }
   float mx = -1e30f;
   for (int i = lane; i < n_expert; i += 32) mx = fmaxf(mx, prob[i]);
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
   for (int i = lane; i < n_expert; i += 32) prob[i] = expf(prob[i] - mx);
   __syncwarp();
+  SEL_STAMP(1);
   float z = 0.f;
   if (lane == 0) {
     int i = 0;
@@ -80,8 +214,10 @@ __device__ __forceinline__ void router_select_warp(float* prob, int n_expert, in
     for (; i < n_expert; ++i) z += prob[i];
   }
   z = __shfl_sync(0xFFFFFFFFu, z, 0);
+  SEL_STAMP(2);
   for (int i = lane; i < n_expert; i += 32) prob[i] = prob[i] / z;
   __syncwarp();
+  SEL_STAMP(3);
 
   // Every lane learns each pick (butterfly reduction); lane kk keeps pick kk in
   // registers, so the results reach global memory once, in parallel, already
@@ -136,6 +272,7 @@ __device__ __forceinline__ void router_select_warp(float* prob, int n_expert, in
     }
     __syncwarp();
   }
+  SEL_STAMP(4);
   if (k <= 32) {
     if (lane < k) {
       out_idx[lane] = my_i;
