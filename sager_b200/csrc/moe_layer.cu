@@ -50,7 +50,8 @@ constexpr int kTokTile = 8;        // token rows per tile of the item kernel (on
 constexpr int kMaxGrid = 192;            // most CTAs the expert kernels are launched with
 constexpr int kRowsKernelMinRows = 16;   // layers of at least this many token rows run the row-streaming kernel
 constexpr int kRouteTok = 8;       // token rows per CTA of the route kernel
-constexpr int kRouteWarps = 16;
+constexpr int kRouteWarps = 8;
+constexpr int kRouteRows = 2 * kRouteWarps;   // experts per CTA of the route kernel: two rows per warp
 
 constexpr int kTeams = 2;                         // consumer teams, items alternate between them
 constexpr int kTeamWarps = 8;
@@ -122,6 +123,7 @@ __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a -
 
 struct WsLayout {
   size_t xq, logits, off, rec, meta, gslot, grows, cnt, tile_cnt, blk_cnt, ready, hbuf, ybuf, hq, xq16, tmaps, total;
+  size_t items_total;   // what the item kernel needs: everything up to and including ybuf
 };
 inline WsLayout ws_layout(int n_max, int H, int FF, int E, int K) {
   WsLayout l{};
@@ -142,6 +144,7 @@ inline WsLayout ws_layout(int n_max, int H, int FF, int E, int K) {
   l.ready = take(tiles * 4);
   l.hbuf = take(rows * FF * 4);
   l.ybuf = take(rows * H * 4);
+  l.items_total = p;
   l.hq = take(rows * (FF / kQK) * 288);     // padded Q8_K blocks (rs::kHq)
   l.xq16 = take(static_cast<size_t>(n_max) * (H / kQK) * 288);
   l.tmaps = take(static_cast<size_t>(kMaxGrid) * 4 * 3 * 128);
@@ -295,14 +298,14 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
 inline size_t plan_smem(int E, int, int) { return static_cast<size_t>(E) * 12 + 2 * 128 * 4; }
 
 // ---- launch 1: route ------------------------------------------------------------------
-// grid (ceil(E / 16), ceil(n / 8)), 512 threads: a CTA computes the logits of sixteen
-// experts (one per warp) for a tile of up to eight token rows. The tile's activations are
-// staged in shared memory k-major (fp16), so that a lane's values of one k for all rows
-// of the tile are one vector load. Dynamic smem: max(H * 8 halves, the selection's 8 * E
-// floats, plan scratch).
+// grid (ceil(E / 16), ceil(n / 8)), 256 threads: a CTA computes the logits of sixteen
+// experts (two per warp) for a tile of up to eight token rows. The tile's activations are
+// staged in shared memory as fp32, k-major (see router_rows2_dot_kmajor), so that a
+// lane's values of one k for four rows are one vector load that serves both expert rows.
+// Dynamic smem: H * (8 + 16) floats (activations, router rows; the selection and the plan reuse it).
 template <int NT>
-__device__ __forceinline__ void route_tile_logits(const LayerDev& L, uint16_t* xs, int tok0, int nt, int row,
-                                                   int warp, int lane, const float (&pre)[kRouterPre]) {
+__device__ __forceinline__ void route_tile_logits(const LayerDev& L, float* xs, const float* ws, int tok0, int nt,
+                                                   int row0, int warp, int lane) {
   // stage: lane = one k of a 32-wide chunk, all rows of the tile (rows beyond nt read as
   // zero); four chunks per pass, so that all loads of a pass are in flight together
   for (int c0 = warp; c0 < L.H / 32; c0 += 4 * kRouteWarps) {
@@ -318,23 +321,36 @@ __device__ __forceinline__ void route_tile_logits(const LayerDev& L, uint16_t* x
     for (int u = 0; u < 4; ++u) {
       const int k = (c0 + u * kRouteWarps) * 32 + lane;
       if (k >= L.H) continue;
-      uint16_t* xp = xs + static_cast<size_t>(k) * NT;
-      auto pack = [&](int t) { return static_cast<uint32_t>(raw[u][t % NT]) | (static_cast<uint32_t>(raw[u][(t + 1) % NT]) << 16); };
-      if (NT == 8) *reinterpret_cast<uint4*>(xp) = make_uint4(pack(0), pack(2), pack(4), pack(6));
-      else if (NT == 4) *reinterpret_cast<uint2*>(xp) = make_uint2(pack(0), pack(2));
-      else if (NT == 2) *reinterpret_cast<uint32_t*>(xp) = pack(0);
-      else xp[0] = raw[u][0];
+      if (NT >= 4) {
+#pragma unroll
+        for (int p = 0; p < NT / 4; ++p)
+          *reinterpret_cast<float4*>(xs + static_cast<size_t>(p) * 4 * L.H + static_cast<size_t>(k) * 4) =
+              make_float4(h2f(raw[u][(4 * p) % NT]), h2f(raw[u][(4 * p + 1) % NT]), h2f(raw[u][(4 * p + 2) % NT]),
+                          h2f(raw[u][(4 * p + 3) % NT]));
+      } else if (NT == 2) {
+        *reinterpret_cast<float2*>(xs + static_cast<size_t>(k) * 2) = make_float2(h2f(raw[u][0]), h2f(raw[u][1 % NT]));
+      } else {
+        xs[k] = h2f(raw[u][0]);
+      }
     }
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");     // this warp's two router rows have landed
   __syncthreads();
-  if (row < L.E) {
-    float out[NT];
-    router_row_dot_kmajor<NT>(L.router_w + static_cast<size_t>(row) * L.H, pre, xs, L.H, lane, out);
-    if (lane == 0) {
-      const float b = L.bias != nullptr ? L.bias[row] : 0.f;
+#ifdef SGR_TRACE
+  if (threadIdx.x == 0) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); (L.prof + 4096 + (blockIdx.y * gridDim.x + blockIdx.x) * 8)[7] = t; }
+#endif
+  float out[2][NT];
+  router_rows2_dot_kmajor<NT>(ws + static_cast<size_t>(2 * warp) * L.H, ws + static_cast<size_t>(2 * warp + 1) * L.H, xs,
+                              L.H, lane, out);
+  if (lane == 0) {
 #pragma unroll
-      for (int t = 0; t < NT; ++t)
-        if (t < nt) L.logits[static_cast<size_t>(tok0 + t) * L.E + row] = out[t] + b;
+    for (int r = 0; r < 2; ++r) {
+      if (row0 + r < L.E) {
+        const float b = L.bias != nullptr ? L.bias[row0 + r] : 0.f;
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+          if (t < nt) L.logits[static_cast<size_t>(tok0 + t) * L.E + row0 + r] = out[r][t] + b;
+      }
     }
   }
 }
@@ -342,19 +358,31 @@ __device__ __forceinline__ void route_tile_logits(const LayerDev& L, uint16_t* x
 __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev L) {
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ int last_sh;
-  uint16_t* xs = reinterpret_cast<uint16_t*>(smem);
+  float* xs = reinterpret_cast<float*>(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tok0 = blockIdx.y * kRouteTok;
   const int nt = min(kRouteTok, L.n - tok0);
-  const int row = blockIdx.x * kRouteWarps + warp;
+  const int row0 = blockIdx.x * kRouteRows + 2 * warp;
 
-  // this warp's router row does not depend on the previous layer: its first 2048 weights
-  // are in registers before the wait for that layer ends
-  float pre[kRouterPre];
+  // this warp's two router rows do not depend on the previous layer: they are on their
+  // way into shared memory (asynchronous copies) before the wait for that layer ends
+  float* ws = xs + static_cast<size_t>(kRouteTok) * L.H;              // [16 rows][H]
   {
-    const float* wrow = L.router_w + static_cast<size_t>(min(row, L.E - 1)) * L.H;
-#pragma unroll
-    for (int j = 0; j < kRouterPre; ++j) pre[j] = lane + j * 32 < L.H ? __ldg(wrow + lane + j * 32) : 0.f;
+    const float* w0 = L.router_w + static_cast<size_t>(min(row0, L.E - 1)) * L.H;
+    const float* w1 = L.router_w + static_cast<size_t>(min(row0 + 1, L.E - 1)) * L.H;
+    float* d0 = ws + static_cast<size_t>(2 * warp) * L.H;
+    float* d1 = d0 + L.H;
+    if ((reinterpret_cast<uintptr_t>(L.router_w) & 15u) == 0) {
+      for (int c = lane * 4; c < L.H; c += 128) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(d0 + c)), "l"(w0 + c) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(d1 + c)), "l"(w1 + c) : "memory");
+      }
+    } else {
+      for (int c = lane; c < L.H; c += 32) {
+        d0[c] = __ldg(w0 + c);
+        d1[c] = __ldg(w1 + c);
+      }
+    }
   }
   pdl_wait();
   pdl_launch_dependents();
@@ -390,10 +418,14 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
                                                 : L.xq16 + (static_cast<size_t>(tok0 + t) * L.nbh + blk) * 288);
     }
   }
-  if (nt > 4) route_tile_logits<8>(L, xs, tok0, nt, row, warp, lane, pre);
-  else if (nt > 2) route_tile_logits<4>(L, xs, tok0, nt, row, warp, lane, pre);
-  else if (nt > 1) route_tile_logits<2>(L, xs, tok0, nt, row, warp, lane, pre);
-  else route_tile_logits<1>(L, xs, tok0, nt, row, warp, lane, pre);
+#ifdef SGR_TRACE
+  __syncthreads();
+  if (tid == 0) rt[5] = gt();      // quantised (slot reused by the plan stamp in the planning CTA only)
+#endif
+  if (nt > 4) route_tile_logits<8>(L, xs, ws, tok0, nt, row0, warp, lane);
+  else if (nt > 2) route_tile_logits<4>(L, xs, ws, tok0, nt, row0, warp, lane);
+  else if (nt > 1) route_tile_logits<2>(L, xs, ws, tok0, nt, row0, warp, lane);
+  else route_tile_logits<1>(L, xs, ws, tok0, nt, row0, warp, lane);
 #ifdef SGR_TRACE
   if (tid == 0) rt[1] = gt();
 #endif
@@ -1053,7 +1085,7 @@ bool matrix_tmap(int row_bytes, int rows, const void* placeholder, uint32_t* out
 template <typename Kern>
 int launch_pdl(Kern kern, dim3 grid, int threads, size_t smem, cudaStream_t stream,
                const LayerDev& L) {
-  if (smem > 48 * 1024 &&
+  if (smem > 32 * 1024 &&     // (static shared memory counts towards the 48 KB default limit)
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return kErrLaunch;
   cudaLaunchConfig_t cfg{};
@@ -1100,7 +1132,6 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   if (a->routing_given && !a->xq_in && !a->xn) return kErrArg;
   if (a->mail && !a->mail_n) return kErrArg;
   const WsLayout lay = ws_layout(a->n_max, a->hidden, a->n_ff, a->n_expert, a->n_used);
-  if (a->workspace_bytes < lay.total) return kErrArg;
   if ((reinterpret_cast<uintptr_t>(a->workspace) & 255u) ||
       (a->xn && (reinterpret_cast<uintptr_t>(a->xn) & 15u)) ||
       (a->xq_in && (reinterpret_cast<uintptr_t>(a->xq_in) & 3u)))
@@ -1160,6 +1191,7 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   // kernel; both stages of a split call must be given the same bits).
   const bool use_rows = (stages & 32) ? false : ((stages & 16) ? true : a->n >= kRowsKernelMinRows);
   L.tok_tile = use_rows ? rs::kTok : kTokTile;
+  if (a->workspace_bytes < (use_rows ? lay.total : lay.items_total)) return kErrArg;
   if (use_rows && (!matrix_tmap(L.nbh * kW4, L.FF, a->workspace, L.tmap_gu) ||
                    !matrix_tmap(L.nbf * kW4, L.H, a->workspace, L.tmap_dn)))
     return kErrUnsupported;
@@ -1184,10 +1216,10 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
     // plan, xq and routing are taken from the workspace as a previous call left them
   } else if (!a->routing_given) {
     const size_t smem = std::max<size_t>(
-        std::max<size_t>(static_cast<size_t>(kRouteTok) * L.H * 2, static_cast<size_t>(kRouteTok) * L.E * 4),
+        std::max<size_t>(static_cast<size_t>(kRouteTok + kRouteRows) * L.H * 4, static_cast<size_t>(kRouteTok) * L.E * 4),
         plan_smem(L.E, L.n_max, L.K));
     if (smem > 200 * 1024) return kErrUnsupported;
-    rc = launch_pdl(route_kernel, dim3((L.E + kRouteWarps - 1) / kRouteWarps, (L.n + kRouteTok - 1) / kRouteTok),
+    rc = launch_pdl(route_kernel, dim3((L.E + kRouteRows - 1) / kRouteRows, (L.n + kRouteTok - 1) / kRouteTok),
                     kRouteWarps * 32, smem, s, L);
   } else {
     if (!a->xq_in) return kErrArg;
@@ -1282,7 +1314,9 @@ SGR_API int sgr_moe_layer_decode_static(const sgr_moe_layer* a, void* stream) {
       a->n_used <= 0 || a->n_max < a->n || a->n_max > kMaxRows)
     return kErrGeometry;
   const WsLayout lay = ws_layout(a->n_max, a->hidden, a->n_ff, a->n_expert, a->n_used);
-  if (lay.total > kStaticWsBytes) return kErrStaticLimit;   // the shape needs more scratch than the array holds
+  // the shape needs more scratch than the array holds (layers of 16 or more rows also need the
+  // row-streaming kernel's regions)
+  if ((a->n >= kRowsKernelMinRows ? lay.total : lay.items_total) > kStaticWsBytes) return kErrStaticLimit;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) return kErrLaunch;
   if (g_static_ws_addr[dev] == nullptr) {

@@ -56,61 +56,56 @@ __device__ __forceinline__ void router_row_dot(const float* __restrict__ wrow,
   }
 }
 
-// One k of the dot below: NT activations (fp16, k-major: xs[k * NT + t]) against one weight.
+// The router dot of two expert rows (one warp) against NT token rows, everything in shared
+// memory as fp32: the rows' weights as they lie in global memory, the activations k-major
+// in planes of four token rows, xs[(t / 4) * 4 * k + kk * 4 + t % 4] (NT = 1, 2:
+// xs[kk * NT + t]). A lane's activations of one k are one 16-byte load per plane and serve
+// both rows. The loop is kept small on purpose: it runs once per CTA, and long unrolled
+// code would spend its time in instruction fetch. The FMAs of a (row, lane, token) chain
+// run in the same order as in router_row_dot, so the logits are bit-identical.
 template <int NT>
-__device__ __forceinline__ void router_fma_k(float wv, const uint16_t* __restrict__ xp, float (&acc)[NT]) {
-  auto lo = [](uint32_t w) { return __half2float(__ushort_as_half(static_cast<uint16_t>(w & 0xFFFFu))); };
-  auto hi = [](uint32_t w) { return __half2float(__ushort_as_half(static_cast<uint16_t>(w >> 16))); };
-  if (NT == 8) {
-    const uint4 a = *reinterpret_cast<const uint4*>(xp);
-    acc[0] = fmaf(wv, lo(a.x), acc[0]); acc[1 % NT] = fmaf(wv, hi(a.x), acc[1 % NT]);
-    acc[2 % NT] = fmaf(wv, lo(a.y), acc[2 % NT]); acc[3 % NT] = fmaf(wv, hi(a.y), acc[3 % NT]);
-    acc[4 % NT] = fmaf(wv, lo(a.z), acc[4 % NT]); acc[5 % NT] = fmaf(wv, hi(a.z), acc[5 % NT]);
-    acc[6 % NT] = fmaf(wv, lo(a.w), acc[6 % NT]); acc[7 % NT] = fmaf(wv, hi(a.w), acc[7 % NT]);
-  } else if (NT == 4) {
-    const uint2 a = *reinterpret_cast<const uint2*>(xp);
-    acc[0] = fmaf(wv, lo(a.x), acc[0]); acc[1 % NT] = fmaf(wv, hi(a.x), acc[1 % NT]);
-    acc[2 % NT] = fmaf(wv, lo(a.y), acc[2 % NT]); acc[3 % NT] = fmaf(wv, hi(a.y), acc[3 % NT]);
+__device__ __forceinline__ void router_fma_k2(float w0, float w1, const float* __restrict__ xs, int k, int kk,
+                                              float (&acc)[2][NT]) {
+  if (NT >= 4) {
+#pragma unroll
+    for (int p = 0; p < NT / 4; ++p) {
+      const float4 a = *reinterpret_cast<const float4*>(xs + static_cast<size_t>(p) * 4 * k + static_cast<size_t>(kk) * 4);
+      const float v[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        acc[0][(4 * p + t) % NT] = fmaf(w0, v[t], acc[0][(4 * p + t) % NT]);
+        acc[1][(4 * p + t) % NT] = fmaf(w1, v[t], acc[1][(4 * p + t) % NT]);
+      }
+    }
   } else if (NT == 2) {
-    const uint32_t a = *reinterpret_cast<const uint32_t*>(xp);
-    acc[0] = fmaf(wv, lo(a), acc[0]); acc[1 % NT] = fmaf(wv, hi(a), acc[1 % NT]);
+    const float2 a = *reinterpret_cast<const float2*>(xs + static_cast<size_t>(kk) * 2);
+    acc[0][0] = fmaf(w0, a.x, acc[0][0]); acc[0][1 % NT] = fmaf(w0, a.y, acc[0][1 % NT]);
+    acc[1][0] = fmaf(w1, a.x, acc[1][0]); acc[1][1 % NT] = fmaf(w1, a.y, acc[1][1 % NT]);
   } else {
-    acc[0] = fmaf(wv, __half2float(__ushort_as_half(xp[0])), acc[0]);
+    const float a = xs[kk];
+    acc[0][0] = fmaf(w0, a, acc[0][0]);
+    acc[1][0] = fmaf(w1, a, acc[1][0]);
   }
 }
 
-// The router dot for NT token rows whose activations sit in shared memory as fp16,
-// k-major. The first `kPre` weights of the lane (k = lane, lane + 32, ...) were loaded
-// by the caller - before it had to wait for the activations - the rest is loaded here.
-// The FMAs of a (lane, token) chain run in the same order as in router_row_dot, so the
-// logits are bit-identical.
-constexpr int kRouterPre = 64;
 template <int NT>
-__device__ __forceinline__ void router_row_dot_kmajor(const float* __restrict__ wrow, const float (&pre)[kRouterPre],
-                                                      const uint16_t* __restrict__ xs, int k, int lane,
-                                                      float (&out)[NT]) {
-  float acc[NT];
+__device__ __forceinline__ void router_rows2_dot_kmajor(const float* __restrict__ w0s, const float* __restrict__ w1s,
+                                                        const float* __restrict__ xs, int k, int lane,
+                                                        float (&out)[2][NT]) {
+  float acc[2][NT];
 #pragma unroll
-  for (int t = 0; t < NT; ++t) acc[t] = 0.f;
+  for (int t = 0; t < NT; ++t) acc[0][t] = acc[1][t] = 0.f;
+#pragma unroll 4
+  for (int kk = lane; kk < k; kk += 32) router_fma_k2<NT>(w0s[kk], w1s[kk], xs, k, kk, acc);
 #pragma unroll
-  for (int j = 0; j < kRouterPre; ++j)
-    if (lane + j * 32 < k) router_fma_k<NT>(pre[j], xs + static_cast<size_t>(lane + j * 32) * NT, acc);
-  int i = lane + kRouterPre * 32;
-  for (; i + 7 * 32 < k; i += 8 * 32) {
-    float wv[8];
+  for (int r = 0; r < 2; ++r)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) wv[j] = __ldg(wrow + i + j * 32);
+    for (int t = 0; t < NT; ++t) {
+      float a = acc[r][t];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) router_fma_k<NT>(wv[j], xs + static_cast<size_t>(i + j * 32) * NT, acc);
-  }
-  for (; i < k; i += 32) router_fma_k<NT>(__ldg(wrow + i), xs + static_cast<size_t>(i) * NT, acc);
-#pragma unroll
-  for (int t = 0; t < NT; ++t) {
-    float a = acc[t];
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) a += __shfl_down_sync(0xFFFFFFFFu, a, off);
-    out[t] = a;
-  }
+      for (int off = 16; off > 0; off >>= 1) a += __shfl_down_sync(0xFFFFFFFFu, a, off);
+      out[r][t] = a;
+    }
 }
 
 // Softmax + top-k of one row by one warp. `prob` is n_expert floats of shared
