@@ -474,9 +474,14 @@ def main():
         stage_ms[name] = s0.elapsed_time(s1) / reps
     peak, peak_kind = load_peaks()
     ex_gbs = ex_bytes / (stage_ms["experts"] * 1e-3) / 1e9
-    roofline = {"kernel": "expert_stream_kernel", "bound": "hbm", "achieved": ex_gbs, "peak": peak,
+    kernel = "expert_rows_kernel" if n >= 16 else "expert_stream_kernel"
+    # DRAM traffic per launch: one ncu capture of this kernel on the 4-layer stack read 295.3 MB and
+    # wrote 6.1 MB for 284.4 MB of algorithmic bytes (profiles/); scaled by the bytes of this run's launches
+    traffic = (295.3e6 + 6.1e6) / 284.44e6 * (ex_bytes / LAYERS) if n >= 16 else None
+    roofline = {"kernel": kernel, "bound": "hbm", "achieved": ex_gbs, "peak": peak,
                 "unit": "GB/s", "frac": ex_gbs / peak, "peak_source": f"{peak_kind} copy bandwidth (burst)",
-                "traffic": None,
+                "traffic": traffic,
+                "traffic_source": "ncu dram__bytes_read+write of a 4-layer capture, scaled by algorithmic bytes",
                 "bytes_per_launch": ex_bytes / LAYERS, "us_per_launch": stage_ms["experts"] * 1e3 / LAYERS,
                 "stage_ms_per_step": stage_ms,
                 "step": {"algorithmic_bytes": step_bytes, "gbs": step_bytes / (ms_step * 1e-3) / 1e9,
