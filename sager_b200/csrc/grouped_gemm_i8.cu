@@ -10,18 +10,25 @@
 // path, not against the fp16 one.
 //
 // A CTA owns 128 weight rows of one expert and walks that expert's token rows in
-// chunks of up to 64. For every super-block (256 weights):
-//   * each thread (= one weight row) unpacks its 144-byte block and writes two
-//     int8 operand tiles per 32-weight sub-block: the product sc*q (< 1024) split
-//     as 128*hi + lo, so that the 6-bit scale rides through the MMA and the whole
-//     block accumulates exactly in int32 (|sum| <= 256*127*127);
-//   * the activation codes of the chunk are laid out as the B operand; the min
-//     term sum_s mn[s]*bsum[s] is one more pair of MMAs (min bytes as A, the
-//     sub-block sums split the same way as B);
-//   * one elected thread issues the 18 MMAs (M=128, N=chunk, K=32) into four
-//     accumulators in tensor memory and commits them to an mbarrier;
-//   * the four warps read their 32 lanes back (tcgen05.ld) and fold
-//     xd*(d*(128*hi+lo) - dmin*(128*mhi+mlo)) into per-token fp32 registers.
+// chunks of up to 64, two chunks per pass. The work of a pass is a list of jobs
+// (super-block, chunk); job j uses accumulator set j & 1 in tensor memory and is
+// finished by epilogue group j & 1, so with one chunk the two groups take alternate
+// super-blocks and with two chunks each group owns a chunk. Four roles run as a
+// pipeline over mbarriers:
+//   * unpack warps (one thread per weight row): the 144-byte block becomes seventeen
+//     int8 operand tiles per super-block. The 6-bit scale rides through the MMA: with
+//     sc = 8a + b the products b*q and a*q (<= 105) are two u8 tiles per sub-block, so a
+//     whole block accumulates exactly in int32 as D_b + 8*D_a; the eight min bytes are
+//     one more tile. Double-buffered.
+//   * stager warps: the activation codes of the job's chunk, copied asynchronously
+//     into the B tiles (three buffers in flight), the sub-block sums split as
+//     128*hi + lo into two more tiles (for the min term), the fp32 scales aside.
+//   * one elected thread issues the 18 MMAs of a job (M=128, N=chunk, K=32,
+//     tcgen05.mma kind::i8) and commits them to the barriers that release the
+//     accumulators to the epilogue and the operand buffers to their producers.
+//   * epilogue warps read their 32 lanes back (tcgen05.ld) and fold
+//     xd*(d*(D_b + 8*D_a) - dmin*(mlo + 128*mhi)) into per-token fp32 registers while the
+//     next job's MMAs run.
 // Operand tiles use the canonical K-major layout without swizzle: 8 rows x 16 bytes
 // per core matrix, the two K halves 128 bytes apart, 8-row groups 256 bytes apart.
 // Every wait is bounded; on expiry the CTA raises the status word, frees its tensor
@@ -36,14 +43,26 @@ constexpr int kGemmRows = 128;     // weight rows per CTA = MMA M
 constexpr int kGemmTok = 64;       // token rows per chunk = max MMA N
 constexpr int kTileA = kGemmRows * 32;            // bytes of one A tile (128 x 32 int8)
 constexpr int kTileB = kGemmTok * 32;             // bytes of one B tile (64 x 32 int8)
-constexpr int kTmemCols = 256;                    // four accumulators of 64 columns
+constexpr int kATiles = 17;                       // 8 sub-blocks x {b*q, a*q} + the min tile
+constexpr int kBTiles = 10;                       // 8 code tiles + 2 split-sum tiles
+constexpr int kABufs = 2, kBBufs = 3, kDdRing = 4, kXdRing = 6;
+constexpr int kTmemCols = 512;                    // two sets of four 64-column accumulators
+
+constexpr int kEpiWarps = 8, kUnpackWarps = 4, kStageWarps = 2;
+constexpr int kWarpUnpack0 = kEpiWarps, kWarpCtrl = kEpiWarps + kUnpackWarps, kWarpStage0 = kWarpCtrl + 1;
+constexpr int kGemmThreads = (kEpiWarps + kUnpackWarps + 1 + kStageWarps) * 32;    // 480
 
 // shared-memory map (bytes)
-constexpr int kOffBar = 0;                        // mbarrier + tmem base
-constexpr int kOffA = 1024;                       // 8 sub-blocks x {lo, hi} + min tile = 17 A tiles
-constexpr int kOffB = kOffA + 17 * kTileA;        // 8 code tiles + 2 sum tiles = 10 B tiles
-constexpr int kOffXd = kOffB + 10 * kTileB;       // fp32 activation scales of the chunk
-constexpr int kGemmSmem = kOffXd + kGemmTok * 4;
+constexpr int kOffBar = 0;                                        // mbarriers, tmem base
+constexpr int kOffA = 1024;
+constexpr int kOffB = kOffA + kABufs * kATiles * kTileA;
+constexpr int kOffXd = kOffB + kBBufs * kBTiles * kTileB;         // [kXdRing][64] fp32 activation scales
+constexpr int kOffDd = kOffXd + kXdRing * kGemmTok * 4;           // [kDdRing][128] float2 (d, dmin)
+constexpr int kOffRed = kOffDd + kDdRing * kGemmRows * 8;         // [128][32] floats: one-chunk passes, group 1 -> group 0
+constexpr int kGemmSmem = kOffRed + kGemmRows * 32 * 4;
+static_assert(kGemmSmem <= 227 * 1024, "shared memory");
+
+enum { kBarAFull = 0, kBarAEmpty = 2, kBarBFull = 4, kBarBEmpty = 7, kBarAccFull = 10, kBarAccEmpty = 12, kBarCount = 14 };
 
 __device__ __forceinline__ uint64_t umma_desc(const void* smem_tile) {
   // K-major, no swizzle: start >> 4 | LBO (128 B) >> 4 << 16 | SBO (256 B) >> 4 << 32 | version 1 << 46
@@ -76,6 +95,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_cta(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 
 // address of (row, 16-byte K half) inside a canonical tile
 __device__ __forceinline__ unsigned char* tile_at(unsigned char* tile, int row, int khalf) {
@@ -101,16 +123,31 @@ __device__ __forceinline__ uint4 load16(const unsigned char* p, int align) {
   return make_uint4(v[0], v[1], v[2], v[3]);
 }
 
-// sc * q for four weights (one per byte of `q4`, each 0..15), split as 128*hi + lo
-__device__ __forceinline__ void scale_split(uint32_t q4, uint32_t sc, uint32_t& lo, uint32_t& hi) {
-  const uint32_t pe = (q4 & 0x00FF00FFu) * sc;            // two 16-bit products, each <= 945
-  const uint32_t po = ((q4 >> 8) & 0x00FF00FFu) * sc;
-  lo = (pe & 0x007F007Fu) | ((po & 0x007F007Fu) << 8);
-  hi = ((pe >> 7) & 0x000F000Fu) | (((po >> 7) & 0x000F000Fu) << 8);
-}
+// The jobs of a CTA in the order every role walks them.
+struct JobWalk {
+  int m_e, nb;
+  int pass, blk, ci, nc, j, abk;         // current pass, block column, chunk in pass, chunks in pass, job number, block number
+  __device__ __forceinline__ void start(int m_e_, int nb_) {
+    m_e = m_e_; nb = nb_; pass = 0; blk = 0; ci = 0; j = 0; abk = 0;
+    nc = min(2, (m_e + kGemmTok - 1) / kGemmTok);
+  }
+  __device__ __forceinline__ bool done() const { return pass * 2 * kGemmTok >= m_e; }
+  __device__ __forceinline__ int t0() const { return (2 * pass + ci) * kGemmTok; }
+  __device__ __forceinline__ int nt() const { return min(kGemmTok, m_e - t0()); }
+  __device__ __forceinline__ bool first_of_block() const { return ci == 0; }
+  __device__ __forceinline__ bool last_of_block() const { return ci == nc - 1; }
+  __device__ __forceinline__ void next() {
+    ++j;
+    if (++ci < nc) return;
+    ci = 0; ++abk;
+    if (++blk < nb) return;
+    blk = 0; ++pass;
+    nc = min(2, (m_e - pass * 2 * kGemmTok + kGemmTok - 1) / kGemmTok);
+  }
+};
 
-// grid (ceil(n_rows / 128), n_expert), 128 threads
-__global__ void __launch_bounds__(kGemmRows, 2)
+// grid (ceil(n_rows / 128), n_expert)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int* __restrict__ off,
                        const unsigned char* __restrict__ xq, uint16_t* __restrict__ y, int n_rows,
                        int nb, int* status) {
@@ -119,25 +156,30 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
   const int row_off = off[e];
   const int m_e = off[e + 1] - row_off;
   if (m_e <= 0) return;
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row0 = blockIdx.x * kGemmRows;
-  const int row = min(row0 + tid, n_rows - 1);            // ragged last tile: duplicate, never store
   const unsigned char* w = w_tab[e];
   if (w == nullptr) {                                      // absent expert: zero rows
-    for (int i = tid; i < m_e * kGemmRows; i += kGemmRows) {
+    for (int i = tid; i < m_e * kGemmRows; i += kGemmThreads) {
       const int t = i / kGemmRows, r = row0 + (i % kGemmRows);
       if (r < n_rows) y[static_cast<size_t>(row_off + t) * n_rows + r] = 0;
     }
     return;
   }
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem + kOffBar);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + 16);
-  unsigned char* a_tiles = smem + kOffA;
-  unsigned char* b_tiles = smem + kOffB;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + 128);
+  int* fail = reinterpret_cast<int*>(smem + kOffBar + 136);
+  unsigned char* a_base = smem + kOffA;
+  unsigned char* b_base = smem + kOffB;
   float* xd_sm = reinterpret_cast<float*>(smem + kOffXd);
+  float2* dd_sm = reinterpret_cast<float2*>(smem + kOffDd);
+  float* red = reinterpret_cast<float*>(smem + kOffRed);
 
   if (tid == 0) {
-    mbar_init(bar, 1);
+    for (int i = 0; i < kABufs; ++i) { mbar_init(&bar[kBarAFull + i], kUnpackWarps * 32); mbar_init(&bar[kBarAEmpty + i], 1); }
+    for (int i = 0; i < kBBufs; ++i) { mbar_init(&bar[kBarBFull + i], kStageWarps * 32); mbar_init(&bar[kBarBEmpty + i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar[kBarAccFull + i], 1); mbar_init(&bar[kBarAccEmpty + i], 4 * 32); }
+    *fail = 0;
     fence_barrier_init();
   }
   if (warp == 0) {
@@ -152,146 +194,258 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
-  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
   const size_t xrow_bytes = static_cast<size_t>(nb) * kX8;
-  const unsigned char* wrow = w + static_cast<size_t>(row) * nb * kW4;
-  const uintptr_t wa = reinterpret_cast<uintptr_t>(w);
-  const int walign = (wa & 15u) == 0 ? 16 : ((wa & 3u) == 0 ? 4 : 2);
-  unsigned phase = 0;
-  bool ok = true;
+  JobWalk jw;
+  jw.start(m_e, nb);
+  // a wait that gives up: flag the CTA, every role leaves its loop at its next wait
+  auto wait = [&](int b, unsigned parity) {
+    if (*reinterpret_cast<volatile int*>(fail)) return false;
+    if (mbar_wait(&bar[b], parity)) return true;
+    *reinterpret_cast<volatile int*>(fail) = 1;
+    return false;
+  };
 
-  for (int t0 = 0; t0 < m_e && ok; t0 += kGemmTok) {
-    const int nt = min(kGemmTok, m_e - t0);
-    const int n_mma = (nt + 15) & ~15;                     // MMA N: multiple of 16
-    const uint32_t idesc = umma_idesc_i8(n_mma);
-    float acc[kGemmTok];
+  if (warp >= kWarpUnpack0 && warp < kWarpCtrl) {
+    // ---------------- unpack: this thread's weight row -> operand tiles ----------------
+    const int r = tid - kWarpUnpack0 * 32;
+    const int row = min(row0 + r, n_rows - 1);             // ragged last tile: duplicate, never stored
+    const unsigned char* wrow = w + static_cast<size_t>(row) * nb * kW4;
+    const uintptr_t wa = reinterpret_cast<uintptr_t>(w);
+    const int walign = (wa & 15u) == 0 ? 16 : ((wa & 3u) == 0 ? 4 : 2);
+    uint4 cur[9];
 #pragma unroll
-    for (int t = 0; t < kGemmTok; ++t) acc[t] = 0.f;
-
-    for (int blk = 0; blk < nb && ok; ++blk) {
-      // ---- A: this thread's weight block -> 16 scaled operand tiles + the min tile ----
-      const unsigned char* wb = wrow + static_cast<size_t>(blk) * kW4;
-      const uint4 hdr = load16(wb, walign);
+    for (int i = 0; i < 9; ++i) cur[i] = load16(wrow + 16 * i, walign);
+    int prev_abk = -1;
+    for (; !jw.done(); jw.next()) {
+      if (jw.abk == prev_abk) continue;                     // one unpack per block column
+      prev_abk = jw.abk;
+      const int buf = jw.abk % kABufs;
+      const unsigned ph = (jw.abk / kABufs) & 1;
+      // the next block column of this row (wraps to column 0 for the next pass) is requested now
+      uint4 nxt[9];
+      {
+        const int nblk = jw.blk + 1 < nb ? jw.blk + 1 : 0;
+        const unsigned char* wn = wrow + static_cast<size_t>(nblk) * kW4;
+#pragma unroll
+        for (int i = 0; i < 9; ++i) nxt[i] = load16(wn + 16 * i, walign);
+      }
+      if (!wait(kBarAEmpty + buf, ph ^ 1u)) break;
+      unsigned char* a_tiles = a_base + static_cast<size_t>(buf) * kATiles * kTileA;
+      const uint4 hdr = cur[0];
       const float d = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x & 0xFFFFu)));
       const float dmin = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x >> 16)));
       const Scales6 s6 = unpack_scales6(hdr.y, hdr.z, hdr.w);
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
-        const uint4 q0 = load16(wb + 16 + 32 * g, walign), q1 = load16(wb + 32 + 32 * g, walign);
+        const uint4 q0 = cur[1 + 2 * g], q1 = cur[2 + 2 * g];
         const uint32_t raw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
         const uint32_t sc_e = (s6.sc[g >> 1] >> (16 * (g & 1))) & 0xFFu;        // sub-block 2g
         const uint32_t sc_o = (s6.sc[g >> 1] >> (16 * (g & 1) + 8)) & 0xFFu;    // sub-block 2g+1
-        uint32_t lo_e[8], hi_e[8], lo_o[8], hi_o[8];
+        const uint32_t be = sc_e & 7u, ae = sc_e >> 3, bo = sc_o & 7u, ao = sc_o >> 3;
+        uint32_t tb_e[8], ta_e[8], tb_o[8], ta_o[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          scale_split(raw[i] & 0x0F0F0F0Fu, sc_e, lo_e[i], hi_e[i]);
-          scale_split((raw[i] >> 4) & 0x0F0F0F0Fu, sc_o, lo_o[i], hi_o[i]);
+          const uint32_t lo = raw[i] & 0x0F0F0F0Fu, hi = (raw[i] >> 4) & 0x0F0F0F0Fu;
+          tb_e[i] = lo * be; ta_e[i] = lo * ae;            // bytes <= 105: no carry between bytes
+          tb_o[i] = hi * bo; ta_o[i] = hi * ao;
         }
-        unsigned char* t_lo_e = a_tiles + (4 * g + 0) * kTileA;   // tile order: [sub-block][lo, hi]
-        unsigned char* t_hi_e = a_tiles + (4 * g + 1) * kTileA;
-        unsigned char* t_lo_o = a_tiles + (4 * g + 2) * kTileA;
-        unsigned char* t_hi_o = a_tiles + (4 * g + 3) * kTileA;
+        unsigned char* t0p = a_tiles + (4 * g + 0) * kTileA;   // tile order: [sub-block][b part, a part]
+        unsigned char* t1p = a_tiles + (4 * g + 1) * kTileA;
+        unsigned char* t2p = a_tiles + (4 * g + 2) * kTileA;
+        unsigned char* t3p = a_tiles + (4 * g + 3) * kTileA;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          *reinterpret_cast<uint4*>(tile_at(t_lo_e, tid, h)) = make_uint4(lo_e[4 * h], lo_e[4 * h + 1], lo_e[4 * h + 2], lo_e[4 * h + 3]);
-          *reinterpret_cast<uint4*>(tile_at(t_hi_e, tid, h)) = make_uint4(hi_e[4 * h], hi_e[4 * h + 1], hi_e[4 * h + 2], hi_e[4 * h + 3]);
-          *reinterpret_cast<uint4*>(tile_at(t_lo_o, tid, h)) = make_uint4(lo_o[4 * h], lo_o[4 * h + 1], lo_o[4 * h + 2], lo_o[4 * h + 3]);
-          *reinterpret_cast<uint4*>(tile_at(t_hi_o, tid, h)) = make_uint4(hi_o[4 * h], hi_o[4 * h + 1], hi_o[4 * h + 2], hi_o[4 * h + 3]);
+          *reinterpret_cast<uint4*>(tile_at(t0p, r, h)) = make_uint4(tb_e[4 * h], tb_e[4 * h + 1], tb_e[4 * h + 2], tb_e[4 * h + 3]);
+          *reinterpret_cast<uint4*>(tile_at(t1p, r, h)) = make_uint4(ta_e[4 * h], ta_e[4 * h + 1], ta_e[4 * h + 2], ta_e[4 * h + 3]);
+          *reinterpret_cast<uint4*>(tile_at(t2p, r, h)) = make_uint4(tb_o[4 * h], tb_o[4 * h + 1], tb_o[4 * h + 2], tb_o[4 * h + 3]);
+          *reinterpret_cast<uint4*>(tile_at(t3p, r, h)) = make_uint4(ta_o[4 * h], ta_o[4 * h + 1], ta_o[4 * h + 2], ta_o[4 * h + 3]);
         }
       }
       {  // min tile: the eight min bytes at k = 0..7, zeros elsewhere
         unsigned char* t_mn = a_tiles + 16 * kTileA;
-        *reinterpret_cast<uint4*>(tile_at(t_mn, tid, 0)) = make_uint4(s6.mn[0], s6.mn[1], 0u, 0u);
-        *reinterpret_cast<uint4*>(tile_at(t_mn, tid, 1)) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(tile_at(t_mn, r, 0)) = make_uint4(s6.mn[0], s6.mn[1], 0u, 0u);
+        *reinterpret_cast<uint4*>(tile_at(t_mn, r, 1)) = make_uint4(0u, 0u, 0u, 0u);
       }
-      // ---- B: activation codes, split sub-block sums and scales of the chunk ----
-      for (int i = tid; i < n_mma * 16; i += kGemmRows) {
-        const int t = i >> 4, c = i & 15;                  // token slot, 16-byte chunk of the block
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (t < nt) {
-          const uint32_t* src = reinterpret_cast<const uint32_t*>(
-              xq + static_cast<size_t>(row_off + t0 + t) * xrow_bytes + static_cast<size_t>(blk) * kX8 + 4 + c * 16);
-          v = make_uint4(__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3));
-        }
-        *reinterpret_cast<uint4*>(tile_at(b_tiles + (c >> 1) * kTileB, t, c & 1)) = v;
+      dd_sm[(jw.abk % kDdRing) * kGemmRows + r] = make_float2(d, dmin);
+      fence_proxy_async();                                 // operand tiles -> visible to the tensor core
+      mbar_arrive_cta(&bar[kBarAFull + buf]);
+#pragma unroll
+      for (int i = 0; i < 9; ++i) cur[i] = nxt[i];
+    }
+  } else if (warp >= kWarpStage0) {
+    // ---------------- stagers: activation codes, split sums and scales of a job's chunk ----------------
+    const int s = tid - kWarpStage0 * 32;                  // 0..63: this thread's word of every token row
+    const int cch = s >> 2;
+    const int dst_off = (cch >> 1) * kTileB + (cch & 1) * 128 + (s & 3) * 4;
+    int landed = 0;                                        // jobs whose copies are known to have landed
+    int issued = 0;
+    auto publish = [&](int jj) {
+      fence_proxy_async();
+      mbar_arrive_cta(&bar[kBarBFull + jj % kBBufs]);
+    };
+    bool ok = true;
+    for (; !jw.done() && ok; jw.next()) {
+      const int j = jw.j, buf = j % kBBufs;
+      const unsigned ph = (j / kBBufs) & 1;
+      if (!wait(kBarBEmpty + buf, ph ^ 1u)) { ok = false; break; }
+      const int t0 = jw.t0(), nt = jw.nt();
+      unsigned char* b_tiles = b_base + static_cast<size_t>(buf) * kBTiles * kTileB;
+      // codes: word s of every token row (a warp covers 128 contiguous bytes of a row)
+      const unsigned char* src = xq + static_cast<size_t>(row_off + t0) * xrow_bytes + static_cast<size_t>(jw.blk) * kX8 + 4 + s * 4;
+#pragma unroll 8
+      for (int i = 0; i < kGemmTok; ++i) {
+        if (i < nt)
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(b_tiles + dst_off + (i >> 3) * 256 + (i & 7) * 16)),
+                       "l"(src + static_cast<size_t>(i) * xrow_bytes) : "memory");
       }
-      for (int t = tid; t < n_mma; t += kGemmRows) {
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      // sums and scale of token row s (threads 0..63): plain loads, split as bsum = 128*hi + lo
+      {
         uint32_t lo01 = 0, lo23 = 0, hi01 = 0, hi23 = 0;
         float xd = 0.f;
-        if (t < nt) {
-          const unsigned char* xb = xq + static_cast<size_t>(row_off + t0 + t) * xrow_bytes + static_cast<size_t>(blk) * kX8;
+        if (s < nt) {
+          const unsigned char* xb = xq + static_cast<size_t>(row_off + t0 + s) * xrow_bytes + static_cast<size_t>(jw.blk) * kX8;
           xd = __uint_as_float(__ldg(reinterpret_cast<const uint32_t*>(xb)));
           const uint32_t* bs = reinterpret_cast<const uint32_t*>(xb + 260);       // 8 x int16
-          uint32_t lo[8], hi[8];
-#pragma unroll
-          for (int p = 0; p < 4; ++p) {
-            const uint32_t v = __ldg(bs + p);
-            const int s0 = static_cast<int16_t>(v & 0xFFFFu), s1 = static_cast<int16_t>(v >> 16);
-            lo[2 * p] = s0 & 127; lo[2 * p + 1] = s1 & 127;
-            hi[2 * p] = (s0 >> 7) & 0xFF; hi[2 * p + 1] = (s1 >> 7) & 0xFF;
-          }
-          lo01 = lo[0] | (lo[1] << 8) | (lo[2] << 16) | (lo[3] << 24);
-          lo23 = lo[4] | (lo[5] << 8) | (lo[6] << 16) | (lo[7] << 24);
-          hi01 = hi[0] | (hi[1] << 8) | (hi[2] << 16) | (hi[3] << 24);
-          hi23 = hi[4] | (hi[5] << 8) | (hi[6] << 16) | (hi[7] << 24);
+          const uint32_t v0 = __ldg(bs), v1 = __ldg(bs + 1), v2 = __ldg(bs + 2), v3 = __ldg(bs + 3);
+          lo01 = __byte_perm(v0 & 0x007F007Fu, v1 & 0x007F007Fu, 0x6420);
+          lo23 = __byte_perm(v2 & 0x007F007Fu, v3 & 0x007F007Fu, 0x6420);
+          hi01 = __byte_perm((v0 >> 7) & 0x00FF00FFu, (v1 >> 7) & 0x00FF00FFu, 0x6420);
+          hi23 = __byte_perm((v2 >> 7) & 0x00FF00FFu, (v3 >> 7) & 0x00FF00FFu, 0x6420);
         }
-        xd_sm[t] = xd;
-        *reinterpret_cast<uint4*>(tile_at(b_tiles + 8 * kTileB, t, 0)) = make_uint4(lo01, lo23, 0u, 0u);
-        *reinterpret_cast<uint4*>(tile_at(b_tiles + 8 * kTileB, t, 1)) = make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(tile_at(b_tiles + 9 * kTileB, t, 0)) = make_uint4(hi01, hi23, 0u, 0u);
-        *reinterpret_cast<uint4*>(tile_at(b_tiles + 9 * kTileB, t, 1)) = make_uint4(0u, 0u, 0u, 0u);
+        xd_sm[(j % kXdRing) * kGemmTok + s] = xd;
+        *reinterpret_cast<uint4*>(tile_at(b_tiles + 8 * kTileB, s, 0)) = make_uint4(lo01, lo23, 0u, 0u);
+        *reinterpret_cast<uint4*>(tile_at(b_tiles + 8 * kTileB, s, 1)) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(tile_at(b_tiles + 9 * kTileB, s, 0)) = make_uint4(hi01, hi23, 0u, 0u);
+        *reinterpret_cast<uint4*>(tile_at(b_tiles + 9 * kTileB, s, 1)) = make_uint4(0u, 0u, 0u, 0u);
       }
-      fence_proxy_async();                                 // operand tiles -> visible to the tensor core
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncthreads();
-      // ---- MMAs: D0 = sum lo, D1 = sum hi, D2 = min x sums_lo, D3 = min x sums_hi ----
-      if (tid == 0) {
+      ++issued;
+      if (issued - landed > 1) {                           // keep one job's copies in flight
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        publish(landed);
+        ++landed;
+      }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (ok) while (landed < issued) { publish(landed); ++landed; }
+  } else if (warp == kWarpCtrl) {
+    // ---------------- MMA issue: one elected thread ----------------
+    if (lane == 0) {
+      for (; !jw.done(); jw.next()) {
+        const int j = jw.j, abuf = jw.abk % kABufs, bbuf = j % kBBufs, set = j & 1;
+        if (jw.first_of_block() && !wait(kBarAFull + abuf, (jw.abk / kABufs) & 1)) break;
+        if (!wait(kBarBFull + bbuf, (j / kBBufs) & 1)) break;
+        if (!wait(kBarAccEmpty + set, ((j >> 1) & 1) ^ 1u)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned char* a_tiles = a_base + static_cast<size_t>(abuf) * kATiles * kTileA;
+        const unsigned char* b_tiles = b_base + static_cast<size_t>(bbuf) * kBTiles * kTileB;
+        const int n_mma = (jw.nt() + 15) & ~15;             // MMA N: multiple of 16
+        const uint32_t idesc = umma_idesc_i8(n_mma);
+        const uint32_t acc = tmem + set * 4 * kGemmTok;
+        // D0 = sum (b*q) x, D1 = sum (a*q) x, D2 = min x sums_lo, D3 = min x sums_hi
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          const uint64_t db = umma_desc(b_tiles + s * kTileB);
-          umma_i8(tmem + 0 * kGemmTok, umma_desc(a_tiles + (2 * s) * kTileA), db, idesc, s > 0);
-          umma_i8(tmem + 1 * kGemmTok, umma_desc(a_tiles + (2 * s + 1) * kTileA), db, idesc, s > 0);
+        for (int sb = 0; sb < 8; ++sb) {
+          const uint64_t db = umma_desc(b_tiles + sb * kTileB);
+          umma_i8(acc + 0 * kGemmTok, umma_desc(a_tiles + (2 * sb) * kTileA), db, idesc, sb > 0);
+          umma_i8(acc + 1 * kGemmTok, umma_desc(a_tiles + (2 * sb + 1) * kTileA), db, idesc, sb > 0);
         }
         const uint64_t dmn = umma_desc(a_tiles + 16 * kTileA);
-        umma_i8(tmem + 2 * kGemmTok, dmn, umma_desc(b_tiles + 8 * kTileB), idesc, 0u);
-        umma_i8(tmem + 3 * kGemmTok, dmn, umma_desc(b_tiles + 9 * kTileB), idesc, 0u);
-        umma_commit(bar);
+        umma_i8(acc + 2 * kGemmTok, dmn, umma_desc(b_tiles + 8 * kTileB), idesc, 0u);
+        umma_i8(acc + 3 * kGemmTok, dmn, umma_desc(b_tiles + 9 * kTileB), idesc, 0u);
+        umma_commit(&bar[kBarAccFull + set]);               // accumulators ready for the epilogue
+        umma_commit(&bar[kBarBEmpty + bbuf]);               // B tiles free
+        if (jw.last_of_block()) umma_commit(&bar[kBarAEmpty + abuf]);   // A tiles free
       }
-      ok = __syncthreads_and(mbar_wait(bar, phase)) != 0;
-      phase ^= 1u;
-      if (!ok) break;
+    }
+  } else {
+    // ---------------- epilogue: two groups of four warps; this thread's row, the job's tokens ----------------
+    const int grp = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;                // accumulator lane = weight row in the tile
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    float acc[kGemmTok];
+#pragma unroll
+    for (int t = 0; t < kGemmTok; ++t) acc[t] = 0.f;
+    bool ok = true;
+    int pass_t0 = 0, pass_nc = jw.nc, pass_nt0 = 0, pass_nt1 = 0, cur_pass = 0;
+    auto flush = [&]() {
+      // end of a pass: one chunk -> group 1 hands its sums to group 0 through shared memory
+      // (two halves of 32 tokens); two chunks -> each group stores its own chunk
+      const bool valid = row0 + row < n_rows && ok && !*reinterpret_cast<volatile int*>(fail);
+      if (pass_nc == 1) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          if (grp == 1) {
+#pragma unroll
+            for (int t = 0; t < 32; ++t) red[t * kGemmRows + row] = acc[32 * half + t];
+          }
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+          if (grp == 0) {
+#pragma unroll
+            for (int t = 0; t < 32; ++t) acc[32 * half + t] += red[t * kGemmRows + row];
+          }
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
+        if (grp == 0 && valid) {
+#pragma unroll
+          for (int t = 0; t < kGemmTok; ++t)
+            if (t < pass_nt0) y[static_cast<size_t>(row_off + pass_t0 + t) * n_rows + row0 + row] = f2h(acc[t]);
+        }
+      } else if (valid) {
+        const int nt = grp == 0 ? pass_nt0 : pass_nt1;
+        const int t0 = pass_t0 + grp * kGemmTok;
+#pragma unroll
+        for (int t = 0; t < kGemmTok; ++t)
+          if (t < nt) y[static_cast<size_t>(row_off + t0 + t) * n_rows + row0 + row] = f2h(acc[t]);
+      }
+#pragma unroll
+      for (int t = 0; t < kGemmTok; ++t) acc[t] = 0.f;
+    };
+    pass_nt0 = min(kGemmTok, m_e);
+    pass_nt1 = min(kGemmTok, max(0, m_e - kGemmTok));
+    for (; !jw.done(); jw.next()) {
+      if (jw.pass != cur_pass) {                            // both groups see the pass change at the same job
+        flush();
+        cur_pass = jw.pass;
+        pass_t0 = cur_pass * 2 * kGemmTok;
+        pass_nc = jw.nc;
+        pass_nt0 = min(kGemmTok, m_e - pass_t0);
+        pass_nt1 = min(kGemmTok, max(0, m_e - pass_t0 - kGemmTok));
+      }
+      const int j = jw.j;
+      if ((j & 1) != grp || !ok) continue;                 // (a group that gave up still walks the list: the
+                                                            //  barriers of the pass ends need both groups)
+      if (!__all_sync(0xFFFFFFFFu, wait(kBarAccFull + grp, (j >> 1) & 1))) { ok = false; continue; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // ---- epilogue: this thread's row, all tokens of the chunk ----
+      const float2 dd = dd_sm[(jw.abk % kDdRing) * kGemmRows + row];
+      const float* xd = xd_sm + (j % kXdRing) * kGemmTok;
+      const int n_mma = (jw.nt() + 15) & ~15;
+      const uint32_t accp = tmem + lane_base + grp * 4 * kGemmTok;
 #pragma unroll
       for (int c0 = 0; c0 < kGemmTok; c0 += 16) {
         if (c0 < n_mma) {
-          int lo[16], hi[16], mlo[16], mhi[16];
-          tmem_ld16(tmem + lane_base + 0 * kGemmTok + c0, lo);
-          tmem_ld16(tmem + lane_base + 1 * kGemmTok + c0, hi);
-          tmem_ld16(tmem + lane_base + 2 * kGemmTok + c0, mlo);
-          tmem_ld16(tmem + lane_base + 3 * kGemmTok + c0, mhi);
+          int vb[16], va[16], mlo[16], mhi[16];
+          tmem_ld16(accp + 0 * kGemmTok + c0, vb);
+          tmem_ld16(accp + 1 * kGemmTok + c0, va);
+          tmem_ld16(accp + 2 * kGemmTok + c0, mlo);
+          tmem_ld16(accp + 3 * kGemmTok + c0, mhi);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int isum = lo[j] + 128 * hi[j];
-            const int msum = mlo[j] + 128 * mhi[j];
-            acc[c0 + j] += xd_sm[c0 + j] * (d * static_cast<float>(isum) - dmin * static_cast<float>(msum));
+          for (int q = 0; q < 16; ++q) {
+            const int isum = vb[q] + 8 * va[q];
+            const int msum = mlo[q] + 128 * mhi[q];
+            acc[c0 + q] += xd[c0 + q] * (dd.x * static_cast<float>(isum) - dd.y * static_cast<float>(msum));
           }
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncthreads();                                     // accumulators and tiles free for the next block
+      mbar_arrive_cta(&bar[kBarAccEmpty + grp]);
     }
-    if (ok && row0 + tid < n_rows) {
-#pragma unroll
-      for (int t = 0; t < kGemmTok; ++t)
-        if (t < nt) y[static_cast<size_t>(row_off + t0 + t) * n_rows + row0 + tid] = f2h(acc[t]);
-    }
+    flush();
   }
-  if (!ok && tid == 0 && status != nullptr) atomicExch(status, 6);
+
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (tid == 0 && *fail && status != nullptr) atomicExch(status, 6);
   if (warp == 0) {
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
@@ -314,7 +468,7 @@ SGR_API int sgr_moe_grouped_gemm_i8(const void* const* w_tab, const int* off, co
   auto kern = grouped_gemm_i8_kernel;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
     return kErrLaunch;
-  kern<<<dim3((n_rows + kGemmRows - 1) / kGemmRows, n_expert), kGemmRows, kGemmSmem, as_stream(stream)>>>(
+  kern<<<dim3((n_rows + kGemmRows - 1) / kGemmRows, n_expert), kGemmThreads, kGemmSmem, as_stream(stream)>>>(
       reinterpret_cast<const unsigned char* const*>(w_tab), off, static_cast<const unsigned char*>(xq), y,
       n_rows, k / kQK, status_word());
   return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
