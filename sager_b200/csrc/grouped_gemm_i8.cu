@@ -39,6 +39,15 @@
 namespace sgr {
 namespace {
 
+#ifdef SGR_PROFILE
+__device__ unsigned long long g_gemm_prof[32];
+#define GP_T0() long long _gp = clock64()
+#define GP_ADD(i) do { const long long _n = clock64(); atomicAdd(&g_gemm_prof[i], static_cast<unsigned long long>(_n - _gp)); _gp = _n; } while (0)
+#else
+#define GP_T0() do {} while (0)
+#define GP_ADD(i) do {} while (0)
+#endif
+
 constexpr int kGemmRows = 128;     // weight rows per CTA = MMA M
 constexpr int kGemmTok = 64;       // token rows per chunk = max MMA N
 constexpr int kTileA = kGemmRows * 32;            // bytes of one A tile (128 x 32 int8)
@@ -48,9 +57,9 @@ constexpr int kBTiles = 10;                       // 8 code tiles + 2 split-sum 
 constexpr int kABufs = 2, kBBufs = 3, kDdRing = 4, kXdRing = 6;
 constexpr int kTmemCols = 512;                    // two sets of four 64-column accumulators
 
-constexpr int kEpiWarps = 8, kUnpackWarps = 4, kStageWarps = 2;
+constexpr int kEpiWarps = 8, kUnpackWarps = 4, kStageWarps = 3;
 constexpr int kWarpUnpack0 = kEpiWarps, kWarpCtrl = kEpiWarps + kUnpackWarps, kWarpStage0 = kWarpCtrl + 1;
-constexpr int kGemmThreads = (kEpiWarps + kUnpackWarps + 1 + kStageWarps) * 32;    // 480
+constexpr int kGemmThreads = (kEpiWarps + kUnpackWarps + 1 + kStageWarps) * 32;    // 512
 
 // shared-memory map (bytes)
 constexpr int kOffBar = 0;                                        // mbarriers, tmem base
@@ -157,6 +166,9 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
   const int m_e = off[e + 1] - row_off;
   if (m_e <= 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef SGR_PROFILE
+  const long long _k0 = clock64();
+#endif
   const int row0 = blockIdx.x * kGemmRows;
   const unsigned char* w = w_tab[e];
   if (w == nullptr) {                                      // absent expert: zero rows
@@ -177,7 +189,7 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
 
   if (tid == 0) {
     for (int i = 0; i < kABufs; ++i) { mbar_init(&bar[kBarAFull + i], kUnpackWarps * 32); mbar_init(&bar[kBarAEmpty + i], 1); }
-    for (int i = 0; i < kBBufs; ++i) { mbar_init(&bar[kBarBFull + i], kStageWarps * 32); mbar_init(&bar[kBarBEmpty + i], 1); }
+    for (int i = 0; i < kBBufs; ++i) { mbar_init(&bar[kBarBFull + i], 32); mbar_init(&bar[kBarBEmpty + i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&bar[kBarAccFull + i], 1); mbar_init(&bar[kBarAccEmpty + i], 4 * 32); }
     *fail = 0;
     fence_barrier_init();
@@ -216,6 +228,7 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
 #pragma unroll
     for (int i = 0; i < 9; ++i) cur[i] = load16(wrow + 16 * i, walign);
     int prev_abk = -1;
+    GP_T0();
     for (; !jw.done(); jw.next()) {
       if (jw.abk == prev_abk) continue;                     // one unpack per block column
       prev_abk = jw.abk;
@@ -229,7 +242,9 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
 #pragma unroll
         for (int i = 0; i < 9; ++i) nxt[i] = load16(wn + 16 * i, walign);
       }
+      if (r == 0) GP_ADD(1);
       if (!wait(kBarAEmpty + buf, ph ^ 1u)) break;
+      if (r == 0) GP_ADD(0);
       unsigned char* a_tiles = a_base + static_cast<size_t>(buf) * kATiles * kTileA;
       const uint4 hdr = cur[0];
       const float d = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x & 0xFFFFu)));
@@ -274,84 +289,110 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
     }
   } else if (warp >= kWarpStage0) {
     // ---------------- stagers: activation codes, split sums and scales of a job's chunk ----------------
-    const int s = tid - kWarpStage0 * 32;                  // 0..63: this thread's word of every token row
-    const int cch = s >> 2;
-    const int dst_off = (cch >> 1) * kTileB + (cch & 1) * 128 + (s & 3) * 4;
-    int landed = 0;                                        // jobs whose copies are known to have landed
-    int issued = 0;
-    auto publish = [&](int jj) {
-      fence_proxy_async();
-      mbar_arrive_cta(&bar[kBarBFull + jj % kBBufs]);
-    };
-    bool ok = true;
-    for (; !jw.done() && ok; jw.next()) {
+    // Each of the three stager warps takes every third job; a lane owns token rows `lane` and
+    // `lane + 32` of the chunk. The 256 codes of a packed Q8_K block start 4 bytes into the
+    // 276-byte block, so their 16-byte pieces are not aligned: the lane reads the 17 aligned
+    // pieces that cover them and picks each operand piece out of two neighbours by whole words.
+    const int sg = warp - kWarpStage0;
+    GP_T0();
+    for (; !jw.done(); jw.next()) {
       const int j = jw.j, buf = j % kBBufs;
+      if (j % kStageWarps != sg) continue;
       const unsigned ph = (j / kBBufs) & 1;
-      if (!wait(kBarBEmpty + buf, ph ^ 1u)) { ok = false; break; }
       const int t0 = jw.t0(), nt = jw.nt();
       unsigned char* b_tiles = b_base + static_cast<size_t>(buf) * kBTiles * kTileB;
-      // codes: word s of every token row (a warp covers 128 contiguous bytes of a row)
-      const unsigned char* src = xq + static_cast<size_t>(row_off + t0) * xrow_bytes + static_cast<size_t>(jw.blk) * kX8 + 4 + s * 4;
-#pragma unroll 8
-      for (int i = 0; i < kGemmTok; ++i) {
-        if (i < nt)
-          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(b_tiles + dst_off + (i >> 3) * 256 + (i & 7) * 16)),
-                       "l"(src + static_cast<size_t>(i) * xrow_bytes) : "memory");
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      // sums and scale of token row s (threads 0..63): plain loads, split as bsum = 128*hi + lo
-      {
-        uint32_t lo01 = 0, lo23 = 0, hi01 = 0, hi23 = 0;
-        float xd = 0.f;
-        if (s < nt) {
+      bool ok = true;
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        const int s = lane + 32 * half;                    // token row of the chunk
+        uint4 wv[17];
+        uint32_t pf[5] = {0u, 0u, 0u, 0u, 0u};             // scale, four words of sub-block sums
+        int sh = 0;
+        if (s < nt) {                                       // requested before the buffer is known to be free
           const unsigned char* xb = xq + static_cast<size_t>(row_off + t0 + s) * xrow_bytes + static_cast<size_t>(jw.blk) * kX8;
-          xd = __uint_as_float(__ldg(reinterpret_cast<const uint32_t*>(xb)));
+          const uintptr_t cs = reinterpret_cast<uintptr_t>(xb) + 4;
+          sh = static_cast<int>(cs & 15u) >> 2;
+          const uint4* a0 = reinterpret_cast<const uint4*>(cs & ~static_cast<uintptr_t>(15));
+#pragma unroll
+          for (int i = 0; i < 17; ++i) wv[i] = __ldg(a0 + i);
+          pf[0] = __ldg(reinterpret_cast<const uint32_t*>(xb));
           const uint32_t* bs = reinterpret_cast<const uint32_t*>(xb + 260);       // 8 x int16
-          const uint32_t v0 = __ldg(bs), v1 = __ldg(bs + 1), v2 = __ldg(bs + 2), v3 = __ldg(bs + 3);
-          lo01 = __byte_perm(v0 & 0x007F007Fu, v1 & 0x007F007Fu, 0x6420);
-          lo23 = __byte_perm(v2 & 0x007F007Fu, v3 & 0x007F007Fu, 0x6420);
-          hi01 = __byte_perm((v0 >> 7) & 0x00FF00FFu, (v1 >> 7) & 0x00FF00FFu, 0x6420);
-          hi23 = __byte_perm((v2 >> 7) & 0x00FF00FFu, (v3 >> 7) & 0x00FF00FFu, 0x6420);
+          pf[1] = __ldg(bs); pf[2] = __ldg(bs + 1); pf[3] = __ldg(bs + 2); pf[4] = __ldg(bs + 3);
         }
-        xd_sm[(j % kXdRing) * kGemmTok + s] = xd;
-        *reinterpret_cast<uint4*>(tile_at(b_tiles + 8 * kTileB, s, 0)) = make_uint4(lo01, lo23, 0u, 0u);
-        *reinterpret_cast<uint4*>(tile_at(b_tiles + 8 * kTileB, s, 1)) = make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(tile_at(b_tiles + 9 * kTileB, s, 0)) = make_uint4(hi01, hi23, 0u, 0u);
-        *reinterpret_cast<uint4*>(tile_at(b_tiles + 9 * kTileB, s, 1)) = make_uint4(0u, 0u, 0u, 0u);
+        if (half == 0) {
+          if (sg == 0 && lane == 0) GP_ADD(3);
+          ok = __all_sync(0xFFFFFFFFu, wait(kBarBEmpty + buf, ph ^ 1u));
+          if (sg == 0 && lane == 0) GP_ADD(2);
+          if (!ok) break;
+        }
+        if (s < nt) {
+          auto put = [&](int c, uint32_t a, uint32_t b, uint32_t cc, uint32_t d) {
+            *reinterpret_cast<uint4*>(tile_at(b_tiles + (c >> 1) * kTileB, s, c & 1)) = make_uint4(a, b, cc, d);
+          };
+          if (sh == 0) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) put(c, wv[c].x, wv[c].y, wv[c].z, wv[c].w);
+          } else if (sh == 1) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) put(c, wv[c].y, wv[c].z, wv[c].w, wv[c + 1].x);
+          } else if (sh == 2) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) put(c, wv[c].z, wv[c].w, wv[c + 1].x, wv[c + 1].y);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) put(c, wv[c].w, wv[c + 1].x, wv[c + 1].y, wv[c + 1].z);
+          }
+        }
+        {                                                   // sums split as bsum = 128*hi + lo; rows beyond nt: zero scale
+          uint32_t lo01 = 0, lo23 = 0, hi01 = 0, hi23 = 0;
+          float xd = 0.f;
+          if (s < nt) {
+            xd = __uint_as_float(pf[0]);
+            lo01 = __byte_perm(pf[1] & 0x007F007Fu, pf[2] & 0x007F007Fu, 0x6420);
+            lo23 = __byte_perm(pf[3] & 0x007F007Fu, pf[4] & 0x007F007Fu, 0x6420);
+            hi01 = __byte_perm((pf[1] >> 7) & 0x00FF00FFu, (pf[2] >> 7) & 0x00FF00FFu, 0x6420);
+            hi23 = __byte_perm((pf[3] >> 7) & 0x00FF00FFu, (pf[4] >> 7) & 0x00FF00FFu, 0x6420);
+          }
+          xd_sm[(j % kXdRing) * kGemmTok + s] = xd;
+          *reinterpret_cast<uint4*>(tile_at(b_tiles + 8 * kTileB, s, 0)) = make_uint4(lo01, lo23, 0u, 0u);
+          *reinterpret_cast<uint4*>(tile_at(b_tiles + 8 * kTileB, s, 1)) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(tile_at(b_tiles + 9 * kTileB, s, 0)) = make_uint4(hi01, hi23, 0u, 0u);
+          *reinterpret_cast<uint4*>(tile_at(b_tiles + 9 * kTileB, s, 1)) = make_uint4(0u, 0u, 0u, 0u);
+        }
       }
-      ++issued;
-      if (issued - landed > 1) {                           // keep one job's copies in flight
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-        publish(landed);
-        ++landed;
-      }
+      if (!ok) break;
+      fence_proxy_async();
+      mbar_arrive_cta(&bar[kBarBFull + buf]);
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    if (ok) while (landed < issued) { publish(landed); ++landed; }
   } else if (warp == kWarpCtrl) {
     // ---------------- MMA issue: one elected thread ----------------
     if (lane == 0) {
+      GP_T0();
       for (; !jw.done(); jw.next()) {
         const int j = jw.j, abuf = jw.abk % kABufs, bbuf = j % kBBufs, set = j & 1;
+        GP_ADD(7);
         if (jw.first_of_block() && !wait(kBarAFull + abuf, (jw.abk / kABufs) & 1)) break;
+        GP_ADD(4);
         if (!wait(kBarBFull + bbuf, (j / kBBufs) & 1)) break;
+        GP_ADD(5);
         if (!wait(kBarAccEmpty + set, ((j >> 1) & 1) ^ 1u)) break;
+        GP_ADD(6);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const unsigned char* a_tiles = a_base + static_cast<size_t>(abuf) * kATiles * kTileA;
-        const unsigned char* b_tiles = b_base + static_cast<size_t>(bbuf) * kBTiles * kTileB;
+        // descriptors of consecutive tiles differ by the tile size in the address field
+        const uint64_t da0 = umma_desc(a_base + static_cast<size_t>(abuf) * kATiles * kTileA);
+        const uint64_t db0 = umma_desc(b_base + static_cast<size_t>(bbuf) * kBTiles * kTileB);
+        constexpr uint64_t kStepA = kTileA >> 4, kStepB = kTileB >> 4;
         const int n_mma = (jw.nt() + 15) & ~15;             // MMA N: multiple of 16
         const uint32_t idesc = umma_idesc_i8(n_mma);
         const uint32_t acc = tmem + set * 4 * kGemmTok;
         // D0 = sum (b*q) x, D1 = sum (a*q) x, D2 = min x sums_lo, D3 = min x sums_hi
 #pragma unroll
         for (int sb = 0; sb < 8; ++sb) {
-          const uint64_t db = umma_desc(b_tiles + sb * kTileB);
-          umma_i8(acc + 0 * kGemmTok, umma_desc(a_tiles + (2 * sb) * kTileA), db, idesc, sb > 0);
-          umma_i8(acc + 1 * kGemmTok, umma_desc(a_tiles + (2 * sb + 1) * kTileA), db, idesc, sb > 0);
+          umma_i8(acc + 0 * kGemmTok, da0 + (2 * sb) * kStepA, db0 + sb * kStepB, idesc, sb > 0);
+          umma_i8(acc + 1 * kGemmTok, da0 + (2 * sb + 1) * kStepA, db0 + sb * kStepB, idesc, sb > 0);
         }
-        const uint64_t dmn = umma_desc(a_tiles + 16 * kTileA);
-        umma_i8(acc + 2 * kGemmTok, dmn, umma_desc(b_tiles + 8 * kTileB), idesc, 0u);
-        umma_i8(acc + 3 * kGemmTok, dmn, umma_desc(b_tiles + 9 * kTileB), idesc, 0u);
+        umma_i8(acc + 2 * kGemmTok, da0 + 16 * kStepA, db0 + 8 * kStepB, idesc, 0u);
+        umma_i8(acc + 3 * kGemmTok, da0 + 16 * kStepA, db0 + 9 * kStepB, idesc, 0u);
         umma_commit(&bar[kBarAccFull + set]);               // accumulators ready for the epilogue
         umma_commit(&bar[kBarBEmpty + bbuf]);               // B tiles free
         if (jw.last_of_block()) umma_commit(&bar[kBarAEmpty + abuf]);   // A tiles free
@@ -402,6 +443,7 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
     };
     pass_nt0 = min(kGemmTok, m_e);
     pass_nt1 = min(kGemmTok, max(0, m_e - kGemmTok));
+    GP_T0();
     for (; !jw.done(); jw.next()) {
       if (jw.pass != cur_pass) {                            // both groups see the pass change at the same job
         flush();
@@ -414,7 +456,9 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
       const int j = jw.j;
       if ((j & 1) != grp || !ok) continue;                 // (a group that gave up still walks the list: the
                                                             //  barriers of the pass ends need both groups)
+      if (tid == 0) GP_ADD(9);
       if (!__all_sync(0xFFFFFFFFu, wait(kBarAccFull + grp, (j >> 1) & 1))) { ok = false; continue; }
+      if (tid == 0) GP_ADD(8);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float2 dd = dd_sm[(jw.abk % kDdRing) * kGemmRows + row];
       const float* xd = xd_sm + (j % kXdRing) * kGemmTok;
@@ -440,12 +484,17 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive_cta(&bar[kBarAccEmpty + grp]);
     }
+    if (tid == 0) GP_ADD(9);
     flush();
+    if (tid == 0) GP_ADD(10);
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (tid == 0 && *fail && status != nullptr) atomicExch(status, 6);
+#ifdef SGR_PROFILE
+  if (tid == 0) { atomicAdd(&g_gemm_prof[11], static_cast<unsigned long long>(clock64() - _k0)); atomicAdd(&g_gemm_prof[12], 1ull); atomicAdd(&g_gemm_prof[13], static_cast<unsigned long long>(jw.nb * ((m_e + kGemmTok - 1) / kGemmTok))); }
+#endif
   if (warp == 0) {
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
@@ -463,7 +512,7 @@ SGR_API int sgr_moe_grouped_gemm_i8(const void* const* w_tab, const int* off, co
                                     uint16_t* y, int n_rows, int k, int n_expert, void* stream) {
   if (n_expert <= 0 || n_rows <= 0) return kOk;
   if (!w_tab || !off || !xq || !y || k <= 0 || k % kQK != 0) return kErrArg;
-  if (reinterpret_cast<uintptr_t>(xq) & 3u) return kErrAlign;
+  if (reinterpret_cast<uintptr_t>(xq) & 15u) return kErrAlign;   // rows are read in aligned 16-byte pieces
   if (n_expert > 65535) return kErrUnsupported;
   auto kern = grouped_gemm_i8_kernel;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
@@ -473,3 +522,13 @@ SGR_API int sgr_moe_grouped_gemm_i8(const void* const* w_tab, const int* off, co
       n_rows, k / kQK, status_word());
   return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
+
+#ifdef SGR_PROFILE
+extern "C" __attribute__((visibility("default"))) int sgr_gemm_prof_read(unsigned long long* out) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, sgr::g_gemm_prof, 32 * 8);
+  unsigned long long z[32] = {0};
+  cudaMemcpyToSymbol(sgr::g_gemm_prof, z, 32 * 8);
+  return 0;
+}
+#endif
