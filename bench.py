@@ -356,6 +356,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=LAYERS, help="shrink the stack (profiling captures)")
     ap.add_argument("--tokens", type=int, default=TOKENS, help="token rows per step, 1..64")
+    ap.add_argument("--check", action="store_true",
+                    help="N > 1: compare one step with the single-GPU layer stack on rank 0 (use with a small --layers)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                     help="decode: the 40-layer stack (default); prefill: one layer over a 2048-row chunk")
     ap.add_argument("--prefill-tokens", type=int, default=2048)

@@ -225,6 +225,16 @@ typedef struct sgr_moe_layer {
   int route_stride;      /* elements between rows of route_idx / route_w (default n_used+1) */
   int xq_stride;         /* bytes between Q8_K rows of xq_in / xq_out (default hidden/256*276) */
   void* xq_out;          /* optional: the router's Q8_K rows are written here, not to the workspace */
+  /* expert parallelism over peer memory: with routing_given, the plan first waits (bounded) until
+   * each of the wait_count words at wait_flags is >= *wait_step * wait_mul + wait_add - the arrival
+   * flags that sgr_ep_push sets on this rank. wait_flags == NULL: no wait. */
+  const unsigned* wait_flags;
+  const unsigned* wait_step;
+  int wait_count, wait_mul, wait_add;
+  /* records between ranks may carry the Q8_K rows in 288-byte blocks (d | 12 bytes | 256 codes |
+   * 8 sums, 16-byte aligned) instead of packed 276-byte ones: set for both the route stage that
+   * writes them (xq_out) and the owner that reads them (xq_in, routing_given, >= 16 rows). */
+  int xq_padded;
 } sgr_moe_layer;
 
 size_t sgr_moe_layer_workspace_bytes(int n_max, int hidden, int n_ff, int n_expert, int n_used);
@@ -261,6 +271,23 @@ int sgr_moe_grouped_gemm_i8(const void* const* w_tab, const int* off, const void
  * single-GPU): x[i] = f16(f32(x[i]) + sum_p parts[p*part_stride + i]), p ascending. */
 int sgr_ep_reduce_add_f16(uint16_t* x_f16, const float* parts, int n_parts, long long part_stride,
                           long long count, void* stream);
+
+/* Expert parallelism over peer memory (NVLink), for buffers every rank has mapped (symmetric
+ * memory; no counterpart in the reference). One kernel copies `bytes` from src + p * src_stride
+ * into dst[p] for every peer p < world with plain 16-byte stores (dst[p] and flags[p] are this
+ * rank's addresses of peer p's buffer and arrival word; src_stride 0 sends the same bytes to
+ * everyone), fences at system scope and then sets every flags[p] to *step * mul + add. `scratch`
+ * is one zeroed device word per call site. src, dst[p] 16-byte aligned, bytes % 16 == 0. */
+int sgr_ep_push(const void* src, long long src_stride, long long bytes, void* const* dst,
+                unsigned* const* flags, int world, const unsigned* step, int mul, int add,
+                unsigned* scratch, void* stream);
+/* sgr_ep_reduce_add_f16 that first waits (bounded) until each of the n_parts words at `flags` is
+ * >= *step * mul + add. */
+int sgr_ep_reduce_add_f16_wait(uint16_t* x_f16, const float* parts, int n_parts, long long part_stride,
+                               long long count, const unsigned* flags, const unsigned* step, int mul,
+                               int add, void* stream);
+/* *step += 1 (one thread), in stream order: the end of a step. */
+int sgr_ep_step_advance(unsigned* step, void* stream);
 
 size_t sgr_moe_layer_static_limit(void);
 int sgr_moe_layer_decode_static(const sgr_moe_layer* args, void* stream);

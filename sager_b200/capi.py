@@ -98,6 +98,9 @@ class MoeLayerArgs(C.Structure):
         ("mail", C.c_void_p), ("mail_n", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("route_stride", C.c_int), ("xq_stride", C.c_int), ("xq_out", C.c_void_p),
+        ("wait_flags", C.c_void_p), ("wait_step", C.c_void_p),
+        ("wait_count", C.c_int), ("wait_mul", C.c_int), ("wait_add", C.c_int),
+        ("xq_padded", C.c_int),
     ]
 
 

@@ -432,7 +432,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
         if (wk.kind == 0) {
           if (lane < rc.y) {
             const int r = rc.x == L.E ? rc.w + lane : __ldcg(L.grows + rc.w + lane);
-            myoff = r * L.nbh * kHq;
+            myoff = r * L.xq16_stride;
           }
         } else {
           if (lane < rc.y) myoff = (rc.z + lane) * L.nbf * kHq;

@@ -95,8 +95,13 @@ struct LayerDev {
   unsigned* ready;     // [max_tiles] row-streaming kernel: quantised blocks of h published
   unsigned char* hq;   // [(n_max*K + n_max)][nbf] Q8_K rows of h, 288-byte blocks (row-streaming kernel)
   int tok_tile;        // token rows per tile: 8 (item kernel) or 16 (row-streaming kernel)
-  unsigned char* xq16; // [n_max][nbh] the quantised rows once more in 288-byte blocks (row-streaming kernel)
+  unsigned char* xq16; // the quantised rows once more in 288-byte blocks (row-streaming kernel)
+  int xq16_stride;     // bytes between its rows (nbh * 288 in the workspace; the record stride for padded records)
+  int xq_padded;       // the caller's xq_in / xq_out rows are in 288-byte blocks already
   int grid;            // CTAs of the expert kernel
+  const unsigned* wait_flags;   // expert parallelism over peer memory: arrival words to wait for before planning
+  const unsigned* wait_step;
+  int wait_count, wait_mul, wait_add;
   unsigned char* tmaps;   // [grid][4][3][128] row-streaming kernel: patched TMA descriptors
   // TMA descriptors (placeholder address) of a gate / up matrix and of a down matrix. Only ever
   // read with constant indices: a dynamic index would make every thread keep a local-memory
@@ -180,7 +185,7 @@ __device__ __forceinline__ void pad_xq_rows(const LayerDev& L, int t0, int nt, i
     const int tb = i / words, w = i - tb * words;
     const int t = tb / L.nbh, blk = tb - t * L.nbh;
     const uint32_t v = reinterpret_cast<const uint32_t*>(L.xq_in + static_cast<size_t>(t0 + t) * L.xq_stride + blk * kX8)[w];
-    uint32_t* o = reinterpret_cast<uint32_t*>(L.xq16 + (static_cast<size_t>(t0 + t) * L.nbh + blk) * 288);
+    uint32_t* o = reinterpret_cast<uint32_t*>(L.xq16 + static_cast<size_t>(t0 + t) * L.xq16_stride + blk * 288);
     o[w == 0 ? 0 : w + 3] = v;
   }
 }
@@ -399,23 +404,25 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
   // Q8_K rows of the tile (packed, and padded for the row-streaming kernel): block
   // b of the tile goes to warp b / gridDim.x of CTA b % gridDim.x
   if (L.xq_in != nullptr) {
-    if (blockIdx.x == 0 && L.tok_tile != kTokTile) pad_xq_rows(L, tok0, nt, tid, blockDim.x);
+    if (blockIdx.x == 0 && L.tok_tile != kTokTile && !L.xq_padded) pad_xq_rows(L, tok0, nt, tid, blockDim.x);
   } else {
     const int b = warp * gridDim.x + blockIdx.x;
     if (b < nt * L.nbh) {
       const int t = b / L.nbh, blk = b - t * L.nbh;
       quantize_block_f16(L.xn + static_cast<size_t>(tok0 + t) * L.H + blk * kQK,
                          L.xq + static_cast<size_t>(tok0 + t) * L.xq_stride + blk * kX8, lane,
-                         L.tok_tile == kTokTile ? nullptr
-                                                : L.xq16 + (static_cast<size_t>(tok0 + t) * L.nbh + blk) * 288);
+                         (L.tok_tile == kTokTile && !L.xq_padded)
+                             ? nullptr
+                             : L.xq16 + static_cast<size_t>(tok0 + t) * L.xq16_stride + blk * 288);
     }
     // more blocks than warps in the tile's CTAs (small expert counts): the rest in a loop
     for (int b2 = b + kRouteWarps * gridDim.x; b2 < nt * L.nbh; b2 += kRouteWarps * gridDim.x) {
       const int t = b2 / L.nbh, blk = b2 - t * L.nbh;
       quantize_block_f16(L.xn + static_cast<size_t>(tok0 + t) * L.H + blk * kQK,
                          L.xq + static_cast<size_t>(tok0 + t) * L.xq_stride + blk * kX8, lane,
-                         L.tok_tile == kTokTile ? nullptr
-                                                : L.xq16 + (static_cast<size_t>(tok0 + t) * L.nbh + blk) * 288);
+                         (L.tok_tile == kTokTile && !L.xq_padded)
+                             ? nullptr
+                             : L.xq16 + static_cast<size_t>(tok0 + t) * L.xq16_stride + blk * 288);
     }
   }
 #ifdef SGR_TRACE
@@ -438,6 +445,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
   if (tid == 0) last_sh = atom_add_acq_rel(&L.cnt[blockIdx.y], 1u) == gridDim.x - 1 ? 1 : 0;
   __syncthreads();
   if (!last_sh) return;
+  if (tid == 0) L.cnt[blockIdx.y] = 0u;       // every CTA of the tile has counted in: ready for the next launch
 #ifdef SGR_TRACE
   if (tid == 0) rt[3] = gt();
 #endif
@@ -471,10 +479,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
   if (L.skip_plan) return;
   // last token tile plans
   __syncthreads();
-  if (tid == 0) {
-    L.cnt[blockIdx.y] = 0u;
-    last_sh = atom_add_acq_rel(&L.cnt[8], 1u) == gridDim.y - 1 ? 1 : 0;
-  }
+  if (tid == 0) last_sh = atom_add_acq_rel(&L.cnt[8], 1u) == gridDim.y - 1 ? 1 : 0;
   __syncthreads();
   if (!last_sh) return;
   if (tid == 0) L.cnt[8] = 0u;
@@ -496,12 +501,29 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
 #endif
 }
 
+// Bounded wait until n arrival words (written by peers over NVLink) reach `want`.
+__device__ __forceinline__ bool wait_arrivals(const unsigned* flags, int n, unsigned want, int tid) {
+  bool ok = true;
+  if (tid < n) {
+    unsigned it = 0, v;
+    do {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + tid) : "memory");
+    } while (static_cast<int>(v - want) < 0 && ++it < (1u << 22) && (__nanosleep(64), true));
+    ok = static_cast<int>(v - want) >= 0;
+  }
+  return __syncthreads_and(ok ? 1 : 0) != 0;
+}
+
 // Routing supplied by the caller (expert-parallel owner side): plan only.
-__global__ void __launch_bounds__(128) plan_kernel(const LayerDev L) {
+__global__ void __launch_bounds__(256) plan_kernel(const LayerDev L) {
   extern __shared__ __align__(16) unsigned char smem[];
   pdl_wait();
   pdl_launch_dependents();
-  if (L.tok_tile != kTokTile) pad_xq_rows(L, 0, L.n, threadIdx.x, blockDim.x);
+  if (L.wait_flags != nullptr &&
+      !wait_arrivals(L.wait_flags, L.wait_count, *L.wait_step * L.wait_mul + L.wait_add, threadIdx.x) &&
+      threadIdx.x == 0)
+    atomicExch(L.status, 8);                  // a peer's records did not arrive: the plan below reads stale rows
+  if (L.tok_tile != kTokTile && !L.xq_padded) pad_xq_rows(L, 0, L.n, threadIdx.x, blockDim.x);
   build_plan(L, smem);
 }
 
@@ -1031,6 +1053,54 @@ __global__ void ep_reduce_add_kernel(uint16_t* __restrict__ x, const float* __re
   }
 }
 
+// ep_reduce_add_kernel after the arrival words of all parts have reached `want` (every CTA waits).
+__global__ void ep_reduce_add_wait_kernel(uint16_t* __restrict__ x, const float* __restrict__ parts,
+                                          int n_parts, size_t part_stride, size_t count, const unsigned* flags,
+                                          const unsigned* step, int mul, int add, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  if (!wait_arrivals(flags, n_parts, *step * mul + add, threadIdx.x) && threadIdx.x == 0) atomicExch(status, 8);
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float acc = h2f(x[i]);
+    for (int p = 0; p < n_parts; ++p) acc += __ldcg(parts + p * part_stride + i);
+    x[i] = f2h(acc);
+  }
+}
+
+// Copies to every peer, then (last CTA to finish) the arrival words. grid (chunks, world).
+__global__ void ep_push_kernel(const unsigned char* __restrict__ src, size_t src_stride, size_t bytes,
+                               void* const* __restrict__ dst, unsigned* const* __restrict__ flags, int world,
+                               const unsigned* step, int mul, int add, unsigned* scratch) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int p = blockIdx.y;
+  const uint4* s = reinterpret_cast<const uint4*>(src + static_cast<size_t>(p) * src_stride);
+  uint4* d = reinterpret_cast<uint4*>(dst[p]);
+  const size_t n16 = bytes / 16;
+  const size_t per = (n16 + gridDim.x - 1) / gridDim.x;
+  const size_t lo = per * blockIdx.x, hi = lo + per < n16 ? lo + per : n16;
+  for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) d[i] = s[i];
+  __threadfence_system();                       // this thread's stores before the count below, at every GPU
+  __syncthreads();
+  __shared__ int last;
+  if (threadIdx.x == 0) last = atomicAdd(scratch, 1u) == gridDim.x * gridDim.y - 1 ? 1 : 0;
+  __syncthreads();
+  if (!last) return;
+  __threadfence_system();
+  if (threadIdx.x == 0) *scratch = 0u;
+  if (static_cast<int>(threadIdx.x) < world) {
+    const unsigned v = *step * mul + add;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags[threadIdx.x]), "r"(v) : "memory");
+  }
+}
+
+__global__ void ep_step_kernel(unsigned* step) {
+  pdl_wait();
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) *step += 1u;
+}
+
 #if defined(SGR_PROFILE) || defined(SGR_TRACE)
 long long* g_prof_buf = nullptr;
 #endif
@@ -1177,6 +1247,8 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   L.ready = reinterpret_cast<unsigned*>(ws + lay.ready);
   L.hq = ws + lay.hq;
   L.xq16 = ws + lay.xq16;
+  L.xq16_stride = L.nbh * 288;
+  L.xq_padded = a->xq_padded ? 1 : 0;
   L.tmaps = ws + lay.tmaps;
   L.meta = reinterpret_cast<int*>(ws + lay.meta);
   L.gslot = reinterpret_cast<int*>(ws + lay.gslot);
@@ -1186,12 +1258,32 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   L.ybuf = reinterpret_cast<float*>(ws + lay.ybuf);
   L.n_max = a->n_max;
   L.status = status_word();
+  L.wait_flags = a->wait_flags; L.wait_step = a->wait_step;
+  L.wait_count = a->wait_count; L.wait_mul = a->wait_mul; L.wait_add = a->wait_add;
+  if (L.wait_flags != nullptr && (!a->routing_given || !L.wait_step || L.wait_count < 0 || L.wait_count > 128)) return kErrArg;
   // Which expert kernel: the row-streaming one pays once a layer has enough tiles to
   // give every SM whole groups (bit 4 of `stages` forces it, bit 5 forces the item
   // kernel; both stages of a split call must be given the same bits).
   const bool use_rows = (stages & 32) ? false : ((stages & 16) ? true : a->n >= kRowsKernelMinRows);
   L.tok_tile = use_rows ? rs::kTok : kTokTile;
   if (a->workspace_bytes < (use_rows ? lay.total : lay.items_total)) return kErrArg;
+  if (L.xq_padded) {
+    // rows in 288-byte blocks travel between ranks: the row-streaming kernel reads them in place
+    // (given routing), or the route stage writes them instead of the packed rows (xq_out)
+    const int stride = a->xq_stride > 0 ? a->xq_stride : L.nbh * 288;
+    if (stride < L.nbh * 288 || (stride & 15)) return kErrArg;
+    if (a->xq_in != nullptr) {
+      if (!use_rows || (reinterpret_cast<uintptr_t>(a->xq_in) & 15u)) return kErrUnsupported;
+      L.xq16 = const_cast<unsigned char*>(static_cast<const unsigned char*>(a->xq_in));
+      L.xq16_stride = stride;
+    } else if (a->xq_out != nullptr) {
+      if (reinterpret_cast<uintptr_t>(a->xq_out) & 15u) return kErrAlign;
+      L.xq16 = static_cast<unsigned char*>(a->xq_out);
+      L.xq16_stride = stride;
+      L.xq = ws + lay.xq;                      // the packed rows stay in the workspace
+      L.xq_stride = L.nbh * kX8;
+    }
+  }
   if (use_rows && (!matrix_tmap(L.nbh * kW4, L.FF, a->workspace, L.tmap_gu) ||
                    !matrix_tmap(L.nbf * kW4, L.H, a->workspace, L.tmap_dn)))
     return kErrUnsupported;
@@ -1223,7 +1315,7 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
                     kRouteWarps * 32, smem, s, L);
   } else {
     if (!a->xq_in) return kErrArg;
-    rc = launch_pdl(plan_kernel, dim3(1), 128, plan_smem(L.E, L.n_max, L.K), s, L);
+    rc = launch_pdl(plan_kernel, dim3(1), 256, plan_smem(L.E, L.n_max, L.K), s, L);
   }
   if (rc != kOk) return rc;
 
@@ -1292,6 +1384,51 @@ SGR_API int sgr_ep_reduce_add_f16(uint16_t* x_f16, const float* parts, int n_par
                                                             static_cast<size_t>(part_stride),
                                                             static_cast<size_t>(count));
   return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+namespace {
+template <typename... Args>
+int launch_pdl_args(void (*kern)(Args...), dim3 grid, int threads, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, args...) == cudaSuccess ? kOk : kErrLaunch;
+}
+}  // namespace
+
+SGR_API int sgr_ep_push(const void* src, long long src_stride, long long bytes, void* const* dst,
+                        unsigned* const* flags, int world, const unsigned* step, int mul, int add,
+                        unsigned* scratch, void* stream) {
+  if (world <= 0 || bytes <= 0) return kOk;
+  if (!src || !dst || !flags || !step || !scratch || world > 64 || src_stride < 0) return kErrArg;
+  if ((reinterpret_cast<uintptr_t>(src) & 15u) || (bytes & 15) || (src_stride & 15)) return kErrAlign;
+  const int chunks = static_cast<int>(std::min<long long>(16, (bytes + 4095) / 4096));
+  return launch_pdl_args(ep_push_kernel, dim3(chunks, world), 256, as_stream(stream),
+                         static_cast<const unsigned char*>(src), static_cast<size_t>(src_stride),
+                         static_cast<size_t>(bytes), dst, flags, world, step, mul, add, scratch);
+}
+
+SGR_API int sgr_ep_reduce_add_f16_wait(uint16_t* x_f16, const float* parts, int n_parts, long long part_stride,
+                                       long long count, const unsigned* flags, const unsigned* step, int mul,
+                                       int add, void* stream) {
+  if (count <= 0 || n_parts <= 0) return kOk;
+  if (!x_f16 || !parts || part_stride < count || !flags || !step || n_parts > 128) return kErrArg;
+  const int blocks = static_cast<int>(std::min<long long>((count + 255) / 256, 148 * 2));
+  return launch_pdl_args(ep_reduce_add_wait_kernel, dim3(blocks), 256, as_stream(stream), x_f16, parts, n_parts,
+                         static_cast<size_t>(part_stride), static_cast<size_t>(count), flags, step, mul, add,
+                         status_word());
+}
+
+SGR_API int sgr_ep_step_advance(unsigned* step, void* stream) {
+  if (!step) return kErrArg;
+  return launch_pdl_args(ep_step_kernel, dim3(1), 32, as_stream(stream), step);
 }
 
 SGR_API size_t sgr_moe_layer_static_limit(void) { return kStaticWsBytes; }

@@ -24,10 +24,11 @@ import torch.distributed as dist
 Q8K_BYTES = 276
 
 
-def record_layout(hidden: int, k: int):
-    """Byte layout of one dispatched token record: Q8_K row, k+1 ids, k+1 weights,
-    padded to 16 bytes. -> (record_bytes, idx_offset, w_offset)."""
-    xq = hidden // 256 * Q8K_BYTES
+def record_layout(hidden: int, k: int, padded: bool = False):
+    """Byte layout of one dispatched token record: Q8_K row (packed 276-byte blocks, or
+    288-byte blocks when `padded`), k+1 ids, k+1 weights, padded to 16 bytes.
+    -> (record_bytes, idx_offset, w_offset)."""
+    xq = hidden // 256 * (288 if padded else Q8K_BYTES)
     idx_off = xq
     w_off = xq + (k + 1) * 4
     rec = (w_off + (k + 1) * 4 + 15) // 16 * 16
@@ -38,9 +39,10 @@ class EpExchange:
     """The two fixed-capacity all-to-alls of a layer, on whatever device the buffers
     live (NCCL on GPUs; gloo on CPU in the host-logic tests)."""
 
-    def __init__(self, world, rank, n_home, hidden, k, device):
+    def __init__(self, world, rank, n_home, hidden, k, device, padded=False):
         self.world, self.rank, self.n_home, self.hidden, self.k = world, rank, n_home, hidden, k
-        self.rec, self.idx_off, self.w_off = record_layout(hidden, k)
+        self.padded = padded
+        self.rec, self.idx_off, self.w_off = record_layout(hidden, k, padded)
         self.send = torch.zeros(world, n_home, self.rec, dtype=torch.uint8, device=device)
         self.recv = torch.zeros(world, n_home, self.rec, dtype=torch.uint8, device=device)
         self.part = torch.zeros(world, n_home, hidden, dtype=torch.float32, device=device)
@@ -58,15 +60,79 @@ class EpExchange:
         dist.all_to_all_single(self.back.view(-1), self.part.view(-1))
 
 
+class PeerExchange:
+    """The same two exchanges as stores into peer memory over NVLink: `recv`, `back` and the
+    arrival words live in one symmetric-memory buffer that every rank has mapped; a rank's
+    kernels write its records / partial sums straight into the owners' / home ranks' slots
+    (sgr_ep_push) and the consumer kernels wait for the arrival words (bounded). No library
+    collective touches the data path."""
+
+    def __init__(self, world, rank, n_home, hidden, k, device, padded=False):
+        import torch.distributed._symmetric_memory as symm
+        self.world, self.rank, self.n_home, self.hidden, self.k = world, rank, n_home, hidden, k
+        self.padded = padded
+        self.rec, self.idx_off, self.w_off = record_layout(hidden, k, padded)
+        slot_r, slot_b = n_home * self.rec, n_home * hidden * 4
+        off_recv, off_back = 0, world * slot_r
+        off_flag_d = off_back + world * slot_b
+        off_flag_r = off_flag_d + 256
+        total = off_flag_r + 256
+        assert slot_r % 16 == 0 and slot_b % 16 == 0 and world <= 64
+        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        hdl = symm.rendezvous(self.buf, dist.group.WORLD.group_name)
+        base = [int(p) for p in hdl.buffer_ptrs]
+        u8, f32, i32 = torch.uint8, torch.float32, torch.int32
+        self.recv = self.buf[off_recv:off_recv + world * slot_r].view(world, n_home, self.rec)
+        self.back = self.buf[off_back:off_back + world * slot_b].view(f32).view(world, n_home, hidden)
+        self.flag_d = self.buf[off_flag_d:off_flag_d + 4 * world].view(i32)      # set by the dispatching peers
+        self.flag_r = self.buf[off_flag_r:off_flag_r + 4 * world].view(i32)      # set by the returning owners
+        self.send = torch.zeros(n_home, self.rec, dtype=u8, device=device)
+        self.part = torch.zeros(world, n_home, hidden, dtype=f32, device=device)
+        i64 = torch.int64
+        # this rank's addresses of its slot in every peer's buffer
+        self.dst_recv = torch.tensor([base[p] + off_recv + rank * slot_r for p in range(world)], dtype=i64, device=device)
+        self.dst_back = torch.tensor([base[p] + off_back + rank * slot_b for p in range(world)], dtype=i64, device=device)
+        self.dst_flag_d = torch.tensor([base[p] + off_flag_d + rank * 4 for p in range(world)], dtype=i64, device=device)
+        self.dst_flag_r = torch.tensor([base[p] + off_flag_r + rank * 4 for p in range(world)], dtype=i64, device=device)
+        self.step = torch.zeros(1, dtype=i32, device=device)
+        self.scratch = torch.zeros(2, dtype=i32, device=device)
+        self.slot_r, self.slot_b = slot_r, slot_b
+        dist.barrier()
+        torch.cuda.synchronize()
+
+
 class EpStack:
-    def __init__(self, layers, tokens, n_used, device, rank, world, biases, inputs, x0):
+    def __init__(self, layers, tokens, n_used, device, rank, world, biases, inputs, x0, peer=None):
         from .layer import MoeLayerRunner
         w0 = layers[0]
         self.layers, self.device, self.rank, self.world = layers, device, rank, world
         self.tokens, self.k = tokens, n_used
         self.n_home = tokens // world
         lo, hi = w0.lo, w0.hi
-        self.ex = EpExchange(world, rank, self.n_home, w0.hidden, n_used, device)
+        # records carry the Q8 rows in 288-byte blocks when the owner runs the row-streaming kernel,
+        # which then reads them in place
+        self.padded = device != "cpu" and tokens >= 16
+        # peer-memory exchange when the ranks can map each other's memory, NCCL all-to-alls otherwise
+        if peer is None:
+            peer = world > 1 and device != "cpu" and os.environ.get("SGR_EP_EXCHANGE", "peer") == "peer"
+        self.peer = None
+        if peer:
+            try:
+                self.peer = PeerExchange(world, rank, self.n_home, w0.hidden, n_used, device, padded=self.padded)
+            except Exception as e:                      # no symmetric memory on this system
+                if rank == 0:
+                    print(f"peer-memory exchange unavailable ({type(e).__name__}: {e}); using NCCL all-to-alls",
+                          file=__import__("sys").stderr)
+                self.peer = None
+        # every rank must take the same path
+        if world > 1 and device != "cpu":
+            ok = torch.tensor([1 if self.peer is not None else 0], device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                self.peer = None
+        self.ex = (EpExchange(world, rank, self.n_home, w0.hidden, n_used, device, padded=self.padded)
+                   if self.peer is None else None)
         self.home = MoeLayerRunner(self.n_home, w0.hidden, w0.n_ff, w0.n_expert, n_used, device)
         self.owner = MoeLayerRunner(tokens, w0.hidden, w0.n_ff, w0.n_expert, n_used, device,
                                     expert_lo=lo, expert_hi=hi)
@@ -77,12 +143,51 @@ class EpStack:
         self.x0 = x0[h0:h0 + self.n_home].contiguous()
         self.x = self.x0.clone()
         self.graph = None
-        self.launches_per_step = 4 * len(layers)     # route, plan, experts, reduce
+        self.launches_per_step = (6 if self.peer is not None else 4) * len(layers)   # route, (push,) plan, experts, (push,) reduce
+        self.n_layers = len(layers)
 
     def _ptr(self, t, off=0):
         return C.c_void_p(t.data_ptr() + off)
 
+    def issue_layer_peer(self, li):
+        """One layer with the exchanges as stores into peer memory."""
+        from .capi import lib
+        from .ops import stream_ptr
+        w, px = self.layers[li], self.peer
+        L, sp = lib(), stream_ptr()
+        mul, add = self.n_layers, li + 1               # arrival value of this layer in this step
+        a = self.home.args(self.n_home, self.inputs[li], w.router, self.tables[li], None, x_f16=self.x,
+                           bias=None if self.biases is None else self.biases[li])
+        a.xq_out = self._ptr(px.send)
+        a.xq_stride = px.rec
+        a.route_idx = self._ptr(px.send, px.idx_off)
+        a.route_w = self._ptr(px.send, px.w_off)
+        a.route_stride = px.rec // 4
+        a.xq_padded = int(self.padded)
+        L.call("sgr_moe_layer_decode_stages", C.byref(a), 1 | 8, sp)
+        L.call("sgr_ep_push", self._ptr(px.send), 0, px.slot_r, self._ptr(px.dst_recv), self._ptr(px.dst_flag_d),
+               self.world, self._ptr(px.step), mul, add, self._ptr(px.scratch), sp)
+        h0 = self.rank * self.n_home
+        b = self.owner.args(self.tokens, None, None, self.tables[li], w.shared_ptrs(), out_f32=px.part,
+                            xq_in=px.recv, routing_given=True, no_residual=True, shared_lo=h0,
+                            shared_hi=h0 + self.n_home)
+        b.xq_stride = px.rec
+        b.route_idx = self._ptr(px.recv, px.idx_off)
+        b.route_w = self._ptr(px.recv, px.w_off)
+        b.route_stride = px.rec // 4
+        b.wait_flags, b.wait_step = self._ptr(px.flag_d), self._ptr(px.step)
+        b.wait_count, b.wait_mul, b.wait_add = self.world, mul, add
+        b.xq_padded = int(self.padded)
+        L.call("sgr_moe_layer_decode_stages", C.byref(b), 7, sp)
+        L.call("sgr_ep_push", self._ptr(px.part), px.slot_b, px.slot_b, self._ptr(px.dst_back), self._ptr(px.dst_flag_r),
+               self.world, self._ptr(px.step), mul, add, self._ptr(px.scratch, 4), sp)
+        n = self.n_home * w.hidden
+        L.call("sgr_ep_reduce_add_f16_wait", self._ptr(self.x), self._ptr(px.back), self.world, n, n,
+               self._ptr(px.flag_r), self._ptr(px.step), mul, add, sp)
+
     def issue_layer(self, li):
+        if self.peer is not None:
+            return self.issue_layer_peer(li)
         from .capi import lib
         from .ops import stream_ptr
         w, ex = self.layers[li], self.ex
@@ -94,6 +199,7 @@ class EpStack:
         a.route_idx = self._ptr(ex.send, ex.idx_off)
         a.route_w = self._ptr(ex.send, ex.w_off)
         a.route_stride = ex.rec // 4
+        a.xq_padded = int(self.padded)
         lib().call("sgr_moe_layer_decode_stages", C.byref(a), 1 | 8, stream_ptr())
         ex.dispatch()
         # 2. owner: the local experts over every received row, weighted, no residual
@@ -105,6 +211,7 @@ class EpStack:
         b.route_idx = self._ptr(ex.recv, ex.idx_off)
         b.route_w = self._ptr(ex.recv, ex.w_off)
         b.route_stride = ex.rec // 4
+        b.xq_padded = int(self.padded)
         lib().call("sgr_moe_layer_decode_stages", C.byref(b), 7, stream_ptr())
         ex.combine()
         # 3. home: residual += sum over owner ranks
@@ -115,6 +222,10 @@ class EpStack:
     def step_eager(self):
         for li in range(len(self.layers)):
             self.issue_layer(li)
+        if self.peer is not None:
+            from .capi import lib
+            from .ops import stream_ptr
+            lib().call("sgr_ep_step_advance", self._ptr(self.peer.step), stream_ptr())
 
     def capture(self):
         s = torch.cuda.Stream(device=self.device)
@@ -170,6 +281,24 @@ def run_ep_bench(args, rank, world, device):
 
     for _ in range(args.warmup):
         step()
+    check = None
+    if getattr(args, "check", False):
+        # every rank's home rows after one step, against the single-GPU fused layer on rank 0
+        step()
+        torch.cuda.synchronize()
+        parts = [torch.empty_like(st.x) for _ in range(world)]
+        dist.all_gather(parts, st.x)
+        if rank == 0:
+            from .layer import MoeStack
+            full = [synth.MoeWeights(H, FF, E, device, seed=bench.SEED + li) for li in range(layers_n)]
+            ref = MoeStack(full, tokens, K, device, biases=biases, inputs=inputs)
+            ref.x.copy_(x0)
+            ref.step_eager(tokens)
+            torch.cuda.synchronize()
+            got = torch.cat(parts).float()
+            want = ref.x.float()
+            check = float((got - want).abs().max() / want.abs().max())
+            del full, ref
     sampler = bench.ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
     sampler.start()
     ms_step = timed(step, args.steps)
@@ -200,7 +329,9 @@ def run_ep_bench(args, rank, world, device):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8 dots, fp32 accumulate", "data": "synthetic",
         "config": dict(bench.workload_config(world), zipf_alpha=alpha,
-                       exchange="2 NCCL all-to-alls per layer, fixed capacity, captured in the step graph"),
+                       exchange=("records and partial sums stored into peer memory over NVLink by the library's "
+                                 "own kernels, arrival words, captured in the step graph") if st.peer is not None
+                       else "2 NCCL all-to-alls per layer, fixed capacity, captured in the step graph"),
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": int(h_in.numel() * 2) * world,
                 "d2h_bytes_per_step": int(h_out.numel() * 2) * world},
@@ -211,4 +342,6 @@ def run_ep_bench(args, rank, world, device):
     }
     if status != 0:
         line["device_status"] = "a bounded device-side wait gave up"
+    if check is not None:
+        line["check_max_rel_err_vs_single_gpu"] = check
     return line

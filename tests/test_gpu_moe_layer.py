@@ -217,7 +217,8 @@ def test_stack_graph_replay_is_deterministic(oracle):
     assert lib().raw("sgr_status")(0) == 0
 
 
-def test_expert_parallel_record_path_on_one_device(full_w):
+@pytest.mark.parametrize("padded", [False, True])
+def test_expert_parallel_record_path_on_one_device(full_w, padded):
     """The expert-parallel layer with its exchanges done by hand on one device: each
     emulated rank routes its home rows straight into dispatch records (strided Q8_K
     rows, ids, weights), every rank's owner call runs its expert range over all
@@ -230,7 +231,7 @@ def test_expert_parallel_record_path_on_one_device(full_w):
     n_home = tokens // world
     x16 = synth.normal_fp16((tokens, w.hidden), 91, DEV)
     _, x_full, out_full = run_layer(w, tokens, k, x16, n_max=64)
-    rec, idx_off, w_off = record_layout(w.hidden, k)
+    rec, idx_off, w_off = record_layout(w.hidden, k, padded)      # padded: Q8 rows in 288-byte blocks, read in place
     records = torch.zeros(world, n_home, rec, dtype=torch.uint8, device=DEV)
     for r in range(world):                                    # home side of every rank
         home = MoeLayerRunner(n_home, w.hidden, w.n_ff, w.n_expert, k, DEV)
@@ -240,6 +241,7 @@ def test_expert_parallel_record_path_on_one_device(full_w):
         a.xq_out, a.xq_stride = C.c_void_p(base), rec
         a.route_idx, a.route_w = C.c_void_p(base + idx_off), C.c_void_p(base + w_off)
         a.route_stride = rec // 4
+        a.xq_padded = int(padded)
         lib().call("sgr_moe_layer_decode_stages", C.byref(a), 1 | 8, stream_ptr())
     torch.cuda.synchronize()
     total = x16.float().clone()
@@ -252,6 +254,7 @@ def test_expert_parallel_record_path_on_one_device(full_w):
                        routing_given=True, no_residual=True, shared_lo=r * n_home,
                        shared_hi=(r + 1) * n_home)
         b.xq_stride, b.route_stride = rec, rec // 4
+        b.xq_padded = int(padded)
         b.route_idx = C.c_void_p(records.data_ptr() + idx_off)
         b.route_w = C.c_void_p(records.data_ptr() + w_off)
         lib().call("sgr_moe_layer_decode_stages", C.byref(b), 7, stream_ptr())
@@ -267,3 +270,25 @@ def test_expert_parallel_record_path_on_one_device(full_w):
     for p_ in range(world):
         want = want + parts[p_]
     assert torch.equal(xh, want.half())
+
+
+def test_route_only_stage_repeats_on_one_workspace(full_w):
+    """The home side of expert parallelism calls the route stage without the plan once per layer on
+    one workspace: the second call must route its own rows (its per-tile counters start at zero
+    again), not leave the first call's routing in place."""
+    import ctypes as C
+    from sager_b200.ops import stream_ptr
+    w, k, n = full_w, 8, 32
+    runner = MoeLayerRunner(n, w.hidden, w.n_ff, w.n_expert, k, DEV)
+    picks = []
+    for seed in (301, 302):
+        x16 = synth.normal_fp16((n, w.hidden), seed, DEV)
+        a = runner.args(n, x16, w.router, w.table(), None,
+                        x_f16=torch.zeros(n, w.hidden, dtype=torch.float16, device=DEV))
+        lib().call("sgr_moe_layer_decode_stages", C.byref(a), 1 | 8, stream_ptr())
+        torch.cuda.synchronize()
+        idx = runner.route_idx.cpu().numpy()[:n, :k].copy()
+        want = (x16.float() @ w.router.t()).topk(k, dim=1).indices.cpu().numpy()
+        assert np.array_equal(np.sort(idx, axis=1), np.sort(want, axis=1)), seed
+        picks.append(idx)
+    assert not np.array_equal(picks[0], picks[1])
