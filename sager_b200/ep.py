@@ -248,7 +248,7 @@ def run_ep_bench(args, rank, world, device):
     from . import synth
     from .capi import lib
     E, K, H, FF = bench.E, bench.K, bench.H, bench.FF
-    layers_n, tokens = bench.LAYERS, bench.TOKENS
+    layers_n, tokens = args.layers, args.tokens     # (`bench` imported here is a second copy of the script's module)
     assert E % world == 0 and tokens % world == 0
     lo, hi = rank * (E // world), (rank + 1) * (E // world)
     ws = [synth.MoeWeights(H, FF, E, device, seed=bench.SEED + li, expert_range=(lo, hi))
@@ -328,7 +328,7 @@ def run_ep_bench(args, rank, world, device):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8 dots, fp32 accumulate", "data": "synthetic",
-        "config": dict(bench.workload_config(world), zipf_alpha=alpha,
+        "config": dict(bench.workload_config(world), layers=layers_n, tokens=tokens, zipf_alpha=alpha,
                        exchange=("records and partial sums stored into peer memory over NVLink by the library's "
                                  "own kernels, arrival words, captured in the step graph") if st.peer is not None
                        else "2 NCCL all-to-alls per layer, fixed capacity, captured in the step graph"),
