@@ -346,6 +346,75 @@ def run_prefill_bench(args, device):
     print(json.dumps(line))
 
 
+def run_gemv_bench(args, device):
+    """Dense Q4_K x Q8_K GEMV sweep (config[1]): the five shapes at batch 1 and 4, weights drawn
+    from N(0, 0.02), activations from N(0, 1) and Q8-quantised by the library. Each shape is timed
+    over enough distinct weight copies to exceed L2 (the small matrices would otherwise be served
+    from it), CUDA events around the loop; GB/s counts the weight bytes only."""
+    import torch
+    from sager_b200 import lib, ops, synth
+    peak, kind = load_peaks()
+    shapes = [(4096, 2048), (2048, 4096), (512, 2048), (2048, 512), (151936, 2048)]
+    rows_out = []
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    for rows, k in shapes:
+        wbytes = rows * (k // 256) * 144
+        copies = max(1, min(512, (192 << 20) // wbytes + 1))       # > 126 MB L2 in flight per sweep
+        g = torch.Generator(device=device).manual_seed(SEED + rows)
+        w1 = synth.quantize_q4k(torch.randn(min(rows, 4096), k, generator=g, device=device) * 0.02).reshape(-1)
+        w = torch.empty(copies, wbytes, dtype=torch.uint8, device=device)
+        for c in range(copies):
+            for r0 in range(0, wbytes, w1.numel()):
+                n = min(w1.numel(), wbytes - r0)
+                w[c, r0:r0 + n] = w1[:n]
+        for batch in (1, 4):
+            x = synth.normal_fp16((batch, k), SEED + k + batch, device)
+            xq = torch.empty(batch, k // 256 * 276, dtype=torch.uint8, device=device)
+            ops.quantize_q8_k(x, xq, batch * k)
+            y = torch.zeros(batch, rows, dtype=torch.float32, device=device)
+            def sweep():
+                for c in range(copies):
+                    if batch == 1:
+                        ops.gemv_q4_k_q8(w[c], xq, y, rows, k)
+                    else:
+                        ops.gemv_q4_k_q8_batched(w[c], xq, y, rows, k, batch)
+            sweep()                                   # sets function attributes outside capture
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()                # launches back to back, no host time between them
+            with torch.cuda.graph(graph):
+                sweep()
+            for _ in range(max(args.warmup, 3)):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (args.steps * copies)
+            rows_out.append({"rows": rows, "k": k, "batch": batch, "us": us, "gbs": wbytes / us / 1e3,
+                             "frac": wbytes / us / 1e3 / peak, "weight_copies": copies})
+    clocks = sampler.stop()
+    head = [r for r in rows_out if r["rows"] == 151936 and r["batch"] == 1][0]
+    line = {
+        "metric": "q4k_gemv_hbm_gbs", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": head["us"] * 1e-3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 dots, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "dense Q4_K GEMV sweep at batch 1 and 4; value = LM head 2048->151936 at batch 1",
+                   "l2": "every launch of a sweep reads a different weight copy, > 126 MB between reuses"},
+        "e2e": None, "gpu_launches": args.steps * sum(r["weight_copies"] for r in rows_out), "clocks": clocks,
+        "roofline": {"kernel": "gemv tile kernels (gemv.cu)", "bound": "hbm", "achieved": head["gbs"], "peak": peak,
+                     "unit": "GB/s", "frac": head["frac"], "peak_source": f"{kind} copy bandwidth (burst)",
+                     "traffic": None},
+        "sweep": rows_out,
+    }
+    if lib().raw("sgr_status")(0) != 0:
+        line["device_status"] = "a bounded device-side wait gave up"
+    print(json.dumps(line))
+
+
 def main():
     global LAYERS, TOKENS
     ap = argparse.ArgumentParser()
@@ -358,8 +427,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=TOKENS, help="token rows per step, 1..64")
     ap.add_argument("--check", action="store_true",
                     help="N > 1: compare one step with the single-GPU layer stack on rank 0 (use with a small --layers)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                    help="decode: the 40-layer stack (default); prefill: one layer over a 2048-row chunk")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gemv"],
+                    help="decode: the 40-layer stack (default); prefill: one layer over a 2048-row chunk; "
+                         "gemv: the dense GEMV sweep")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -391,6 +461,10 @@ def main():
     if args.workload == "prefill":
         if world == 1:
             run_prefill_bench(args, device)
+        return
+    if args.workload == "gemv":
+        if world == 1:
+            run_gemv_bench(args, device)
         return
     if world > 1:
         from sager_b200.ep import run_ep_bench

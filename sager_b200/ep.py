@@ -336,7 +336,7 @@ def run_ep_bench(args, rank, world, device):
                 "h2d_bytes_per_step": int(h_in.numel() * 2) * world,
                 "d2h_bytes_per_step": int(h_out.numel() * 2) * world},
         "gpu_launches": st.launches_per_step * args.steps, "clocks": clocks,
-        "roofline": {"kernel": "expert_stream_kernel", "bound": "hbm", "achieved": None, "peak": bench.load_peaks()[0],
+        "roofline": {"kernel": "expert_rows_kernel", "bound": "hbm", "achieved": None, "peak": bench.load_peaks()[0],
                      "unit": "GB/s", "frac": None, "traffic": None,
                      "note": "per-kernel timing is taken at N=1; at N>1 the step is exchange-latency bound"},
     }
