@@ -1,7 +1,8 @@
 // expert_rows.cuh - the expert kernel for layers with many token rows (part of
 // moe_layer.cu, which defines LayerDev and the plan before including this file).
 //
-// A persistent kernel, one CTA per SM, 16 consumer warps and 4 producer warps.
+// A persistent kernel, one CTA per SM: 16 consumer warps, a weight warp, three
+// activation warps and a finisher warp.
 // Work is cut into groups: 128 (gate, up) row pairs of one tile (up to 16 token
 // rows of one expert), or 256 rows of its down matrix. A group is streamed through
 // a ring of shared-memory stages one super-block column at a time: a stage holds
@@ -36,10 +37,6 @@
 // Down groups write fp32 y; after a grid-wide barrier the CTAs add
 // residual + sum_k w_k * y_k + shared expert (combine_rows).
 #pragma once
-
-#ifndef SGR_RS_PREFETCH
-#define SGR_RS_PREFETCH 0
-#endif
 
 namespace rs {
 
@@ -583,11 +580,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[0][j] = acc[1][j] = 0.f;
     }
-#ifdef SGR_RS_NOCOMPUTE
-    if (false) {
-#else
     if (d_mode == 0) {
-#endif
       XTile xt;
       xt.qs = reinterpret_cast<int8_t*>(st + kWBytes);
       xt.bs = reinterpret_cast<int16_t*>(st + kWBytes + kXCodes);
@@ -601,38 +594,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
       auto row_at = [&](int u) {
         return d_kind == 0 ? ((u & 7) + 8 * warp) * kW4 + (u >> 3) * kHalfBytes : (16 * warp + u) * kW4;
       };
-#if defined(SGR_RS_EXP) && SGR_RS_EXP == 1
-      if (true) {                                // experiment: the shared-memory loads of the dp4a path, no math
-        const uint4* wrow = reinterpret_cast<const uint4*>(st + row_at(lane >> 1));
-        const int half = lane & 1;
-        uint4 v = wrow[0];
-        for (int gg = 0; gg < 2; ++gg) {
-          const int g = 2 * half + gg;
-          const uint4 q0 = wrow[1 + 2 * g], q1 = wrow[2 + 2 * g];
-          v.x ^= q0.x ^ q1.y; v.y ^= q0.z ^ q1.w;
-          for (int t = 0; t < 2; ++t) if (t < d_ntok) {
-            const uint4* xa = xt.codes(t, 0, 2 * g);
-            v.z ^= xa[0].x ^ xa[1].y ^ xa[2].z ^ xa[3].w;
-          }
-        }
-        const uint4 bs = xt.sums(0, 0);
-        acc[0][0] += __uint_as_float((v.x ^ v.y ^ v.z ^ v.w ^ bs.x) & 0x3FFFFFFFu);
-      } else if (false) {
-#elif defined(SGR_RS_EXP) && SGR_RS_EXP == 2
-      if (true) {                                // experiment: the math of the dp4a path on register data, no loads
-        uint32_t w = lane * 0x01010101u + q, x = lane * 0x00010203u + s;
-        int i0 = 0, i1 = 0;
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          i0 = __dp4a(static_cast<int>(w & 0x0F0F0F0Fu), static_cast<int>(x), i0);
-          i1 = __dp4a(static_cast<int>((w >> 4) & 0x0F0F0F0Fu), static_cast<int>(x ^ 0x55u), i1);
-          w = w * 5u + 1u; x = x * 3u + 7u;
-        }
-        acc[0][0] += static_cast<float>(i0 * 3 + i1 * 5);
-      } else if (false) {
-#else
       if (d_ntok <= 2) {
-#endif
         float a2[2] = {acc[0][0], acc[0][1]};
         half_block_dot<2>(reinterpret_cast<const uint4*>(st + row_at(lane >> 1)), lane & 1, xt, d_ntok, a2);
         acc[0][0] = a2[0];

@@ -292,3 +292,31 @@ def test_route_only_stage_repeats_on_one_workspace(full_w):
         assert np.array_equal(np.sort(idx, axis=1), np.sort(want, axis=1)), seed
         picks.append(idx)
     assert not np.array_equal(picks[0], picks[1])
+
+
+def test_peer_memory_entry_points_with_one_rank():
+    """sgr_ep_push / the waits / sgr_ep_step_advance with this device as its own only peer: the
+    bytes arrive, the arrival word takes step * mul + add, a wait on a word that is already set
+    returns, and the step counter advances in stream order."""
+    import ctypes as C
+    from sager_b200.ops import stream_ptr
+    L, sp = lib(), stream_ptr()
+    src = torch.arange(4096, dtype=torch.int32, device=DEV)
+    dst = torch.zeros(2, 4096, dtype=torch.int32, device=DEV)
+    flags = torch.zeros(2, dtype=torch.int32, device=DEV)
+    step = torch.full((1,), 3, dtype=torch.int32, device=DEV)
+    scratch = torch.zeros(1, dtype=torch.int32, device=DEV)
+    dptr = torch.tensor([dst[0].data_ptr(), dst[1].data_ptr()], dtype=torch.int64, device=DEV)
+    fptr = torch.tensor([flags.data_ptr(), flags.data_ptr() + 4], dtype=torch.int64, device=DEV)
+    p = lambda t: C.c_void_p(t.data_ptr())
+    L.call("sgr_ep_push", p(src), 0, src.numel() * 4, p(dptr), p(fptr), 2, p(step), 5, 2, p(scratch), sp)
+    torch.cuda.synchronize()
+    assert torch.equal(dst[0], src) and torch.equal(dst[1], src)
+    assert flags.tolist() == [17, 17] and int(scratch.item()) == 0
+    x = torch.ones(1024, dtype=torch.float16, device=DEV)
+    parts = torch.full((2, 1024), 0.5, dtype=torch.float32, device=DEV)
+    L.call("sgr_ep_reduce_add_f16_wait", p(x), p(parts), 2, 1024, 1024, p(flags), p(step), 5, 2, sp)
+    L.call("sgr_ep_step_advance", p(step), sp)
+    torch.cuda.synchronize()
+    assert torch.all(x == 2.0) and int(step.item()) == 4
+    assert lib().raw("sgr_status")(0) == 0
