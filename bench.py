@@ -199,6 +199,52 @@ def cpu_pool_sample(ws0, xn0, bias0, budget_s=12.0):
     return {"t_layer_s": t_layer, "cores": cores, "kind": kind, "layers_timed": len(times)}
 
 
+def ref_cuda_decode(ws, inputs, x0, biases, n, device, steps, ours_x):
+    """The same decode step on the reference's own CUDA kernels (compiled for sm_100a into
+    oracle/_ref/libsager_ref_cuda.so) in the reference's launch sequence for its device MoE
+    path (src/core/session.cpp:2482-3030, dp4a branch), captured in a CUDA graph like the
+    reference's step graph. None when that library was not built."""
+    import torch
+    from oracle import ref_cuda
+    if not ref_cuda.available():
+        return None
+    path = ref_cuda.DeviceMoePath(ref_cuda.reference_launchers(), n, H, FF, E, K, device)
+    x = x0.clone()
+    tables = [w.table() for w in ws]
+
+    def issue():
+        for li, w in enumerate(ws):
+            path.run(n, inputs[li], x, w.router, tables[li], w.shared_ptrs(), bias=biases[li])
+
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        issue()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    diff = float((x.float() - ours_x.float()).abs().max() / ours_x.float().abs().max())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        issue()
+    for _ in range(3):
+        x.copy_(x0, non_blocking=True)
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        x.copy_(x0, non_blocking=True)
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"value": n / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+            "kind": "the reference's CUDA kernels built for sm_100a, its device MoE launch sequence "
+                    "(dp4a branch), one CUDA graph per step",
+            "launches_per_step": (path.launches + 2) * len(ws),
+            "max_rel_diff_vs_this_library_after_one_step": diff}
+
+
 def _port_batch(o, w3_ptrs, xs, cores):
     """expert_ffn_batch on raw addresses (the C port takes void* either way)."""
     import ctypes as C
@@ -584,6 +630,15 @@ def main():
             "kind": res["kind"],
             "sample": f"layer 0 of the stack ({n} rows: router + {n * (K + 1)} expert FFNs through the "
                       f"CPU pool), median of {res['layers_timed']} runs; step time = {LAYERS} x layer time"}
+        stack.x.copy_(x0)
+        stack.replay()
+        torch.cuda.synchronize()
+        try:
+            gpu_ref = ref_cuda_decode(ws, inputs, x0, biases, n, device, max(3, min(args.steps, 10)), stack.x)
+        except Exception as exc:                      # a baseline, never a reason to lose the line
+            gpu_ref = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+        if gpu_ref is not None:
+            line["gpu_baseline"] = gpu_ref
     print(json.dumps(line))
 
 

@@ -267,6 +267,41 @@ int sgr_moe_layer_decode_stages(const sgr_moe_layer* args, int stages, void* str
 int sgr_moe_grouped_gemm_i8(const void* const* w_tab, const int* off, const void* xq, uint16_t* y,
                             int n_rows, int k, int n_expert, void* stream);
 
+/* ---- the fp16 tensor-core family of the prefill path (cuda_ops.hpp:104-152) ----------------
+ * The reference dequantises Q4_K to fp16 and calls a library GEMM; here the GEMM is the
+ * library's own tcgen05 kernel (kind::f16, fp32 accumulation in tensor memory, TMA operand
+ * tiles). Layout contract of all of them: y[t * n_rows + row] = sum_k x[t * k + kk] * w[row * k + kk].
+ * Where the reference returns bool, 0 means "ran" and a non-zero code means "not run, take the
+ * GEMV path" (SGR_EUNSUPPORTED / SGR_EALIGN for the reference's own refusals). w16, x16 and the
+ * scratch must be 16-byte aligned and k a multiple of 64. */
+/* tc_handle (cuda_ops.hpp:112): non-null when the tensor-core path can run on this driver. */
+void* sgr_tc_handle(void);
+/* tc_scratch_elems (cuda_ops.hpp:113). */
+size_t sgr_tc_scratch_elems(int max_rows, int max_k);
+/* tc_gemm_q4_k_f16 (cuda_ops.hpp:109-111): dequantise w into scratch, then the GEMM. */
+int sgr_tc_gemm_q4_k_f16(const void* w, const uint16_t* x, uint16_t* y, uint16_t* scratch, int n_rows,
+                         int k, int n_tokens, void* stream);
+/* tc_gemm_f16_raw (cuda_ops.hpp:125-126). */
+int sgr_tc_gemm_f16_raw(const void* w16, const void* x16, void* y16, int n_rows, int k, int n_tokens,
+                        void* stream);
+/* tc_gemm_f16_f32out_raw (cuda_ops.hpp:137-139). */
+int sgr_tc_gemm_f16_f32out_raw(const void* w16, const void* x16, float* y32, int n_rows, int k,
+                               int n_tokens, void* stream);
+/* dequant_experts_q4_k_f16 (cuda_ops.hpp:127-131): routed experts into a ring of fp16 slots; slot
+ * e % ring, rows_per = 1 << rows_sl2 rows of k halfs from element dst_row0; with tab_b the second
+ * half of the rows reads tab_b[e]; experts with no routed rows or a null entry are skipped. */
+int sgr_dequant_experts_q4_k_f16(const void* const* tab_a, const void* const* tab_b, const int* off,
+                                 void* slots, long long dst_row0, int rows_sl2, int k, int n_experts,
+                                 int ring, long long slot_elems, void* stream);
+/* The dense dequantisation tc_gemm_q4_k_f16 starts with, on its own: out16[row * k + i]. */
+int sgr_dequant_q4_k_f16(const void* w, uint16_t* out16, int n_rows, int k, void* stream);
+/* tc_router_f32 (cuda_ops.hpp:143-145): router weights cast to fp16 in scratch, fp32 logits. */
+int sgr_tc_router_f32(const float* w_f32, const uint16_t* x, float* y, uint16_t* scratch, int n_rows,
+                      int k, int n_tokens, void* stream);
+/* Operand tile layout of the GEMM kernel: 0 = 128-byte swizzled tiles (default), 1 = unswizzled
+ * core matrices. Same results; a diagnostic, not part of the reference's surface. */
+int sgr_tc_set_operand_layout(int layout);
+
 /* Expert parallelism, last step on the home rank (no counterpart in the reference, which is
  * single-GPU): x[i] = f16(f32(x[i]) + sum_p parts[p*part_stride + i]), p ascending. */
 int sgr_ep_reduce_add_f16(uint16_t* x_f16, const float* parts, int n_parts, long long part_stride,

@@ -65,6 +65,13 @@ void sigmoid_gate_scalar_batched_f16(uint16_t* out, const float* g, int n_rows, 
 void moe_combine_f16(uint16_t* out, const uint16_t* expert_out, const int* idx, const float* weight, int n_expert_used, int hidden, cudaStream_t stream);
 void moe_combine_batched_f16(uint16_t* out, const uint16_t* expert_y, const float* weight, int n_used, int hidden, int n_rows, cudaStream_t stream);
 void moe_combine_add_slots_f16(uint16_t* out, const uint16_t* expert_y, const float* weight, const int* rk, int n_used, int hidden, int n_list, cudaStream_t stream);
+bool tc_gemm_q4_k_f16(const q4k::BlockQ4K* w, const uint16_t* x, uint16_t* y, uint16_t* scratch, int n_rows, int k, int n_tokens, cudaStream_t stream);
+void* tc_handle();
+size_t tc_scratch_elems(int max_rows, int max_k);
+bool tc_gemm_f16_raw(const void* w16, const void* x16, void* y16, int n_rows, int k, int n_tokens, cudaStream_t stream);
+void dequant_experts_q4_k_f16(const q4k::BlockQ4K* const* tab_a, const q4k::BlockQ4K* const* tab_b, const int* off, void* slots, long long dst_row0, int rows_sl2, int k, int n_experts, int ring, long long slot_elems, cudaStream_t stream);
+bool tc_gemm_f16_f32out_raw(const void* w16, const void* x16, float* y32, int n_rows, int k, int n_tokens, cudaStream_t stream);
+void tc_router_f32(const float* w_f32, const uint16_t* x, float* y, uint16_t* scratch, int n_rows, int k, int n_tokens, cudaStream_t stream);
 
 #ifdef SAGER_B200_SHIM_IMPLEMENTATION
 namespace b200_detail {
@@ -180,6 +187,23 @@ void moe_combine_batched_f16(uint16_t* out, const uint16_t* expert_y, const floa
 }
 void moe_combine_add_slots_f16(uint16_t* out, const uint16_t* expert_y, const float* weight, const int* rk, int n_used, int hidden, int n_list, cudaStream_t stream) {
   b200_detail::note(sgr_moe_combine_add_slots_f16(out, expert_y, weight, rk, n_used, hidden, n_list, stream));
+}
+bool tc_gemm_q4_k_f16(const q4k::BlockQ4K* w, const uint16_t* x, uint16_t* y, uint16_t* scratch, int n_rows, int k, int n_tokens, cudaStream_t stream) {
+  return sgr_tc_gemm_q4_k_f16(w, x, y, scratch, n_rows, k, n_tokens, stream) == 0;
+}
+void* tc_handle() { return sgr_tc_handle(); }
+size_t tc_scratch_elems(int max_rows, int max_k) { return sgr_tc_scratch_elems(max_rows, max_k); }
+bool tc_gemm_f16_raw(const void* w16, const void* x16, void* y16, int n_rows, int k, int n_tokens, cudaStream_t stream) {
+  return sgr_tc_gemm_f16_raw(w16, x16, y16, n_rows, k, n_tokens, stream) == 0;
+}
+void dequant_experts_q4_k_f16(const q4k::BlockQ4K* const* tab_a, const q4k::BlockQ4K* const* tab_b, const int* off, void* slots, long long dst_row0, int rows_sl2, int k, int n_experts, int ring, long long slot_elems, cudaStream_t stream) {
+  b200_detail::note(sgr_dequant_experts_q4_k_f16(reinterpret_cast<const void* const*>(tab_a), reinterpret_cast<const void* const*>(tab_b), off, slots, dst_row0, rows_sl2, k, n_experts, ring, slot_elems, stream));
+}
+bool tc_gemm_f16_f32out_raw(const void* w16, const void* x16, float* y32, int n_rows, int k, int n_tokens, cudaStream_t stream) {
+  return sgr_tc_gemm_f16_f32out_raw(w16, x16, y32, n_rows, k, n_tokens, stream) == 0;
+}
+void tc_router_f32(const float* w_f32, const uint16_t* x, float* y, uint16_t* scratch, int n_rows, int k, int n_tokens, cudaStream_t stream) {
+  b200_detail::note(sgr_tc_router_f32(w_f32, x, y, scratch, n_rows, k, n_tokens, stream));
 }
 #endif  // SAGER_B200_SHIM_IMPLEMENTATION
 

@@ -31,6 +31,8 @@ def build(ref_root: str = "/root/reference") -> None:
     if os.path.isdir(ref_root):
         subprocess.check_call(["make", "-s", "-C", HERE, "ref", f"REF={ref_root}"],
                               stderr=subprocess.DEVNULL)
+        subprocess.check_call(["make", "-s", "-C", HERE, "refcuda", f"REF={ref_root}"],
+                              stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
 
 
 def _ptr(a):

@@ -34,8 +34,8 @@ def parse_header(path: str = HEADER):
     text = open(path).read()
     text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
     protos = {}
-    for m in re.finditer(r"\b(int|void|size_t)\s+(sgr_\w+)\s*\(([^)]*)\)\s*;", text):
-        ret, name, args = m.group(1), m.group(2), m.group(3).strip()
+    for m in re.finditer(r"\b(int|void\s*\*|void|size_t)\s*(sgr_\w+)\s*\(([^)]*)\)\s*;", text):
+        ret, name, args = "".join(m.group(1).split()), m.group(2), m.group(3).strip()
         argtypes = []
         if args and args != "void":
             for a in args.split(","):
@@ -45,7 +45,7 @@ def parse_header(path: str = HEADER):
                 else:
                     base = a.rsplit(" ", 1)[0].replace("const ", "").strip()
                     argtypes.append(_SCALARS[base])
-        protos[name] = ({"int": C.c_int, "size_t": C.c_size_t, "void": None}[ret], argtypes)
+        protos[name] = ({"int": C.c_int, "size_t": C.c_size_t, "void": None, "void*": C.c_void_p}[ret], argtypes)
     return protos
 
 

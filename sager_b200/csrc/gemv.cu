@@ -174,6 +174,10 @@ int launch_dense(const void* w0, const void* w1, const void* xq, void* y0, void*
     a.tok_tile = 1;
     return launch_tile<NMAT, 1, kDense, F16>(a, dim3((n_rows + rc - 1) / rc, 1), stream);
   }
+  if (n_tokens <= 4) {              // a verify window: dp4a over four token slots beats the MMA fragment set-up
+    a.tok_tile = 4;
+    return launch_tile<NMAT, 4, kDense, F16>(a, dim3((n_rows + rc - 1) / rc, 1), stream);
+  }
   a.tok_tile = kDenseTokTile;
   return launch_tile<NMAT, 8, kDense, F16>(
       a, dim3((n_rows + rc - 1) / rc, (n_tokens + kDenseTokTile - 1) / kDenseTokTile), stream);

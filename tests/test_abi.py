@@ -29,6 +29,11 @@ def test_argument_validation_needs_no_gpu():
     assert lib.raw("sgr_quantize_q8_k")(16, 16, 100, None) == 1
     assert lib.raw("sgr_router_topk_batched")(16, 16, 16, 256, 8, 8, 1, 1.0, None) == 1  # stride < K+1
     assert lib.raw("sgr_gemv_q4_k_q8")(16, 16, 16, 0, 2048, None) == 0      # empty: nothing to do
+    # the tensor-core family refuses what the reference refuses, before any CUDA call
+    assert lib.raw("sgr_tc_gemm_f16_raw")(16, 16, 16, 8, 100, 4, None) == 3          # k % 64 != 0
+    assert lib.raw("sgr_tc_gemm_f16_raw")(18, 16, 16, 8, 64, 4, None) == 2           # operand not 16-byte aligned
+    assert lib.raw("sgr_tc_gemm_q4_k_f16")(16, 16, 16, 16, 8, 768, 4, None) == 3     # k not a power of two
+    assert lib.raw("sgr_tc_scratch_elems")(512, 2048) == 512 * 2048
 
 
 def test_shim_header_compiles_against_c_abi():

@@ -96,8 +96,9 @@ def test_gemv_sweep_vs_oracle(oracle, rows, k, batch):
     assert f16_close(y16.cpu().numpy(), want)
 
 
-def test_multi_token_variants_agree(oracle):
-    rows, k, tok = 512, 2048, 5
+@pytest.mark.parametrize("tok", [2, 4, 5, 19])
+def test_multi_token_variants_agree(oracle, tok):
+    rows, k = 512, 2048
     w_np, w_dev = make_q4k(rows, k, 1)
     w2_np, w2_dev = make_q4k(rows, k, 2)
     x_np, x_dev = make_x16(tok, k, 1234, std=0.6)
