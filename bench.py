@@ -469,6 +469,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gpu-baseline", action="store_true",
+                    help="skip the leg that times the reference's own CUDA kernels on this GPU")
     ap.add_argument("--layers", type=int, default=LAYERS, help="shrink the stack (profiling captures)")
     ap.add_argument("--tokens", type=int, default=TOKENS, help="token rows per step, 1..64")
     ap.add_argument("--check", action="store_true",
@@ -630,6 +632,7 @@ def main():
             "kind": res["kind"],
             "sample": f"layer 0 of the stack ({n} rows: router + {n * (K + 1)} expert FFNs through the "
                       f"CPU pool), median of {res['layers_timed']} runs; step time = {LAYERS} x layer time"}
+    if not args.no_gpu_baseline:
         stack.x.copy_(x0)
         stack.replay()
         torch.cuda.synchronize()
