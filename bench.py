@@ -402,6 +402,11 @@ def run_gemv_bench(args, device):
     peak, kind = load_peaks()
     shapes = [(4096, 2048), (2048, 4096), (512, 2048), (2048, 512), (151936, 2048)]
     rows_out = []
+    ref = None
+    if not args.no_gpu_baseline:
+        from oracle import ref_cuda
+        if ref_cuda.available():
+            ref = ref_cuda.reference_launchers()      # the reference's own kernels, timed on the same buffers
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
     for rows, k in shapes:
@@ -419,29 +424,36 @@ def run_gemv_bench(args, device):
             xq = torch.empty(batch, k // 256 * 276, dtype=torch.uint8, device=device)
             ops.quantize_q8_k(x, xq, batch * k)
             y = torch.zeros(batch, rows, dtype=torch.float32, device=device)
-            def sweep():
-                for c in range(copies):
-                    if batch == 1:
-                        ops.gemv_q4_k_q8(w[c], xq, y, rows, k)
-                    else:
-                        ops.gemv_q4_k_q8_batched(w[c], xq, y, rows, k, batch)
-            sweep()                                   # sets function attributes outside capture
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()                # launches back to back, no host time between them
-            with torch.cuda.graph(graph):
-                sweep()
-            for _ in range(max(args.warmup, 3)):
-                graph.replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(args.steps):
-                graph.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / (args.steps * copies)
-            rows_out.append({"rows": rows, "k": k, "batch": batch, "us": us, "gbs": wbytes / us / 1e3,
-                             "frac": wbytes / us / 1e3 / peak, "weight_copies": copies})
+            def timed(o):
+                def sweep():
+                    for c in range(copies):
+                        if batch == 1:
+                            o.gemv_q4_k_q8(w[c], xq, y, rows, k)
+                        else:
+                            o.gemv_q4_k_q8_batched(w[c], xq, y, rows, k, batch)
+                sweep()                                   # sets function attributes outside capture
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()                # launches back to back, no host time between them
+                with torch.cuda.graph(graph):
+                    sweep()
+                for _ in range(max(args.warmup, 3)):
+                    graph.replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(args.steps):
+                    graph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                return e0.elapsed_time(e1) * 1e3 / (args.steps * copies)
+            us = timed(ops)
+            row = {"rows": rows, "k": k, "batch": batch, "us": us, "gbs": wbytes / us / 1e3,
+                   "frac": wbytes / us / 1e3 / peak, "weight_copies": copies}
+            if ref is not None:
+                ref_us = timed(ref)
+                row["reference_cuda_us"] = ref_us
+                row["reference_cuda_gbs"] = wbytes / ref_us / 1e3
+            rows_out.append(row)
     clocks = sampler.stop()
     head = [r for r in rows_out if r["rows"] == 151936 and r["batch"] == 1][0]
     line = {
@@ -455,6 +467,68 @@ def run_gemv_bench(args, device):
                      "unit": "GB/s", "frac": head["frac"], "peak_source": f"{kind} copy bandwidth (burst)",
                      "traffic": None},
         "sweep": rows_out,
+    }
+    if lib().raw("sgr_status")(0) != 0:
+        line["device_status"] = "a bounded device-side wait gave up"
+    print(json.dumps(line))
+
+
+def run_tc_bench(args, device):
+    """The fp16 tensor-core GEMM behind the tc_* entries on the prefill shapes: one projection
+    over a whole 2048-row chunk and over the 64 rows one expert gets (the reference issues one
+    GEMM per expert and matrix). Operands beyond L2 by rotating over copies."""
+    import torch
+    from sager_b200 import lib, ops
+    peak_bw, kind = load_peaks()
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
+        os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    peak_tf = float(peaks.get("bf16_tflops", 1590.0))
+    out = []
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    for rows, k, tok in [(512, 2048, 2048), (2048, 512, 2048), (512, 2048, 64), (2048, 512, 64)]:
+        copies = max(2, min(128, (192 << 20) // (rows * k * 2) + 1))
+        g = torch.Generator(device=device).manual_seed(SEED + rows + tok)
+        w = (torch.randn(copies, rows, k, generator=g, device=device) * 0.02).half()
+        x = torch.randn(tok, k, generator=g, device=device).half()
+        y = torch.zeros(tok, rows, dtype=torch.float16, device=device)
+
+        def sweep():
+            for c in range(copies):
+                ops.tc_gemm_f16_raw(w[c], x, y, rows, k, tok)
+        sweep()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            sweep()
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (args.steps * copies)
+        flops = 2.0 * rows * k * tok
+        nbytes = 2.0 * (rows * k + tok * k + tok * rows)
+        out.append({"rows": rows, "k": k, "tokens": tok, "us": us, "tflops": flops / us / 1e6,
+                    "tensor_frac": flops / us / 1e6 / peak_tf, "gbs": nbytes / us / 1e3,
+                    "hbm_frac": nbytes / us / 1e3 / peak_bw, "weight_copies": copies})
+    clocks = sampler.stop()
+    head = out[0]
+    line = {
+        "metric": "tc_gemm_f16_tflops", "value": head["tflops"], "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": head["us"] * 1e-3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp16 operands, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "tc_gemm_f16_raw on the prefill projection shapes; value = 512x2048 weights, 2048 rows",
+                   "l2": "every launch reads another weight copy"},
+        "e2e": None, "gpu_launches": args.steps * sum(r["weight_copies"] for r in out), "clocks": clocks,
+        "roofline": {"kernel": "tc_gemm_kernel", "bound": "tensor", "achieved": head["tflops"], "peak": peak_tf,
+                     "unit": "TFLOP/s", "frac": head["tensor_frac"],
+                     "peak_source": "measured bf16 GEMM (burst)" if peaks else "fallback", "traffic": None},
+        "shapes": out,
     }
     if lib().raw("sgr_status")(0) != 0:
         line["device_status"] = "a bounded device-side wait gave up"
@@ -475,9 +549,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=TOKENS, help="token rows per step, 1..64")
     ap.add_argument("--check", action="store_true",
                     help="N > 1: compare one step with the single-GPU layer stack on rank 0 (use with a small --layers)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gemv"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gemv", "tc"],
                     help="decode: the 40-layer stack (default); prefill: one layer over a 2048-row chunk; "
-                         "gemv: the dense GEMV sweep")
+                         "gemv: the dense GEMV sweep; tc: the fp16 tensor-core GEMM of the tc_* entries")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -513,6 +587,10 @@ def main():
     if args.workload == "gemv":
         if world == 1:
             run_gemv_bench(args, device)
+        return
+    if args.workload == "tc":
+        if world == 1:
+            run_tc_bench(args, device)
         return
     if world > 1:
         from sager_b200.ep import run_ep_bench

@@ -150,6 +150,116 @@ int launch_tile(const GemvArgs& a, dim3 grid, cudaStream_t stream) {
   return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
+// ---- dense matrices far larger than the machine (the LM head): a persistent kernel ----------
+// One CTA per SM walks stages of 256 consecutive super-blocks (36,864 contiguous bytes: a
+// whole number of rows when nb divides 256), each stage one bulk copy into a five-deep
+// ring issued by a producer warp. Thread t of the eight consumer warps owns block t of the
+// stage: a quarter-warp reads eight consecutive 144-byte blocks, 16 bytes per lane per
+// load, which spreads over all 32 banks without padding. The activations (at most four
+// token rows) are staged once per CTA. The nb lanes of a row meet by shuffle.
+constexpr int kStreamBlocks = 256;                       // super-blocks per stage = consumer threads
+constexpr int kStreamStageBytes = kStreamBlocks * kW4;   // 36,864
+constexpr int kStreamStages = 5;
+constexpr int kStreamThreads = kStreamBlocks + 32;       // + the producer warp
+inline size_t stream_gemv_smem(int nb, int tt) {
+  return 128 + static_cast<size_t>(kStreamStages) * kStreamStageBytes + xtile_bytes(tt, nb);
+}
+
+template <int TT, bool F16>
+__global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const GemvArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* empty = full + kStreamStages;
+  unsigned char* ring = smem + 128;
+  const int nb = a.nb;
+  const XTile xt = xtile_at(ring + kStreamStages * kStreamStageBytes, TT, nb);
+  const long long total_blocks = static_cast<long long>(a.n_rows) * nb;
+  const int n_stages = static_cast<int>((total_blocks + kStreamBlocks - 1) / kStreamBlocks);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStreamStages; ++i) {
+      mbar_init(full + i, 1);
+      mbar_init(empty + i, kStreamBlocks / 32);
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+
+  bool ok = true;
+  if (warp == kStreamBlocks / 32) {                      // producer
+    if (lane == 0) {
+      int it = 0;
+      for (int st = blockIdx.x; st < n_stages; st += gridDim.x, ++it) {
+        const int s = it % kStreamStages;
+        if (it >= kStreamStages && !mbar_wait(empty + s, ((it / kStreamStages) - 1) & 1)) {
+          ok = false;
+          break;
+        }
+        const long long b0 = static_cast<long long>(st) * kStreamBlocks;
+        const long long nblk = total_blocks - b0 < kStreamBlocks ? total_blocks - b0 : kStreamBlocks;
+        const uint32_t bytes = static_cast<uint32_t>(nblk) * kW4;
+        mbar_expect_tx(full + s, bytes);
+        bulk_g2s(ring + s * kStreamStageBytes, a.w[0] + b0 * kW4, bytes, full + s);
+      }
+    }
+  } else {
+    xtile_stage(xt, a.n_tokens, [&](int t) { return a.xq + static_cast<size_t>(t) * nb * kX8; },
+                threadIdx.x, kStreamBlocks);
+    asm volatile("bar.sync 1, %0;" ::"n"(kStreamBlocks) : "memory");
+    const int blk = threadIdx.x & (nb - 1);              // nb is a power of two <= 16
+    int it = 0;
+    for (int st = blockIdx.x; st < n_stages && ok; st += gridDim.x, ++it) {
+      const int s = it % kStreamStages;
+      ok = mbar_wait(full + s, (it / kStreamStages) & 1);
+      if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+      const long long b = static_cast<long long>(st) * kStreamBlocks + threadIdx.x;
+      float acc[1][TT];
+#pragma unroll
+      for (int t = 0; t < TT; ++t) acc[0][t] = 0.f;
+      if (b < total_blocks) {
+        const uint4* wb[1] = {reinterpret_cast<const uint4*>(ring + s * kStreamStageBytes + threadIdx.x * kW4)};
+        block_dot<1, TT>(wb, xt, blk, a.n_tokens, acc);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive_one(empty + s);          // this warp has read its blocks
+#pragma unroll
+      for (int t = 0; t < TT; ++t) acc[0][t] = reduce_lanes(acc[0][t], nb);
+      if (blk == 0 && b < total_blocks) {
+        const long long row = b / nb;
+#pragma unroll
+        for (int t = 0; t < TT; ++t)
+          if (t < a.n_tokens) store_out<F16>(a.y[0], static_cast<size_t>(t) * a.n_rows + row, acc[0][t]);
+      }
+    }
+  }
+  if (!ok && lane == 0 && a.status != nullptr) atomicExch(a.status, 1);
+}
+
+template <int TT, bool F16>
+int launch_stream(const GemvArgs& a, int sms, cudaStream_t stream) {
+  const size_t smem = stream_gemv_smem(a.nb, TT);
+  auto kern = gemv_stream_kernel<TT, F16>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+      cudaSuccess)
+    return kErrLaunch;
+  kern<<<sms, kStreamThreads, smem, stream>>>(a);
+  return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+// The persistent kernel pays off when every SM gets several stages.
+inline int stream_sms(const GemvArgs& a) {
+  if (a.n_tokens > 4 || a.nb > 16 || (a.nb & (a.nb - 1)) != 0) return 0;
+  if (reinterpret_cast<uintptr_t>(a.w[0]) & 15u) return 0;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    return 0;
+  const long long stages = (static_cast<long long>(a.n_rows) * a.nb + kStreamBlocks - 1) / kStreamBlocks;
+  return stages >= 8LL * sms ? sms : 0;
+}
+
 // tokens per CTA of the dense multi-token kernels (walked in sub-tiles of 8)
 constexpr int kDenseTokTile = 16;
 
@@ -170,6 +280,13 @@ int launch_dense(const void* w0, const void* w1, const void* xq, void* y0, void*
   a.n_tokens = n_tokens;
   a.status = status_word();
   const int rc = tile_rows(a.nb);
+  if constexpr (NMAT == 1) {
+    if (const int sms = stream_sms(a)) {
+      if (n_tokens == 1) return launch_stream<1, F16>(a, sms, stream);
+      if (n_tokens == 2) return launch_stream<2, F16>(a, sms, stream);
+      return launch_stream<4, F16>(a, sms, stream);
+    }
+  }
   if (n_tokens == 1) {
     a.tok_tile = 1;
     return launch_tile<NMAT, 1, kDense, F16>(a, dim3((n_rows + rc - 1) / rc, 1), stream);

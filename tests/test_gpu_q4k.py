@@ -96,6 +96,26 @@ def test_gemv_sweep_vs_oracle(oracle, rows, k, batch):
     assert f16_close(y16.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("rows,k,batch", [(40005, 2048, 3), (160001, 512, 2), (20003, 4096, 1)])
+def test_large_dense_gemv_persistent_kernel(oracle, rows, k, batch):
+    """Matrices of several stages per SM take the persistent streaming kernel; ragged last
+    stage, every supported row length (2, 8, 16 super-blocks) and token count."""
+    w_np, w_dev = make_q4k(rows, k, 41)
+    x_np, x_dev = make_x16(batch, k, 42)
+    xq = quantize_dev(x_dev)
+    xq_np = xq.cpu().numpy()
+    want = np.stack([oracle.gemv(w_np, xq_np[t], rows, k) for t in range(batch)])
+    y = torch.full((batch, rows), float("nan"), dtype=torch.float32, device=DEV)
+    if batch == 1:
+        ops.gemv_q4_k_q8(w_dev, xq, y, rows, k)
+    else:
+        ops.gemv_q4_k_q8_batched(w_dev, xq, y, rows, k, batch)
+    assert rel(y.cpu().numpy(), want) < GEMV_TOL
+    y16 = torch.full((batch, rows), float("nan"), dtype=torch.float16, device=DEV)
+    ops.gemv_q4_k_q8_f16out_mtok(w_dev, xq, y16, rows, k, batch)
+    assert f16_close(y16.cpu().numpy(), want)
+
+
 @pytest.mark.parametrize("tok", [2, 4, 5, 19])
 def test_multi_token_variants_agree(oracle, tok):
     rows, k = 512, 2048
