@@ -401,6 +401,8 @@ def run_gemv_bench(args, device):
     from sager_b200 import lib, ops, synth
     peak, kind = load_peaks()
     shapes = [(4096, 2048), (2048, 4096), (512, 2048), (2048, 512), (151936, 2048)]
+    if args.shape:
+        shapes = [tuple(int(v) for v in args.shape.split(","))]
     rows_out = []
     ref = None
     if not args.no_gpu_baseline:
@@ -455,7 +457,7 @@ def run_gemv_bench(args, device):
                 row["reference_cuda_gbs"] = wbytes / ref_us / 1e3
             rows_out.append(row)
     clocks = sampler.stop()
-    head = [r for r in rows_out if r["rows"] == 151936 and r["batch"] == 1][0]
+    head = max((r for r in rows_out if r["batch"] == 1), key=lambda r: r["rows"] * r["k"])
     line = {
         "metric": "q4k_gemv_hbm_gbs", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": head["us"] * 1e-3, "higher_is_better": True,
@@ -463,7 +465,7 @@ def run_gemv_bench(args, device):
         "config": {"workload": "dense Q4_K GEMV sweep at batch 1 and 4; value = LM head 2048->151936 at batch 1",
                    "l2": "every launch of a sweep reads a different weight copy, > 126 MB between reuses"},
         "e2e": None, "gpu_launches": args.steps * sum(r["weight_copies"] for r in rows_out), "clocks": clocks,
-        "roofline": {"kernel": "gemv tile kernels (gemv.cu)", "bound": "hbm", "achieved": head["gbs"], "peak": peak,
+        "roofline": {"kernel": "gemv_stream_kernel (gemv.cu)", "bound": "hbm", "achieved": head["gbs"], "peak": peak,
                      "unit": "GB/s", "frac": head["frac"], "peak_source": f"{kind} copy bandwidth (burst)",
                      "traffic": None},
         "sweep": rows_out,
@@ -553,6 +555,7 @@ def main():
                     help="decode: the 40-layer stack (default); prefill: one layer over a 2048-row chunk; "
                          "gemv: the dense GEMV sweep; tc: the fp16 tensor-core GEMM of the tc_* entries")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--shape", default=None, help="gemv workload: only this ROWS,K shape (profiling captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     LAYERS, TOKENS = args.layers, args.tokens

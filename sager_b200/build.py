@@ -46,7 +46,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     if not force and not needs_build():
         return LIB
     cmd = [nvcc_path()] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + \
-        ["-I", CSRC, "-I", os.path.join(os.path.dirname(HERE), "include"), "-o", LIB] + sources()
+        ["-I", CSRC, "-I", os.path.join(os.path.dirname(HERE), "include"), "-o", LIB + ".tmp"] + sources()
     if verbose:
         print(" ".join(cmd))
     res = subprocess.run(cmd, capture_output=True, text=True)
@@ -55,6 +55,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         raise RuntimeError("nvcc failed")
     if ptxas_info or verbose:
         sys.stderr.write(res.stderr)
+    os.replace(LIB + ".tmp", LIB)          # a reader never sees a half-written library
     return LIB
 
 

@@ -260,6 +260,120 @@ inline int stream_sms(const GemvArgs& a) {
   return stages >= 8LL * sms ? sms : 0;
 }
 
+// ---- small dense matrices, two to four token rows (a verify window) ------------------------
+// Fewer tiles than SMs: latency decides, not bandwidth, and staging through shared memory
+// only adds to it. One lane per 32-byte nibble group (two sub-blocks) straight from global
+// memory, no barriers. The integer partial sums of a super-block meet exactly by shuffle
+// over its four lanes, its fp32 term is formed once, and the terms of a row are added in
+// the order of the tile kernels' shuffle tree.
+constexpr int kDirectThreads = 128;
+
+template <int NMAT, int TT, bool F16>
+__global__ void __launch_bounds__(kDirectThreads) gemv_direct_kernel(const GemvArgs a) {
+  const int nb = a.nb;
+  const int groups = nb * 4;
+  const int lpr = groups < 32 ? groups : 32;               // lanes per row (a power of two >= 4)
+  const int lane = threadIdx.x & 31;
+  const int warp = blockIdx.x * (kDirectThreads / 32) + (threadIdx.x >> 5);
+  const int row_raw = warp * (32 / lpr) + lane / lpr;
+  const int row = min(row_raw, a.n_rows - 1);              // every lane runs the same loops
+  const int lr = lane & (lpr - 1);
+  const int nt = a.n_tokens;
+  float acc[NMAT][TT];
+#pragma unroll
+  for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+    for (int t = 0; t < TT; ++t) acc[m][t] = 0.f;
+  for (int gi = lr; gi < groups; gi += lpr) {
+    const int blk = gi >> 2, g = gi & 3;
+    float d[NMAT], dmin[NMAT];
+    uint32_t lo[NMAT][8], hi[NMAT][8];
+    int sc_lo[NMAT], sc_hi[NMAT], mn_lo[NMAT], mn_hi[NMAT];
+#pragma unroll
+    for (int m = 0; m < NMAT; ++m) {
+      const unsigned char* wb = a.w[m] + (static_cast<size_t>(row) * nb + blk) * kW4;
+      const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(wb));
+      const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(wb + 16 + 32 * g));
+      const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(wb + 32 + 32 * g));
+      d[m] = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x & 0xFFFFu)));
+      dmin[m] = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x >> 16)));
+      const Scales6 s6 = unpack_scales6(hdr.y, hdr.z, hdr.w);
+      const uint32_t scw = g < 2 ? s6.sc[0] : s6.sc[1], mnw = g < 2 ? s6.mn[0] : s6.mn[1];
+      sc_lo[m] = (scw >> (16 * (g & 1))) & 0xFF;
+      sc_hi[m] = (scw >> (16 * (g & 1) + 8)) & 0xFF;
+      mn_lo[m] = (mnw >> (16 * (g & 1))) & 0xFF;
+      mn_hi[m] = (mnw >> (16 * (g & 1) + 8)) & 0xFF;
+      const uint32_t raw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        lo[m][i] = raw[i] & 0x0F0F0F0Fu;
+        hi[m][i] = (raw[i] >> 4) & 0x0F0F0F0Fu;
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+      if (t < nt) {
+        const unsigned char* xb = a.xq + (static_cast<size_t>(t) * nb + blk) * kX8;
+        const uint32_t* xc = reinterpret_cast<const uint32_t*>(xb + 4 + 64 * g);
+        uint32_t xv[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) xv[i] = __ldg(xc + i);
+        const uint32_t bs = __ldg(reinterpret_cast<const uint32_t*>(xb + 260 + 4 * g));   // two int16 sums
+        const float xd = __ldg(reinterpret_cast<const float*>(xb));
+        const int bs_lo = static_cast<int16_t>(bs & 0xFFFFu), bs_hi = static_cast<int16_t>(bs >> 16);
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) {
+          int dl = 0, dh = 0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            dl = __dp4a(static_cast<int>(lo[m][i]), static_cast<int>(xv[i]), dl);
+            dh = __dp4a(static_cast<int>(hi[m][i]), static_cast<int>(xv[8 + i]), dh);
+          }
+          int isum = sc_lo[m] * dl + sc_hi[m] * dh;
+          int msum = mn_lo[m] * bs_lo + mn_hi[m] * bs_hi;
+          isum += __shfl_xor_sync(0xFFFFFFFFu, isum, 1);
+          msum += __shfl_xor_sync(0xFFFFFFFFu, msum, 1);
+          isum += __shfl_xor_sync(0xFFFFFFFFu, isum, 2);
+          msum += __shfl_xor_sync(0xFFFFFFFFu, msum, 2);
+          if (g == 0) acc[m][t] += xd * (d[m] * static_cast<float>(isum) - dmin[m] * static_cast<float>(msum));
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+    for (int t = 0; t < TT; ++t) acc[m][t] = reduce_lanes(acc[m][t], lpr);
+  if (lr == 0 && row_raw < a.n_rows) {
+#pragma unroll
+    for (int t = 0; t < TT; ++t)
+      if (t < nt) {
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m)
+          store_out<F16>(a.y[m], static_cast<size_t>(t) * a.n_rows + row_raw, acc[m][t]);
+      }
+  }
+}
+
+template <int NMAT, bool F16>
+int launch_direct(const GemvArgs& a, cudaStream_t stream) {
+  const int lpr = a.nb * 4 < 32 ? a.nb * 4 : 32;
+  const int rows_per_cta = (kDirectThreads / 32) * (32 / lpr);
+  const int grid = (a.n_rows + rows_per_cta - 1) / rows_per_cta;
+  if (a.n_tokens == 2) gemv_direct_kernel<NMAT, 2, F16><<<grid, kDirectThreads, 0, stream>>>(a);
+  else gemv_direct_kernel<NMAT, 4, F16><<<grid, kDirectThreads, 0, stream>>>(a);
+  return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+// Two to four token rows over a matrix of at most a few tiles per SM, 16-byte aligned.
+template <int NMAT>
+inline bool direct_fits(const GemvArgs& a) {
+  if (a.n_tokens < 2 || a.n_tokens > 4 || (a.nb & (a.nb - 1)) != 0) return false;
+  for (int m = 0; m < NMAT; ++m)
+    if (reinterpret_cast<uintptr_t>(a.w[m]) & 15u) return false;
+  return static_cast<long long>(a.n_rows) * a.nb <= 148LL * 4 * kStreamBlocks;
+}
+
 // tokens per CTA of the dense multi-token kernels (walked in sub-tiles of 8)
 constexpr int kDenseTokTile = 16;
 
@@ -287,6 +401,7 @@ int launch_dense(const void* w0, const void* w1, const void* xq, void* y0, void*
       return launch_stream<4, F16>(a, sms, stream);
     }
   }
+  if (direct_fits<NMAT>(a)) return launch_direct<NMAT, F16>(a, stream);
   if (n_tokens == 1) {
     a.tok_tile = 1;
     return launch_tile<NMAT, 1, kDense, F16>(a, dim3((n_rows + rc - 1) / rc, 1), stream);
