@@ -488,7 +488,10 @@ def run_tc_bench(args, device):
     out = []
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
-    for rows, k, tok in [(512, 2048, 2048), (2048, 512, 2048), (512, 2048, 64), (2048, 512, 64)]:
+    tc_shapes = [(512, 2048, 2048), (2048, 512, 2048), (512, 2048, 64), (2048, 512, 64)]
+    if args.shape:
+        tc_shapes = [tuple(int(v) for v in args.shape.split(","))]
+    for rows, k, tok in tc_shapes:
         copies = max(2, min(128, (192 << 20) // (rows * k * 2) + 1))
         g = torch.Generator(device=device).manual_seed(SEED + rows + tok)
         w = (torch.randn(copies, rows, k, generator=g, device=device) * 0.02).half()
@@ -555,7 +558,7 @@ def main():
                     help="decode: the 40-layer stack (default); prefill: one layer over a 2048-row chunk; "
                          "gemv: the dense GEMV sweep; tc: the fp16 tensor-core GEMM of the tc_* entries")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
-    ap.add_argument("--shape", default=None, help="gemv workload: only this ROWS,K shape (profiling captures)")
+    ap.add_argument("--shape", default=None, help="gemv workload: only this ROWS,K shape; tc workload: ROWS,K,TOKENS (profiling captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     LAYERS, TOKENS = args.layers, args.tokens

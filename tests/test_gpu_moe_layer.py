@@ -218,7 +218,8 @@ def test_stack_graph_replay_is_deterministic(oracle):
 
 
 @pytest.mark.parametrize("padded", [False, True])
-def test_expert_parallel_record_path_on_one_device(full_w, padded):
+@pytest.mark.parametrize("world,tokens", [(4, 16), (4, 64), (8, 64)])
+def test_expert_parallel_record_path_on_one_device(full_w, padded, world, tokens):
     """The expert-parallel layer with its exchanges done by hand on one device: each
     emulated rank routes its home rows straight into dispatch records (strided Q8_K
     rows, ids, weights), every rank's owner call runs its expert range over all
@@ -227,7 +228,9 @@ def test_expert_parallel_record_path_on_one_device(full_w, padded):
     from sager_b200 import lib
     from sager_b200.ep import record_layout
     from sager_b200.ops import stream_ptr
-    w, k, world, tokens = full_w, 8, 4, 16
+    if not padded and tokens >= 16 and tokens // world >= 16:
+        pytest.skip("packed records with a row-streaming home stage: not a combination the host code issues")
+    w, k = full_w, 8
     n_home = tokens // world
     x16 = synth.normal_fp16((tokens, w.hidden), 91, DEV)
     _, x_full, out_full = run_layer(w, tokens, k, x16, n_max=64)
