@@ -557,6 +557,8 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gemv", "tc"],
                     help="decode: the 40-layer stack (default); prefill: one layer over a 2048-row chunk; "
                          "gemv: the dense GEMV sweep; tc: the fp16 tensor-core GEMM of the tc_* entries")
+    ap.add_argument("--kernel", default=None, choices=["rows", "items"],
+                    help="decode: force the row-streaming or the item expert kernel (default: the library's choice)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--shape", default=None, help="gemv workload: only this ROWS,K shape; tc workload: ROWS,K,TOKENS (profiling captures)")
     args = ap.parse_args()
@@ -608,7 +610,7 @@ def main():
 
     ws, inputs, x0, biases, alpha = build_workload(device, rank, world, LAYERS, TOKENS)
     n = TOKENS
-    stack = MoeStack(ws, n, K, device, biases=biases, inputs=inputs, per_layer_ws=True)
+    stack = MoeStack(ws, n, K, device, biases=biases, inputs=inputs, per_layer_ws=True, kernel=args.kernel)
     stack.x.copy_(x0)
     stack.capture(n)
 
@@ -682,10 +684,11 @@ def main():
         stage_ms[name] = s0.elapsed_time(s1) / reps
     peak, peak_kind = load_peaks()
     ex_gbs = ex_bytes / (stage_ms["experts"] * 1e-3) / 1e9
-    kernel = "expert_rows_kernel" if n >= 16 else "expert_stream_kernel"
+    use_rows = args.kernel == "rows" or (args.kernel is None and n >= 4)
+    kernel = "expert_rows_kernel" if use_rows else "expert_stream_kernel"
     # DRAM traffic per launch: one ncu capture of this kernel on the 4-layer stack read 295.3 MB and
     # wrote 6.1 MB for 284.4 MB of algorithmic bytes (profiles/); scaled by the bytes of this run's launches
-    traffic = (295.3e6 + 6.1e6) / 284.44e6 * (ex_bytes / LAYERS) if n >= 16 else None
+    traffic = (295.3e6 + 6.1e6) / 284.44e6 * (ex_bytes / LAYERS) if use_rows else None
     roofline = {"kernel": kernel, "bound": "hbm", "achieved": ex_gbs, "peak": peak,
                 "unit": "GB/s", "frac": ex_gbs / peak, "peak_source": f"{peak_kind} copy bandwidth (burst)",
                 "traffic": traffic,

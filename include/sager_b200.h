@@ -233,7 +233,7 @@ typedef struct sgr_moe_layer {
   int wait_count, wait_mul, wait_add;
   /* records between ranks may carry the Q8_K rows in 288-byte blocks (d | 12 bytes | 256 codes |
    * 8 sums, 16-byte aligned) instead of packed 276-byte ones: set for both the route stage that
-   * writes them (xq_out) and the owner that reads them (xq_in, routing_given, >= 16 rows). */
+   * writes them (xq_out) and the owner that reads them (xq_in, routing_given, >= 4 rows). */
   int xq_padded;
 } sgr_moe_layer;
 

@@ -40,15 +40,15 @@ enum { kLayoutSwizzled = 0, kLayoutCore = 1 };
 
 // Shared-memory operand descriptors (K-major).
 //   swizzled: rows of 128 bytes, eight-row groups 1024 bytes apart, 128-byte swizzle
-//   core:     8x16-byte core matrices; K-adjacent ones a whole 128-row column apart
-//             (2048 bytes), eight-row groups 128 bytes apart
-__device__ __forceinline__ uint64_t tc_desc(uint32_t saddr, int layout) {
+//   core:     8x16-byte core matrices; K-adjacent ones a whole column of the tile apart
+//             (tile rows x 16 bytes), eight-row groups 128 bytes apart
+__device__ __forceinline__ uint64_t tc_desc(uint32_t saddr, int layout, int tile_rows) {
   const uint64_t start = (saddr & 0x3FFFFu) >> 4;
   if (layout == kLayoutSwizzled)
     return start | (static_cast<uint64_t>(1) << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) |
            (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(2) << 61);
-  return start | (static_cast<uint64_t>(2048 >> 4) << 16) | (static_cast<uint64_t>(128 >> 4) << 32) |
-         (static_cast<uint64_t>(1) << 46);
+  return start | (static_cast<uint64_t>(tile_rows) << 16) /* tile_rows * 16 bytes >> 4 */ |
+         (static_cast<uint64_t>(128 >> 4) << 32) | (static_cast<uint64_t>(1) << 46);
 }
 // D fp32, A and B fp16, both K-major, M = 128, N = n
 __device__ __forceinline__ uint32_t tc_idesc(int n) {
@@ -88,6 +88,7 @@ struct TcArgs {
   void* y;
   int n_rows, k, n_tokens;
   int layout;
+  int bn;                 // token rows per CTA: 128, or 64 when that is what fills the machine
   int* status;
 };
 
@@ -107,8 +108,9 @@ __global__ void __launch_bounds__(kTcThreads) tc_gemm_kernel(const __grid_consta
   const uint32_t tiles = base + 1024;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row0 = blockIdx.x * kBM, tok0 = blockIdx.y * kBN;
-  const int ntok = min(kBN, a.n_tokens - tok0);
+  const int row0 = blockIdx.x * kBM, tok0 = blockIdx.y * a.bn;
+  const int ntok = min(a.bn, a.n_tokens - tok0);
+  const uint32_t b_bytes = static_cast<uint32_t>(a.bn) * kBK * 2;
   const int n_mma = max(16, (ntok + 15) & ~15);
   const int nkb = a.k / kBK;
 
@@ -141,7 +143,7 @@ __global__ void __launch_bounds__(kTcThreads) tc_gemm_kernel(const __grid_consta
           atomicExch(fail, 1);
           break;
         }
-        mbar_expect_tx(full + s, 2 * kTileBytes);
+        mbar_expect_tx(full + s, kTileBytes + b_bytes);
         const uint32_t ta = tiles + s * 2 * kTileBytes, tb = ta + kTileBytes;
         if (a.layout == kLayoutSwizzled) {
           tc_tma_2d(ta, &map_w, kb * kBK, row0, full + s);
@@ -155,7 +157,9 @@ __global__ void __launch_bounds__(kTcThreads) tc_gemm_kernel(const __grid_consta
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = tc_idesc(n_mma);
-      const int kstep = a.layout == kLayoutSwizzled ? 32 : 2 * 2048;     // bytes between K = 16 slices
+      // bytes between K = 16 slices of a tile
+      const int kstep_a = a.layout == kLayoutSwizzled ? 32 : 2 * kBM * 16;
+      const int kstep_b = a.layout == kLayoutSwizzled ? 32 : 2 * a.bn * 16;
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int s = kb % kTcStages;
@@ -165,7 +169,7 @@ __global__ void __launch_bounds__(kTcThreads) tc_gemm_kernel(const __grid_consta
         const uint32_t ta = tiles + s * 2 * kTileBytes, tb = ta + kTileBytes;
 #pragma unroll
         for (int j = 0; j < kBK / 16; ++j)
-          tc_mma(tmem, tc_desc(ta + j * kstep, a.layout), tc_desc(tb + j * kstep, a.layout), idesc,
+          tc_mma(tmem, tc_desc(ta + j * kstep_a, a.layout, kBM), tc_desc(tb + j * kstep_b, a.layout, a.bn), idesc,
                  (kb | j) != 0);
         tc_commit(empty + s);
       }
@@ -307,13 +311,13 @@ EncodeFn tc_encoder() {
 std::atomic<int> g_tc_layout{kLayoutSwizzled};
 
 // A [rows][k] fp16 matrix as operand tiles of 128 rows x 64 halfs.
-bool operand_map(CUtensorMap* tm, const void* base, int rows, int k, int layout) {
+bool operand_map(CUtensorMap* tm, const void* base, int rows, int k, int layout, int tile_rows) {
   EncodeFn enc = tc_encoder();
   if (enc == nullptr) return false;
   if (layout == kLayoutSwizzled) {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-    const cuuint32_t box[2] = {kBK, kBM};
+    const cuuint32_t box[2] = {kBK, static_cast<cuuint32_t>(tile_rows)};
     const cuuint32_t estr[2] = {1u, 1u};
     return enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -322,7 +326,7 @@ bool operand_map(CUtensorMap* tm, const void* base, int rows, int k, int layout)
   // (8 halfs, rows, k / 8): the box lands as [k-chunk][row][16 bytes]
   const cuuint64_t dims[3] = {8, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(k / 8)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(k) * 2, 16};
-  const cuuint32_t box[3] = {8, kBM, kBK / 8};
+  const cuuint32_t box[3] = {8, static_cast<cuuint32_t>(tile_rows), kBK / 8};
   const cuuint32_t estr[3] = {1u, 1u, 1u};
   return enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -337,8 +341,11 @@ int launch_tc_gemm(const void* w16, const void* x16, void* y, int n_rows, int k,
   if ((reinterpret_cast<uintptr_t>(w16) | reinterpret_cast<uintptr_t>(x16)) & 15u) return kErrAlign;
   if (reinterpret_cast<uintptr_t>(y) & (F32OUT ? 3u : 1u)) return kErrAlign;
   const int layout = g_tc_layout.load(std::memory_order_relaxed);
+  // 128 x 128 tiles when they fill the machine, else 128 x 64 for twice the CTAs
+  const int row_tiles = (n_rows + kBM - 1) / kBM;
+  const int bn = row_tiles * ((n_tokens + kBN - 1) / kBN) >= 148 ? kBN : 64;
   CUtensorMap mw, mx;
-  if (!operand_map(&mw, w16, n_rows, k, layout) || !operand_map(&mx, x16, n_tokens, k, layout))
+  if (!operand_map(&mw, w16, n_rows, k, layout, kBM) || !operand_map(&mx, x16, n_tokens, k, layout, bn))
     return kErrUnsupported;
   auto kern = tc_gemm_kernel<F32OUT>;
   static std::atomic<bool> attr_set{false};
@@ -347,8 +354,8 @@ int launch_tc_gemm(const void* w16, const void* x16, void* y, int n_rows, int k,
       return kErrLaunch;
     attr_set.store(true, std::memory_order_release);
   }
-  TcArgs a{y, n_rows, k, n_tokens, layout, status_word()};
-  kern<<<dim3((n_rows + kBM - 1) / kBM, (n_tokens + kBN - 1) / kBN), kTcThreads, kTcSmem, s>>>(mw, mx, a);
+  TcArgs a{y, n_rows, k, n_tokens, layout, bn, status_word()};
+  kern<<<dim3(row_tiles, (n_tokens + bn - 1) / bn), kTcThreads, kTcSmem, s>>>(mw, mx, a);
   return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
