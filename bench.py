@@ -389,6 +389,28 @@ def run_prefill_bench(args, device):
     }
     if lib().raw("sgr_status")(0) != 0:
         line["device_status"] = "a bounded device-side wait gave up"
+    if not args.no_gpu_baseline:
+        # the same chunk on the reference's own CUDA kernels in its device MoE sequence (dp4a branch)
+        try:
+            from oracle import ref_cuda
+            if ref_cuda.available():
+                path = ref_cuda.DeviceMoePath(ref_cuda.reference_launchers(), n, H, FF, E, K, device)
+                xr = x0.clone()
+
+                def ref_step():
+                    xr.copy_(x0, non_blocking=True)
+                    path.run(n, xn, xr, w.router, table, w.shared_ptrs(), logits=logits)
+                ms_ref = timed(ref_step, max(2, min(args.steps, 5)))
+                step()
+                torch.cuda.synchronize()
+                line["gpu_baseline"] = {
+                    "value": n / (ms_ref * 1e-3), "unit": "tokens/s", "ms_per_step": ms_ref,
+                    "kind": "the reference's CUDA kernels built for sm_100a, its device MoE launch sequence "
+                            "(dp4a branch), eager launches",
+                    "max_rel_diff_vs_this_library": float((xr.float() - x.float()).abs().max() /
+                                                          x.float().abs().max())}
+        except Exception as exc:
+            line["gpu_baseline"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
     print(json.dumps(line))
 
 

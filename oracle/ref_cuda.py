@@ -109,13 +109,17 @@ class DeviceMoePath:
         self.sh_q = torch.empty(n_max, n_ff // 256 * 276, dtype=u8, device=d)
         self.sh_y = torch.empty(n_max, hidden, dtype=f16, device=d)
 
-    def run(self, n, xn, x, router, table, shared_ptrs, bias=None):
+    def run(self, n, xn, x, router, table, shared_ptrs, bias=None, logits=None):
         """xn [n][H] fp16 layer input, x [n][H] fp16 residual (combined in place);
         table = the [3][E] pointer-table slices, shared_ptrs = (gate, up, down); bias [E]
-        fp32 is added to the logits (the benchmark's routing skew; one more launch)."""
+        fp32 is added to the logits (the benchmark's routing skew; one more launch); `logits`
+        replaces the router GEMV."""
         o, H, F, E, K = self.o, self.H, self.F, self.E, self.K
         o.quantize_q8_k(xn, self.xq, n * H)
-        o.gemv_f32_out_f16x_mtok(router, xn, self.logits, E, H, n)
+        if logits is None:
+            o.gemv_f32_out_f16x_mtok(router, xn, self.logits, E, H, n)
+        else:                        # the prefill benchmark draws the logits directly
+            self.logits[:n].copy_(logits)
         if bias is not None:
             self.logits[:n].add_(bias)
         o.router_topk_batched(self.logits, self.idx, self.w, E, K, K + 1, n, 1.0)
