@@ -134,22 +134,29 @@ def calibrate_alpha(x0_rows, router, device):
     return 0.5 * (lo + hi)
 
 
-def cpu_pool_sample(ws0, xn0, bias0, budget_s=12.0):
-    """Time the reference's CPU expert pool (oracle/_ref) - or, without it, the C port -
-    on layer 0 of the workload: router + top-8 on one thread, then one pool job per
-    (token, expert) and per (token, shared expert), weighted sum on the host."""
+def cpu_pool_sample(ws0, xn0, bias0, budget_s=12.0, layers=None, max_steps=20):
+    """Time the reference's CPU expert pool (oracle/_ref: src/kernels/cpu/pool.cpp:74-134 running
+    src/kernels/cpu/q4_avx2.cpp:175-196 per job) - or, without it, the C port - on the workload's
+    expert FFNs. The routing of layer 0 (router + top-8 with the stack's Zipf bias, by the C
+    restatement on one thread; the reference itself never routes on the CPU) is computed once and
+    timed apart. A step submits, for each of `layers` layers, one pool job per (token row, routed
+    expert) and per (token row, shared expert) - layer 0's jobs every time, 453 MB of expert
+    weights, more than the host's last-level cache - and waits for them; the weighted sum is done
+    on the host. `layers` is cut down (and the step time scaled up, which the result says) only
+    when a full step would not fit the time budget."""
     from oracle import oracle as orc
     o = orc.Oracle() if os.path.exists(os.path.join(orc.HERE, "libsager_oracle.so")) else None
     if o is None:
-        orc.build(ref_root="/nonexistent")
+        orc.build(ref_root=os.devnull)
         o = orc.Oracle()
+    layers = LAYERS if layers is None else layers
     cores = os.cpu_count() or 1
     x16 = xn0.cpu().numpy()
     router = ws0.router.cpu().numpy()
     bias = bias0.cpu().numpy()
     n = x16.shape[0]
     blob = ws0.blob.cpu().numpy()
-    gu, dn = ws0.gu_bytes, ws0.dn_bytes
+    gu = ws0.gu_bytes
     base = blob.ctypes.data
 
     def ptrs(e):
@@ -163,40 +170,77 @@ def cpu_pool_sample(ws0, xn0, bias0, budget_s=12.0):
     except (FileNotFoundError, OSError, RuntimeError):
         ref, pool, kind = None, None, "port"
 
+    t0 = time.perf_counter()
+    idx = np.zeros((n, K + 1), dtype=np.int32)
+    wts = np.zeros((n, K + 1), dtype=np.float32)
+    for t in range(n):
+        lg = o.router_logits(router, x16[t]) + bias
+        idx[t], wts[t] = o.router_topk(lg, K, shared_w=1.0)
+    router_s = time.perf_counter() - t0
+    xf = x16.astype(np.float32)
+    w3, xs = [], []
+    for t in range(n):
+        for kk in range(K + 1):
+            w3 += ptrs(int(idx[t, kk]) if kk < K else E)
+            xs.append(xf[t])
+    xs = np.stack(xs)
+    n_ffn = xs.shape[0]
+
+    def run_jobs(p, w3_, xs_):
+        return p.run(w3_, xs_) if p is not None else _port_batch(o, w3_, xs_, cores)
+
     def one_layer():
-        t0 = time.perf_counter()
-        idx = np.zeros((n, K + 1), dtype=np.int32)
-        wts = np.zeros((n, K + 1), dtype=np.float32)
-        for t in range(n):
-            lg = o.router_logits(router, x16[t]) + bias
-            idx[t], wts[t] = o.router_topk(lg, K, shared_w=1.0)
-        w3, xs = [], []
-        xf = x16.astype(np.float32)
-        for t in range(n):
-            for kk in range(K + 1):
-                w3 += ptrs(int(idx[t, kk]) if kk < K else E)
-                xs.append(xf[t])
-        xs = np.stack(xs)
-        if pool is not None:
-            ys = pool.run(w3, xs)
-        else:
-            ys = _port_batch(o, w3, xs, cores)
+        t1 = time.perf_counter()
+        ys = run_jobs(pool, w3, xs).reshape(n, K + 1, H)
         out = xf.copy()
-        ys = ys.reshape(n, K + 1, H)
         for kk in range(K + 1):
             out += wts[:, kk:kk + 1] * ys[:, kk]
-        return time.perf_counter() - t0
+        return time.perf_counter() - t1
 
     one_layer()                                   # warm-up (page in the weights)
-    times = []
+    t_probe = one_layer()
+    per_step = max(1, min(layers, int(budget_s / 3.0 / max(t_probe, 1e-4))))    # layers actually run per step
+    steps_t = []
     t_start = time.perf_counter()
-    while time.perf_counter() - t_start < budget_s and len(times) < 20:
-        times.append(one_layer())
+    while (time.perf_counter() - t_start < budget_s and len(steps_t) < max_steps) or not steps_t:
+        t_step = 0.0
+        for _ in range(per_step):
+            t_step += one_layer()
+        steps_t.append(t_step * layers / per_step)
+    # one worker, on a slice of the same jobs
+    one_worker_ms = None
+    if ref is not None:
+        m = min(n_ffn, 36)
+        p1 = ref.pool(1, H, FF, E)
+        p1.run(w3[:3 * m], xs[:m])
+        t1 = time.perf_counter()
+        p1.run(w3[:3 * m], xs[:m])
+        one_worker_ms = (time.perf_counter() - t1) * 1e3 / m
+        p1.close()
     if pool is not None:
         pool.close()
-    t_layer = float(np.median(times))
+    t_step = float(np.median(steps_t))
     del blob
-    return {"t_layer_s": t_layer, "cores": cores, "kind": kind, "layers_timed": len(times)}
+    return {"t_step_s": t_step, "steps_list": steps_t, "cores": cores, "kind": kind, "steps_timed": len(steps_t),
+            "layers_per_step_run": per_step, "layers": layers, "ffn_per_layer": n_ffn,
+            "ms_per_ffn": t_step * 1e3 / (layers * n_ffn),
+            "effective_gbs": layers * n_ffn * EXPERT_BYTES / t_step / 1e9,
+            "one_worker_ms_per_ffn": one_worker_ms,
+            "router_ms_per_layer_not_in_value": router_s * 1e3}
+
+
+def cpu_baseline_entry(res, n):
+    scaled = "" if res["layers_per_step_run"] == res["layers"] else \
+        f" ({res['layers_per_step_run']} layers run per step, time scaled to {res['layers']})"
+    return {"value": n / res["t_step_s"], "unit": "tokens/s", "cores": res["cores"], "kind": res["kind"],
+            "sample": f"{res['steps_timed']} steps of {res['layers']} layers x {res['ffn_per_layer']} expert FFNs "
+                      f"({n} token rows x (top-{K} + shared), layer 0's routing and weights every layer) through the "
+                      f"reference's CPU pool on all host cores{scaled}; the router (C restatement, one thread, "
+                      f"{res['router_ms_per_layer_not_in_value']:.0f} ms per layer) is not in the value: the reference never "
+                      "routes on the CPU",
+            "ms_per_step": res["t_step_s"] * 1e3, "ms_per_ffn": res["ms_per_ffn"],
+            "effective_gbs": res["effective_gbs"], "one_worker_ms_per_ffn": res["one_worker_ms_per_ffn"],
+            "router_ms_per_layer": res["router_ms_per_layer_not_in_value"]}
 
 
 def ref_cuda_decode(ws, inputs, x0, biases, n, device, steps, ours_x):
@@ -257,9 +301,9 @@ def _port_batch(o, w3_ptrs, xs, cores):
 
 
 def run_reference_arm(args):
-    """The reference's own CPU implementation of the path on this machine's cores:
-    each step is a bounded sample (layer 0 of the workload, 64 token rows: 576 expert
-    FFNs through the reference's CpuPool); tokens/s is scaled to the 40-layer step."""
+    """The reference's own CPU implementation of the path on this machine's cores: each step
+    runs the expert FFNs of the 40-layer, 64-row step through the reference's CpuPool (see
+    cpu_pool_sample), with the same calibrated routing skew as the GPU arm."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -268,26 +312,21 @@ def run_reference_arm(args):
     from sager_b200 import synth
     w0 = synth.MoeWeights(H, FF, E, device, seed=SEED)
     xn0 = synth.normal_fp16((TOKENS, H), SEED + 500, device)
-    bias0 = torch.from_numpy(synth.zipf_bias(E, SEED + 900, 1.0)).to(device)
-    per_step = max(2.0, min(20.0, 150.0 / max(1, args.steps + args.warmup)))
-    res = None
-    t_all = []
-    for i in range(args.warmup + args.steps):
-        res = cpu_pool_sample(w0, xn0, bias0, budget_s=per_step)
-        if i >= args.warmup:
-            t_all.append(res["t_layer_s"])
-    t_layer = float(np.median(t_all))
-    value = TOKENS / (t_layer * LAYERS)
-    sample = (f"layer 0 of the stack, {TOKENS} token rows: router + {TOKENS * (K + 1)} expert FFNs "
-              f"through the CPU pool; step time = {LAYERS} x layer time")
+    alpha = calibrate_alpha(xn0, w0.router, device)
+    bias0 = torch.from_numpy(synth.zipf_bias(E, SEED + 900, alpha)).to(device)
+    total = args.steps + args.warmup
+    res = cpu_pool_sample(w0, xn0, bias0, budget_s=max(10.0, min(150.0, 6.0 * total)), max_steps=total)
+    timed = res["steps_list"][args.warmup:] or res["steps_list"]      # the first W steps are warm-up
+    res["t_step_s"], res["steps_timed"] = float(np.median(timed)), len(timed)
+    value = TOKENS / res["t_step_s"]
+    cb = cpu_baseline_entry(res, TOKENS)
     line = {
         "impl": "reference", "metric": "q4k_moe_decode_tokens_per_s", "value": value, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": t_layer * LAYERS * 1e3, "higher_is_better": True, "scaling": "strong",
+        "n_gpus": args.gpus, "steps": res["steps_timed"], "warmup": args.warmup,
+        "ms_per_step": res["t_step_s"] * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 dots, fp32 accumulate", "data": "synthetic",
-        "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": res["cores"], "kind": res["kind"],
-                         "sample": sample},
+        "config": dict(workload_config(args.gpus), zipf_alpha=alpha),
+        "cpu_baseline": cb,
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
@@ -303,7 +342,7 @@ def workload_config(n_gpus):
 
 
 # ---------------------------------------------------------------------------------------
-def run_prefill_bench(args, device):
+def prefill_measure(args, device, sampler=None):
     """Prefill chunk of one MoE layer: 2048 token rows, top-8 of 256 experts, router logits
     drawn uniformly (about 64 rows per expert), expert math on the int8 tensor-core grouped
     GEMM. A step = quantise, top-k, plan, gather, gate/up/down grouped GEMMs, SwiGLU,
@@ -338,10 +377,12 @@ def run_prefill_bench(args, device):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / reps
 
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
+    own_sampler = sampler is None
+    if own_sampler:
+        sampler = ClockSampler(torch.cuda.current_device())
+        sampler.start()
     ms_step = timed(step, args.steps)
-    # the three routed grouped GEMMs alone (plan and gathered rows still in place)
+    # the routed expert stage alone: gate, up, SwiGLU, requantise, down (plan and gathered rows still in place)
     ms_gemm = timed(lambda: layer.run(n, xn, x, w, table, experts_only=True), args.steps)
     h_xn, h_x = xn.cpu().pin_memory(), x0.cpu().pin_memory()
     h_lg = logits.cpu().pin_memory()
@@ -355,7 +396,7 @@ def run_prefill_bench(args, device):
         h_out.copy_(x, non_blocking=True)
 
     ms_e2e = timed(e2e_step, args.steps)
-    clocks = sampler.stop()
+    clocks = sampler.stop() if own_sampler else None
     off = layer.off.cpu().numpy()
     rows = np.diff(off)
     routed = int(rows.sum())
@@ -380,10 +421,10 @@ def run_prefill_bench(args, device):
                 "h2d_bytes_per_step": int(h_xn.numel() * 2 + h_x.numel() * 2 + h_lg.numel() * 4),
                 "d2h_bytes_per_step": int(h_out.numel() * 2)},
         "gpu_launches": 15 * args.steps, "clocks": clocks,
-        "roofline": {"kernel": "grouped_gemm_i8_kernel (gate, up, down launches)", "bound": "tensor",
+        "roofline": {"kernel": "grouped_gemm_i8_kernel (gate, up, down launches; the timed region also holds the SwiGLU and requantise launches between them)", "bound": "tensor",
                      "achieved": tops, "peak": i8_peak, "unit": "TOP/s", "frac": tops / i8_peak,
                      "peak_source": "2 x measured cuBLAS bf16 burst rate (dense int8 runs at twice bf16)",
-                     "traffic": None, "ms_three_launches": ms_gemm,
+                     "traffic": None, "ms_expert_stage": ms_gemm,
                      "hbm": {"achieved": gbs, "peak": float(peaks["hbm_gbs"]), "unit": "GB/s",
                              "frac": gbs / float(peaks["hbm_gbs"]), "bytes": gemm_bytes}},
     }
@@ -411,10 +452,27 @@ def run_prefill_bench(args, device):
                                                           x.float().abs().max())}
         except Exception as exc:
             line["gpu_baseline"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
-    print(json.dumps(line))
+    return line
 
 
-def run_gemv_bench(args, device):
+def run_prefill_bench(args, device):
+    print(json.dumps(prefill_measure(args, device)))
+
+
+def prefill_config_leg(args, device):
+    """config[3] inside the default line: the prefill chunk, compact."""
+    line = prefill_measure(args, device, sampler=False)
+    r = line["roofline"]
+    out = {"workload": line["config"]["workload"], "tokens_per_s": line["value"], "ms_per_step": line["ms_per_step"],
+           "e2e_tokens_per_s": line["e2e"]["value"], "ms_expert_stage": r["ms_expert_stage"],
+           "tensor_frac_of_int8_peak": r["frac"], "tops": r["achieved"], "hbm_frac": r["hbm"]["frac"], "hbm_gbs": r["hbm"]["achieved"],
+           "binding": "hbm (227 op/B at ~64 rows per expert is below the int8 ridge of ~500 op/B)"}
+    if "gpu_baseline" in line:
+        out["gpu_baseline"] = line["gpu_baseline"]
+    return out
+
+
+def gemv_measure(args, device, shapes=None, sampler=None):
     """Dense Q4_K x Q8_K GEMV sweep (config[1]): the five shapes at batch 1 and 4, weights drawn
     from N(0, 0.02), activations from N(0, 1) and Q8-quantised by the library. Each shape is timed
     over enough distinct weight copies to exceed L2 (the small matrices would otherwise be served
@@ -422,7 +480,7 @@ def run_gemv_bench(args, device):
     import torch
     from sager_b200 import lib, ops, synth
     peak, kind = load_peaks()
-    shapes = [(4096, 2048), (2048, 4096), (512, 2048), (2048, 512), (151936, 2048)]
+    shapes = shapes or [(4096, 2048), (2048, 4096), (512, 2048), (2048, 512), (151936, 2048)]
     if args.shape:
         shapes = [tuple(int(v) for v in args.shape.split(","))]
     rows_out = []
@@ -431,8 +489,10 @@ def run_gemv_bench(args, device):
         from oracle import ref_cuda
         if ref_cuda.available():
             ref = ref_cuda.reference_launchers()      # the reference's own kernels, timed on the same buffers
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
+    own_sampler = sampler is None
+    if own_sampler:
+        sampler = ClockSampler(torch.cuda.current_device())
+        sampler.start()
     for rows, k in shapes:
         wbytes = rows * (k // 256) * 144
         copies = max(1, min(512, (192 << 20) // wbytes + 1))       # > 126 MB L2 in flight per sweep
@@ -478,7 +538,7 @@ def run_gemv_bench(args, device):
                 row["reference_cuda_us"] = ref_us
                 row["reference_cuda_gbs"] = wbytes / ref_us / 1e3
             rows_out.append(row)
-    clocks = sampler.stop()
+    clocks = sampler.stop() if own_sampler else None
     head = max((r for r in rows_out if r["batch"] == 1), key=lambda r: r["rows"] * r["k"])
     line = {
         "metric": "q4k_gemv_hbm_gbs", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
@@ -494,7 +554,20 @@ def run_gemv_bench(args, device):
     }
     if lib().raw("sgr_status")(0) != 0:
         line["device_status"] = "a bounded device-side wait gave up"
-    print(json.dumps(line))
+    return line
+
+
+def run_gemv_bench(args, device):
+    print(json.dumps(gemv_measure(args, device)))
+
+
+def gemv_config_leg(args, device):
+    """config[1] inside the default line: all five shapes at batch 1 and 4, with the reference's own
+    CUDA kernels timed on the same buffers."""
+    line = gemv_measure(args, device, sampler=False)
+    keys = ("rows", "k", "batch", "us", "gbs", "frac", "reference_cuda_us")
+    return {"workload": line["config"]["workload"], "lm_head_gbs": line["value"], "lm_head_frac": line["roofline"]["frac"],
+            "sweep": [{k: r[k] for k in keys if k in r} for r in line["sweep"]]}
 
 
 def run_tc_bench(args, device):
@@ -570,6 +643,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-configs", action="store_true",
+                    help="decode: skip the `configs` block (1 and 4 token rows, GEMV sweep points, prefill chunk)")
     ap.add_argument("--no-gpu-baseline", action="store_true",
                     help="skip the leg that times the reference's own CUDA kernels on this GPU")
     ap.add_argument("--layers", type=int, default=LAYERS, help="shrink the stack (profiling captures)")
@@ -632,117 +707,53 @@ def main():
 
     ws, inputs, x0, biases, alpha = build_workload(device, rank, world, LAYERS, TOKENS)
     n = TOKENS
-    stack = MoeStack(ws, n, K, device, biases=biases, inputs=inputs, per_layer_ws=True, kernel=args.kernel)
-    stack.x.copy_(x0)
-    stack.capture(n)
-
-    # ---- value: graph replays, inputs resident ---------------------------------------
-    def step():
-        stack.x.copy_(x0, non_blocking=True)
-        stack.replay()
-
-    for _ in range(args.warmup):
-        step()
-    torch.cuda.synchronize()
     sampler = ClockSampler(local_rank)
-    sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(args.steps):
-        step()
-    ev1.record()
-    torch.cuda.synchronize()
-    ms_step = ev0.elapsed_time(ev1) / args.steps
-    value = n / (ms_step * 1e-3)
-
-    # ---- e2e: host buffers in, host buffer out ------------------------------------------
-    h_in = torch.empty(LAYERS + 1, n, H, dtype=torch.float16).pin_memory()
-    h_in[0].copy_(x0.cpu())
-    for li in range(LAYERS):
-        h_in[li + 1].copy_(inputs[li].cpu())
-    d_in = torch.empty(LAYERS + 1, n, H, dtype=torch.float16, device=device)
-    h_out = torch.empty(n, H, dtype=torch.float16).pin_memory()
-    stack_inputs_backup = stack.inputs
-    # the graph reads stack.inputs[l]; point them at d_in by copying into place each step
-    def e2e_step():
-        d_in.copy_(h_in, non_blocking=True)
-        stack.x.copy_(d_in[0], non_blocking=True)
-        for li in range(LAYERS):
-            stack_inputs_backup[li].copy_(d_in[li + 1], non_blocking=True)
-        stack.replay()
-        h_out.copy_(stack.x, non_blocking=True)
-
-    for _ in range(3):
-        e2e_step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e1.record()
-    torch.cuda.synchronize()
-    clocks = sampler.stop()
-    ms_e2e = e0.elapsed_time(e1) / args.steps
-    e2e = {"value": n / (ms_e2e * 1e-3), "unit": "tokens/s",
-           "h2d_bytes_per_step": int(h_in.numel() * 2), "d2h_bytes_per_step": int(h_out.numel() * 2)}
-
-    # ---- roofline of the dominant kernel: gate/up of every layer, back to back -------------
-    idx = stack.idx.cpu().numpy()[:, :n, :K]
-    uniq = [len(np.unique(idx[li])) for li in range(LAYERS)]
-    ex_bytes = sum((u + 1) * EXPERT_BYTES for u in uniq)
-    step_bytes = sum((u + 1) * EXPERT_BYTES + ROUTER_BYTES for u in uniq)
-    stage_ms = {}
-    for name, mask in (("route", 1), ("experts", 6)):
-        g = stack.capture_stage(n, mask)          # that stage of all layers, back to back
-        g.replay()
-        torch.cuda.synchronize()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 3
-        s0.record()
-        for _ in range(reps):
-            g.replay()
-        s1.record()
-        torch.cuda.synchronize()
-        stage_ms[name] = s0.elapsed_time(s1) / reps
-    peak, peak_kind = load_peaks()
-    ex_gbs = ex_bytes / (stage_ms["experts"] * 1e-3) / 1e9
-    use_rows = args.kernel == "rows" or (args.kernel is None and n >= 4)
-    kernel = "expert_rows_kernel" if use_rows else "expert_stream_kernel"
-    # DRAM traffic per launch: one ncu capture of this kernel on the 4-layer stack read 295.3 MB and
-    # wrote 6.1 MB for 284.4 MB of algorithmic bytes (profiles/); scaled by the bytes of this run's launches
-    traffic = (295.3e6 + 6.1e6) / 284.44e6 * (ex_bytes / LAYERS) if use_rows else None
-    roofline = {"kernel": kernel, "bound": "hbm", "achieved": ex_gbs, "peak": peak,
-                "unit": "GB/s", "frac": ex_gbs / peak, "peak_source": f"{peak_kind} copy bandwidth (burst)",
-                "traffic": traffic,
-                "traffic_source": "ncu dram__bytes_read+write of a 4-layer capture, scaled by algorithmic bytes",
-                "bytes_per_launch": ex_bytes / LAYERS, "us_per_launch": stage_ms["experts"] * 1e3 / LAYERS,
-                "stage_ms_per_step": stage_ms,
-                "step": {"algorithmic_bytes": step_bytes, "gbs": step_bytes / (ms_step * 1e-3) / 1e9,
-                         "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak}}
-    from sager_b200 import synth
-    hot = float(np.mean([synth.hot_share(idx[li], E) for li in range(LAYERS)]))
+    sampler.start()                      # runs across every timed region of this process
+    main_leg = decode_leg(ws, inputs, x0, biases, n, args, device, e2e=True)
+    ms_step, value, e2e, roofline = main_leg["ms_step"], main_leg["value"], main_leg["e2e"], main_leg["roofline"]
 
     line = {
         "metric": "q4k_moe_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8 dots, fp32 accumulate",
         "data": "synthetic",
-        "config": dict(workload_config(1), zipf_alpha=alpha, hot20_share=hot,
-                       distinct_experts_per_layer=float(np.mean(uniq))),
-        "e2e": e2e, "gpu_launches": stack.launches_per_step * args.steps, "clocks": clocks,
+        "config": dict(workload_config(1), layers=LAYERS, tokens=n, zipf_alpha=alpha, hot20_share=main_leg["hot"],
+                       distinct_experts_per_layer=main_leg["uniq_mean"]),
+        "e2e": e2e, "gpu_launches": main_leg["launches_per_step"] * args.steps,
         "roofline": roofline,
     }
+    if not args.no_configs and n == 64 and LAYERS == 40:
+        # the other configurations of the benchmark, measured in the same run (a few seconds each)
+        cfgs = {}
+        for name, tok, use_bias in (("tokens1", 1, False), ("tokens4", 4, True)):
+            try:
+                leg = decode_leg(ws, inputs, x0, biases if use_bias else None, tok, args, device, e2e=False)
+                cfgs[name] = {
+                    "workload": ("one token row through the 40-layer stack (the single-token layer x 40)" if tok == 1 else
+                                 "verify window: 4 token rows through the 40-layer stack, Zipf-skewed routing"),
+                    "tokens_per_s": leg["value"], "ms_per_step": leg["ms_step"], "us_per_layer": leg["ms_step"] * 1e3 / LAYERS,
+                    "distinct_experts_per_layer": leg["uniq_mean"],
+                    "step_frac_of_hbm_peak": leg["roofline"]["step"]["frac"],
+                    "expert_kernel": leg["roofline"]["kernel"], "expert_kernel_frac": leg["roofline"]["frac"],
+                    "expert_kernel_us": leg["roofline"]["us_per_launch"],
+                    "stage_ms_per_step": leg["roofline"]["stage_ms_per_step"]}
+            except Exception as exc:
+                cfgs[name] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+        for name, fn in (("gemv", gemv_config_leg), ("prefill", prefill_config_leg)):
+            try:
+                cfgs[name] = fn(args, device)
+            except Exception as exc:
+                cfgs[name] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+        line["configs"] = cfgs
+    line["clocks"] = sampler.stop()
     if lib().raw("sgr_status")(0) != 0:
         line["device_status"] = "a bounded device-side wait gave up"
     if not args.no_cpu_baseline:
         res = cpu_pool_sample(ws[0], inputs[0], biases[0])
-        line["cpu_baseline"] = {
-            "value": n / (res["t_layer_s"] * LAYERS), "unit": "tokens/s", "cores": res["cores"],
-            "kind": res["kind"],
-            "sample": f"layer 0 of the stack ({n} rows: router + {n * (K + 1)} expert FFNs through the "
-                      f"CPU pool), median of {res['layers_timed']} runs; step time = {LAYERS} x layer time"}
+        line["cpu_baseline"] = cpu_baseline_entry(res, n)
     if not args.no_gpu_baseline:
-        stack.x.copy_(x0)
+        stack = main_leg["stack"]
+        stack.x.copy_(x0[:n])
         stack.replay()
         torch.cuda.synchronize()
         try:
@@ -752,6 +763,103 @@ def main():
         if gpu_ref is not None:
             line["gpu_baseline"] = gpu_ref
     print(json.dumps(line))
+
+
+def decode_leg(ws, inputs, x0, biases, n, args, device, e2e):
+    """One decode measurement over the layer stack with n token rows: graph-replayed steps with
+    the inputs resident (value), optionally the same through host buffers (e2e), and each stage of
+    all layers back to back (the roofline of the expert kernel)."""
+    import torch
+    from sager_b200 import synth
+    from sager_b200.layer import MoeStack
+    layers = len(ws)
+    stack = MoeStack(ws, n, K, device, biases=biases, inputs=inputs, per_layer_ws=True, kernel=args.kernel)
+    stack.x.copy_(x0[:n])
+    stack.capture(n)
+
+    def step():
+        stack.x.copy_(x0[:n], non_blocking=True)
+        stack.replay()
+
+    def timed(fn, reps):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    for _ in range(args.warmup):
+        step()
+    ms_step = timed(step, args.steps)
+    out = {"stack": stack, "ms_step": ms_step, "value": n / (ms_step * 1e-3),
+           "launches_per_step": stack.launches_per_step, "e2e": None}
+
+    if e2e:
+        # host buffers in, host buffer out: the 40 layer inputs and the residual rows come from
+        # pinned host memory every step, the result goes back
+        h_in = torch.empty(layers + 1, n, H, dtype=torch.float16).pin_memory()
+        h_in[0].copy_(x0[:n].cpu())
+        for li in range(layers):
+            h_in[li + 1].copy_(inputs[li][:n].cpu())
+        d_in = torch.empty(layers + 1, n, H, dtype=torch.float16, device=device)
+        h_out = torch.empty(n, H, dtype=torch.float16).pin_memory()
+
+        def e2e_step():
+            d_in.copy_(h_in, non_blocking=True)
+            stack.x.copy_(d_in[0], non_blocking=True)
+            for li in range(layers):
+                inputs[li][:n].copy_(d_in[li + 1], non_blocking=True)     # the graph reads inputs[l] in place
+            stack.replay()
+            h_out.copy_(stack.x, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        ms_e2e = timed(e2e_step, args.steps)
+        out["e2e"] = {"value": n / (ms_e2e * 1e-3), "unit": "tokens/s",
+                      "h2d_bytes_per_step": int(h_in.numel() * 2), "d2h_bytes_per_step": int(h_out.numel() * 2)}
+
+    # ---- roofline of the dominant kernel: the expert kernel of every layer, back to back ----
+    idx = stack.idx.cpu().numpy()[:, :n, :K]
+    uniq = [len(np.unique(idx[li])) for li in range(layers)]
+    ex_bytes = sum((u + 1) * EXPERT_BYTES for u in uniq)
+    step_bytes = sum((u + 1) * EXPERT_BYTES + ROUTER_BYTES for u in uniq)
+    stage_ms = {}
+    for name, mask in (("route", 1), ("experts", 6)):
+        g = stack.capture_stage(n, mask)          # that stage of all layers, back to back
+        g.replay()
+        stage_ms[name] = timed(g.replay, 5)
+    peak, peak_kind = load_peaks()
+    ex_gbs = ex_bytes / (stage_ms["experts"] * 1e-3) / 1e9
+    use_rows = args.kernel == "rows" or (args.kernel is None and n >= 4)
+    kernel = "expert_rows_kernel" if use_rows else "expert_stream_kernel"
+    traffic, traffic_source = traffic_per_launch(kernel, ex_bytes / layers)
+    out["roofline"] = {"kernel": kernel, "bound": "hbm", "achieved": ex_gbs, "peak": peak,
+                       "unit": "GB/s", "frac": ex_gbs / peak, "peak_source": f"{peak_kind} copy bandwidth (burst)",
+                       "frac_of_nominal_8tbs": ex_gbs / 8000.0,
+                       "traffic": traffic, "traffic_source": traffic_source,
+                       "bytes_per_launch": ex_bytes / layers, "us_per_launch": stage_ms["experts"] * 1e3 / layers,
+                       "stage_ms_per_step": stage_ms,
+                       "step": {"algorithmic_bytes": step_bytes, "gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+                                "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak}}
+    out["uniq_mean"] = float(np.mean(uniq))
+    out["hot"] = float(np.mean([synth.hot_share(idx[li], E) for li in range(layers)]))
+    return out
+
+
+def traffic_per_launch(kernel, algorithmic_bytes):
+    """DRAM bytes per launch of `kernel` from the ncu capture recorded in profiles/traffic.json
+    (dram__bytes_read.sum + dram__bytes_write.sum of a smaller case of the same kernel), scaled to
+    this run's launch by the algorithmic bytes; (None, reason) when no capture of it is recorded."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        rec = json.load(open(path))[kernel]
+        scale = (rec["dram_read_bytes"] + rec["dram_write_bytes"]) / rec["algorithmic_bytes"]
+        return scale * algorithmic_bytes, f"profiles/traffic.json: {rec['source']}; scaled by algorithmic bytes"
+    except (OSError, KeyError, ValueError):
+        return None, "no ncu capture of this kernel is recorded in profiles/traffic.json"
 
 
 if __name__ == "__main__":

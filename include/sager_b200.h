@@ -15,7 +15,11 @@
  * Conventions kept from the reference (cuda_ops.hpp:1-14): all calls are
  * stream-ordered and never synchronise; all buffers are caller-owned device
  * pointers; per-step values (row counts, tile counts, residency) are read from
- * fixed-address device memory, so every call is legal inside stream capture.
+ * fixed-address device memory, so every call is legal inside stream capture -
+ * with one exception: the first call of the library on a device looks up the
+ * address of its status word (cudaGetSymbolAddress) and must be made outside
+ * capture; until that has happened the entry points that need the word return
+ * SGR_ELAUNCH inside a capture.
  * fp16 values travel as uint16_t. A null pointer-table entry means "expert
  * not resident": its output rows are written as zero and, for the gate/up
  * call, the expert id is posted to the mailbox.
@@ -209,7 +213,7 @@ typedef struct sgr_moe_layer {
   const void* xq_in;     /* optional [n][hidden/256] Q8_K blocks: skip the quantiser */
   const float* router_w; /* [n_expert][hidden] */
   const float* router_bias; /* optional [n_expert], added to the logits */
-  const void* const* w_tab; /* [3][n_expert] device pointers to Q4_K matrices */
+  const void* const* w_tab; /* [3][n_expert] device pointers to Q4_K matrices (slices tab_stride apart) */
   const void* shared_gate;  /* shared expert matrices, or all NULL */
   const void* shared_up;
   const void* shared_down;
@@ -235,6 +239,10 @@ typedef struct sgr_moe_layer {
    * 8 sums, 16-byte aligned) instead of packed 276-byte ones: set for both the route stage that
    * writes them (xq_out) and the owner that reads them (xq_in, routing_given, >= 4 rows). */
   int xq_padded;
+  /* pointers between the gate, up and down slices of w_tab; 0 = n_expert (a packed [3][E] table).
+   * The reference's decode table is [3][Lm][E] (src/core/session.cpp:3596-3598): pass
+   * w_tab = table + layer * E and tab_stride = Lm * E to use it in place. */
+  long long tab_stride;
 } sgr_moe_layer;
 
 size_t sgr_moe_layer_workspace_bytes(int n_max, int hidden, int n_ff, int n_expert, int n_used);
@@ -246,18 +254,6 @@ int sgr_moe_layer_decode(const sgr_moe_layer* args, void* stream);
  * at a time and for the home side of an expert-parallel layer. */
 int sgr_moe_layer_decode_stages(const sgr_moe_layer* args, int stages, void* stream);
 
-/* No counterpart in the reference. sgr_moe_layer_decode for callers that cannot
- * allocate device memory - an engine whose whole VRAM budget was handed out at
- * start-up (KV cache, expert slab) and that treats any later cudaMalloc as a bug,
- * a host binding with no way to own CUDA buffers, code that only ever runs inside a
- * captured region. The scratch is a file-scope device array inside the library,
- * sgr_moe_layer_static_limit() bytes (1 MiB: e.g. 8 token rows at hidden 2048,
- * expert FFN 512, 256 experts, top-8); `workspace` / `workspace_bytes` of the
- * argument block are ignored, inputs and outputs are still the caller's. A shape
- * whose scratch would not fit returns SGR_ESTATICLIMIT and launches nothing. The first
- * call on each device looks up the array's device address and must be made outside
- * stream capture. Every call on a device uses the same array: calls that overlap on
- * the GPU race. */
 /* Prefill grouped GEMM on int8 tensor cores (tcgen05, accumulators in tensor memory).
  * Replaces dequant_experts_q4_k_f16 + tc_gemm_f16_raw (cuda_ops.hpp:125-131, one cuBLAS GEMM per
  * expert and matrix) with the contract of gemv_grouped_tab_q4_k_q8_f16out_mtok (cuda_ops.hpp:247):
@@ -266,6 +262,53 @@ int sgr_moe_layer_decode_stages(const sgr_moe_layer* args, int stages, void* str
  * arithmetic is that of the Q4_K x Q8_K path (exact sub-block dots), not of the fp16 GEMM. */
 int sgr_moe_grouped_gemm_i8(const void* const* w_tab, const int* off, const void* xq, uint16_t* y,
                             int n_rows, int k, int n_expert, void* stream);
+
+/* ---- one MoE layer over a prefill chunk, behind one call -----------------------------------
+ * The launch sequence of Session::moe_dispatch_device for a chunk of n token rows
+ * (src/core/session.cpp:2482-3030 of the reference) on the session's own scratch buffers
+ * (src/core/session.cpp:207-257; shapes below with R = n_max * n_used): quantise, router logits,
+ * top-k, device plan, gather, gate / up, SwiGLU, requantise, down, scatter, shared expert,
+ * combine into x_f16. The routed projections run on sgr_moe_grouped_gemm_i8; every other step is
+ * the library's launcher of the same name. Stream-ordered, allocates nothing. */
+typedef struct sgr_moe_prefill {
+  int n, n_max;             /* token rows of this chunk / rows the buffers were sized for */
+  int hidden, n_ff, n_expert, n_used;
+  int tok_per;              /* rows per tile of the device plan (0 = 16) */
+  float shared_w;           /* weight of the shared expert (slot K of route_w), 1.0 in the reference */
+  const uint16_t* xn;       /* [n][hidden] fp16 layer input */
+  const float* router_w;    /* [n_expert][hidden]; unused when logits_in is given */
+  const float* logits_in;   /* optional [n][n_expert]: skip the router GEMV */
+  const void* const* w_tab; /* gate / up / down slices of n_expert pointers, tab_stride apart */
+  long long tab_stride;     /* 0 = n_expert */
+  const void* shared_gate;  /* shared expert matrices, or all NULL */
+  const void* shared_up;
+  const void* shared_down;
+  const float* shared_gate_w; /* optional [hidden] scalar gate of the shared expert (needs sgate) */
+  uint16_t* x_f16;          /* [n][hidden] residual stream, combined in place */
+  void* xq;                 /* [n_max][hidden/256] Q8_K blocks */
+  float* logits;            /* [n_max][n_expert] */
+  int* route_idx;           /* [n_max][n_used+1] */
+  float* route_w;           /* [n_max][n_used+1] */
+  int* gslot;               /* [R] */
+  int* grows;               /* [R] */
+  int* off;                 /* [n_expert+1] */
+  int* toff;                /* [n_expert+1] */
+  int* meta;                /* [4] */
+  int* mail;                /* [n_expert] */
+  int* mail_n;              /* [1] */
+  void* xqg;                /* [R][hidden/256] Q8_K blocks, 16-byte aligned */
+  uint16_t* g;              /* [R][n_ff] */
+  uint16_t* u;              /* [R][n_ff] */
+  void* hq;                 /* [R][n_ff/256] Q8_K blocks, 16-byte aligned */
+  uint16_t* y_grouped;      /* [R][hidden] */
+  uint16_t* expert_y;       /* [n_max][n_used+1][hidden] combine slab */
+  uint16_t* sh_g;           /* [n_max][n_ff] */
+  uint16_t* sh_u;           /* [n_max][n_ff] */
+  void* sh_q;               /* [n_max][n_ff/256] Q8_K blocks */
+  uint16_t* sh_y;           /* [n_max][hidden] */
+  float* sgate;             /* [n_max], only with shared_gate_w */
+} sgr_moe_prefill;
+int sgr_moe_layer_prefill(const sgr_moe_prefill* args, void* stream);
 
 /* ---- the fp16 tensor-core family of the prefill path (cuda_ops.hpp:104-152) ----------------
  * The reference dequantises Q4_K to fp16 and calls a library GEMM; here the GEMM is the
@@ -298,9 +341,6 @@ int sgr_dequant_q4_k_f16(const void* w, uint16_t* out16, int n_rows, int k, void
 /* tc_router_f32 (cuda_ops.hpp:143-145): router weights cast to fp16 in scratch, fp32 logits. */
 int sgr_tc_router_f32(const float* w_f32, const uint16_t* x, float* y, uint16_t* scratch, int n_rows,
                       int k, int n_tokens, void* stream);
-/* Operand tile layout of the GEMM kernel: 0 = 128-byte swizzled tiles (default), 1 = unswizzled
- * core matrices. Same results; a diagnostic, not part of the reference's surface. */
-int sgr_tc_set_operand_layout(int layout);
 
 /* Expert parallelism, last step on the home rank (no counterpart in the reference, which is
  * single-GPU): x[i] = f16(f32(x[i]) + sum_p parts[p*part_stride + i]), p ascending. */
@@ -321,9 +361,28 @@ int sgr_ep_push(const void* src, long long src_stride, long long bytes, void* co
 int sgr_ep_reduce_add_f16_wait(uint16_t* x_f16, const float* parts, int n_parts, long long part_stride,
                                long long count, const unsigned* flags, const unsigned* step, int mul,
                                int add, void* stream);
+/* How long a kernel that waits for a peer's arrival words (the plan of an owner-side layer with
+ * wait_flags, sgr_ep_reduce_add_f16_wait) polls before it gives up: `polls` loads, 64 ns apart, per
+ * word (default 1 << 22, several seconds). A kernel whose wait runs out sets the status word to 8 and
+ * returns with the context intact - the plan then reads the records of an earlier step, the home
+ * reduction leaves x_f16 as it was - so a rank that stopped posting turns into an error code that the
+ * host reads with sgr_status, not into a hang. Applies to launches made after the call. */
+int sgr_ep_set_wait_limit(int polls);
 /* *step += 1 (one thread), in stream order: the end of a step. */
 int sgr_ep_step_advance(unsigned* step, void* stream);
 
+/* No counterpart in the reference. sgr_moe_layer_decode for callers that cannot
+ * allocate device memory - an engine whose whole VRAM budget was handed out at
+ * start-up (KV cache, expert slab) and that treats any later cudaMalloc as a bug,
+ * a host binding with no way to own CUDA buffers, code that only ever runs inside a
+ * captured region. The scratch is a file-scope device array inside the library,
+ * sgr_moe_layer_static_limit() bytes (2 MiB: at hidden 2048, expert FFN 512, 256 experts,
+ * top-8 that is up to n_max = 16 token rows; n_max = 8 needs 1.3 MB); `workspace` / `workspace_bytes` of the
+ * argument block are ignored, inputs and outputs are still the caller's. A shape
+ * whose scratch would not fit returns SGR_ESTATICLIMIT and launches nothing. The first
+ * call on each device looks up the array's device address and must be made outside
+ * stream capture. Every call on a device uses the same array: calls that overlap on
+ * the GPU race. */
 size_t sgr_moe_layer_static_limit(void);
 int sgr_moe_layer_decode_static(const sgr_moe_layer* args, void* stream);
 

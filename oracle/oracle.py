@@ -24,9 +24,16 @@ _i = C.c_int
 _f = C.c_float
 
 
-def build(ref_root: str = "/root/reference") -> None:
+def reference_root() -> str:
+    """Where the reference's source tree lies: $SAGER_REFERENCE, else a directory named
+    `reference` beside this repository."""
+    return os.environ.get("SAGER_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(ref_root: str | None = None) -> None:
     """Compile the C restatement and, when the reference tree is present, the
     reference's own CPU sources."""
+    ref_root = ref_root or reference_root()
     subprocess.check_call(["make", "-s", "-C", HERE, "oracle"])
     if os.path.isdir(ref_root):
         subprocess.check_call(["make", "-s", "-C", HERE, "ref", f"REF={ref_root}"],

@@ -14,6 +14,7 @@ import re
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 HEADER = os.path.join(ROOT, "include", "sager_b200.h")
+DIAG_HEADER = os.path.join(ROOT, "include", "sager_b200_diag.h")
 LIB_PATH = os.path.join(HERE, "libsager_b200.so")
 
 ERRORS = {1: "SGR_EARG", 2: "SGR_EALIGN", 3: "SGR_EUNSUPPORTED", 4: "SGR_ELAUNCH", 5: "SGR_EGEOMETRY",
@@ -34,7 +35,7 @@ def parse_header(path: str = HEADER):
     text = open(path).read()
     text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
     protos = {}
-    for m in re.finditer(r"\b(int|void\s*\*|void|size_t)\s*(sgr_\w+)\s*\(([^)]*)\)\s*;", text):
+    for m in re.finditer(r"\b(int|long long|void\s*\*|void|size_t)\s*(sgr_\w+)\s*\(([^)]*)\)\s*;", text):
         ret, name, args = "".join(m.group(1).split()), m.group(2), m.group(3).strip()
         argtypes = []
         if args and args != "void":
@@ -45,7 +46,7 @@ def parse_header(path: str = HEADER):
                 else:
                     base = a.rsplit(" ", 1)[0].replace("const ", "").strip()
                     argtypes.append(_SCALARS[base])
-        protos[name] = ({"int": C.c_int, "size_t": C.c_size_t, "void": None, "void*": C.c_void_p}[ret], argtypes)
+        protos[name] = ({"int": C.c_int, "longlong": C.c_longlong, "size_t": C.c_size_t, "void": None, "void*": C.c_void_p}[ret], argtypes)
     return protos
 
 
@@ -57,7 +58,7 @@ class Lib:
                 "(there is no CPU or PyTorch fallback)")
         self.path = path
         self.cdll = C.CDLL(path)
-        self.protos = parse_header()
+        self.protos = dict(parse_header(), **parse_header(DIAG_HEADER))
         missing = []
         for name, (res, args) in self.protos.items():
             try:
@@ -101,6 +102,27 @@ class MoeLayerArgs(C.Structure):
         ("wait_flags", C.c_void_p), ("wait_step", C.c_void_p),
         ("wait_count", C.c_int), ("wait_mul", C.c_int), ("wait_add", C.c_int),
         ("xq_padded", C.c_int),
+        ("tab_stride", C.c_longlong),
+    ]
+
+
+class MoePrefillArgs(C.Structure):
+    """struct sgr_moe_prefill of include/sager_b200.h."""
+    _fields_ = [
+        ("n", C.c_int), ("n_max", C.c_int),
+        ("hidden", C.c_int), ("n_ff", C.c_int), ("n_expert", C.c_int), ("n_used", C.c_int),
+        ("tok_per", C.c_int), ("shared_w", C.c_float),
+        ("xn", C.c_void_p), ("router_w", C.c_void_p), ("logits_in", C.c_void_p),
+        ("w_tab", C.c_void_p), ("tab_stride", C.c_longlong),
+        ("shared_gate", C.c_void_p), ("shared_up", C.c_void_p), ("shared_down", C.c_void_p),
+        ("shared_gate_w", C.c_void_p),
+        ("x_f16", C.c_void_p), ("xq", C.c_void_p), ("logits", C.c_void_p),
+        ("route_idx", C.c_void_p), ("route_w", C.c_void_p), ("gslot", C.c_void_p), ("grows", C.c_void_p),
+        ("off", C.c_void_p), ("toff", C.c_void_p), ("meta", C.c_void_p), ("mail", C.c_void_p),
+        ("mail_n", C.c_void_p), ("xqg", C.c_void_p), ("g", C.c_void_p), ("u", C.c_void_p),
+        ("hq", C.c_void_p), ("y_grouped", C.c_void_p), ("expert_y", C.c_void_p),
+        ("sh_g", C.c_void_p), ("sh_u", C.c_void_p), ("sh_q", C.c_void_p), ("sh_y", C.c_void_p),
+        ("sgate", C.c_void_p),
     ]
 
 

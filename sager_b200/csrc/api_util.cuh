@@ -10,6 +10,7 @@
 #include <stdint.h>
 
 #include "sager_b200.h"   // the public prototypes: definitions must agree with them
+#include "sager_b200_diag.h"
 
 #define SGR_API extern "C" __attribute__((visibility("default")))
 

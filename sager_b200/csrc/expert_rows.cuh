@@ -45,11 +45,7 @@ constexpr int kConsumerWarps = 16;
 constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kXWarps = 3;                      // activation-row producers
 constexpr int kXThreads = kXWarps * 32;
-#ifdef SGR_PROFILE
-constexpr int kThreads = kConsumers + 32 + kXThreads + 32 + 64; // + two observer warps (profiling builds)
-#else
 constexpr int kThreads = kConsumers + 32 + kXThreads + 32;      // consumers, weight warp, activation warps, finisher warp
-#endif
 constexpr int kStageCount = 5;
 constexpr int kHalfRows = 128;                  // a stage is two halves of 128 rows
 constexpr int kHalfBytes = kHalfRows * kW4;     // 18432
@@ -65,9 +61,12 @@ constexpr int kGateUpPairs = 128;               // pairs per gate/up group
 constexpr int kDownRows = 256;                  // rows per down group
 constexpr int kCombineRows = 64;
 constexpr int kFullArrivals = 32 + kXThreads;     // weight warp: one arrival per lane; activation warps: copies landed
-constexpr int kMapRing = 4;                      // descriptor slots per CTA and matrix
+constexpr int kMapRing = kStageCount + 1;        // descriptor slots per CTA: a slot is patched again only after every
+                                                 // stage that could still reference it has been refilled (a tile has at
+                                                 // least one stage, and at most kStageCount stages are in flight)
 
 static_assert(kSmem <= 227 * 1024, "ring exceeds shared memory");
+static_assert(kMapRing <= kTmapSlots, "the workspace holds kTmapSlots descriptor sets per CTA");
 
 struct Desc {     // one 16-byte shared-memory load per stage and warp
   int flags;     // bit 0 kind (0 gate/up, 1 down), bit 1 expert absent, bits 2-7 token rows,
@@ -296,8 +295,8 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
         rc = __ldcg(L.rec + wk.tile);
         const bool shared = rc.x == L.E;
         w0 = shared ? L.sh[0] : L.tab[rc.x];
-        w1 = shared ? L.sh[1] : L.tab[L.E + rc.x];
-        w2 = shared ? L.sh[2] : L.tab[2 * L.E + rc.x];
+        w1 = shared ? L.sh[1] : L.tab[L.tab_stride + rc.x];
+        w2 = shared ? L.sh[2] : L.tab[2 * L.tab_stride + rc.x];
         absent = w0 == nullptr || w1 == nullptr || w2 == nullptr;
         aligned = ((reinterpret_cast<uintptr_t>(w0) | reinterpret_cast<uintptr_t>(w1) |
                     reinterpret_cast<uintptr_t>(w2)) & 15u) == 0;
@@ -357,9 +356,6 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
             tma_load_box(st, maps + 256, blk * kW4, wk.gi * kDownRows, &full[s]);
             tma_load_box(st + kHalfBytes, maps + 256, blk * kW4, wk.gi * kDownRows + kHalfRows, &full[s]);
           }
-#ifdef SGR_PROFILE
-          if (q < 120) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); (L.prof + 1024 * 16 + blockIdx.x * 512)[7 + 4 * q] = t; }
-#endif
         } else {
           mbar_arrive(&full[s]);
         }
@@ -419,8 +415,8 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
           rc = __ldcg(L.rec + wk.tile);
           const bool shared = rc.x == L.E;
           const unsigned char* a0 = shared ? L.sh[0] : L.tab[rc.x];
-          const unsigned char* a1 = shared ? L.sh[1] : L.tab[L.E + rc.x];
-          const unsigned char* a2 = shared ? L.sh[2] : L.tab[2 * L.E + rc.x];
+          const unsigned char* a1 = shared ? L.sh[1] : L.tab[L.tab_stride + rc.x];
+          const unsigned char* a2 = shared ? L.sh[2] : L.tab[2 * L.tab_stride + rc.x];
           absent = a0 == nullptr || a1 == nullptr || a2 == nullptr;
         }
         cur_tile = wk.tile;
@@ -518,63 +514,20 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     return;
   }
 
-#ifdef SGR_PROFILE
-  if (warp >= kConsumerWarps + 2 + kXWarps) {
-    // observers: when does each stage become full / free again
-    const bool obs_full = warp == kConsumerWarps + 2 + kXWarps;
-    if (lane == 0) {
-      long long* tr2 = L.prof + 1024 * 16 + 160 * 512 + blockIdx.x * 256;
-      for (int q = 0; q < 120; ++q) {
-        const int s = q % kStageCount;
-        const unsigned ph = (q / kStageCount) & 1;
-        if (!mbar_wait(obs_full ? &full[s] : &empty[s], ph)) break;
-        long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        tr2[2 * q + (obs_full ? 0 : 1)] = t;
-      }
-    }
-    return;
-  }
-#endif
   // ---------------- consumers ----------------
   float acc[2][4];
   bool ok = true;
-#ifdef SGR_TRACE
-  auto gt = []() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
-  long long tl[8] = {0, 0, 0, 0, 0, 0, 0, 0};     // start, first full, gu end, dn start, last done, barrier, end
-  int ncls[3] = {0, 0, 0}, last_kind = 0;
-  if (tid == 0) tl[0] = gt();
-#endif
-#ifdef SGR_PROFILE
-  const int _pw = 0;
-  long long* trace = L.prof + 1024 * 16 + blockIdx.x * 512;
-  auto gtime = []() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
-  if (tid == 0) { trace[0] = gtime(); trace[1] = 0; }
-#endif
-  PROF_T0();
   for (int q = 0;; ++q) {
     const int s = q % kStageCount;
     const unsigned ph = (q / kStageCount) & 1;
-    PROF_ADD(2);
     if (!mbar_wait(&full[s], ph)) {
       if (lane == 0) atomicExch(L.status, 3);
       ok = false;
       break;
     }
-    PROF_ADD(0);
     const Desc d = desc[s];
     if (d.end()) break;
     const int d_kind = d.kind(), d_mode = d.absent(), d_ntok = d.ntok(), d_blk = d.blk(), d_last = d.last(), d_seq = d.seq();
-#ifdef SGR_TRACE
-    if (tid == 0) {
-      if (q == 0) tl[1] = gt();
-      if (d_kind == 1 && last_kind == 0) tl[3] = gt();
-      last_kind = d_kind;
-      ++ncls[d_ntok <= 2 ? 0 : (d_ntok <= 8 ? 1 : 2)];
-    }
-#endif
-#ifdef SGR_PROFILE
-    if (tid == 0 && q < 120) { trace[4 + 4 * q] = gtime(); trace[6 + 4 * q] = d_kind * 1000 + d_ntok * 10 + (d_blk == 0 ? 1 : 0); }
-#endif
     unsigned char* st = stages + static_cast<size_t>(s) * kStageBytes;
     if (d_blk == 0) {
 #pragma unroll
@@ -609,18 +562,6 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[s]);       // this warp no longer reads the stage
-#ifdef SGR_TRACE
-    if (tid == 0 && d_last && true) { if (d_kind == 0) tl[2] = gt(); else tl[4] = gt(); }
-#endif
-#ifdef SGR_PROFILE
-    if (tid == 0 && q < 120) trace[5 + 4 * q] = gtime();
-    if (lane == 0 && warp == 0) {
-      const int cls = d_ntok <= 2 ? 0 : (d_ntok <= 8 ? 1 : 2);
-      atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + blockIdx.x * 16 + 8 + cls), static_cast<unsigned long long>(clock64() - _pt));
-      atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + blockIdx.x * 16 + 11 + cls), 1ull);
-    }
-#endif
-    PROF_ADD(1);
     if (!d_last) continue;
 
     // ---- the group is complete for this warp's rows ----
@@ -659,7 +600,6 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
           }
         }
       }
-      PROF_ADD(5);
       // Count the warp in at the CTA's counter of this group (shared memory); the last
       // warp hands the group to the finisher warp. Groups finish in order: a warp is at
       // most a ring's depth of stages ahead of the slowest one.
@@ -679,8 +619,6 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
           *done_tail = static_cast<unsigned>(d_seq) + 1u;
         }
       }
-      PROF_ADD(6);
-      PROF_ADD(7);
     } else {
       if (d_mode == 1) {
         for (int j = lane; j < 16 * d_ntok; j += 32)
@@ -708,12 +646,10 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
           }
         }
       }
-      PROF_ADD(14);
     }
   }
 
   // ---- all y rows written everywhere: blend ------------------------------------------------
-  PROF_ADD(2);
   __threadfence();
   rs_consumers_sync();
   if (tid == 0) {
@@ -723,13 +659,6 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     flag[0] = (it < kSpinLimit && ok) ? 1 : 0;
   }
   rs_consumers_sync();
-#ifdef SGR_TRACE
-  if (tid == 0) tl[5] = gt();
-#endif
-  PROF_ADD(3);
-#ifdef SGR_PROFILE
-  if (tid == 0) trace[2] = gtime();
-#endif
   if (!flag[0]) {
     if (tid == 0) atomicExch(L.status, 5);
     return;
@@ -741,18 +670,6 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     combine_rows(L, c * kCombineRows, min(kCombineRows, L.H - c * kCombineRows), tg * 16, min(L.n, tg * 16 + 16),
                  tid, kConsumers);
   }
-  PROF_ADD(4);
-#ifdef SGR_PROFILE
-  if (tid == 0) trace[3] = gtime();
-#endif
-#ifdef SGR_TRACE
-  if (tid == 0) {
-    tl[6] = gt();
-    long long* o = L.prof + blockIdx.x * 16;
-    for (int i = 0; i < 7; ++i) o[i] = tl[i];
-    o[8] = ncls[0]; o[9] = ncls[1]; o[10] = ncls[2]; o[11] = ncls[0] + ncls[1] + ncls[2];
-  }
-#endif
 }
 
 }  // namespace rs

@@ -39,14 +39,8 @@
 namespace sgr {
 namespace {
 
-#ifdef SGR_PROFILE
-__device__ unsigned long long g_gemm_prof[32];
-#define GP_T0() long long _gp = clock64()
-#define GP_ADD(i) do { const long long _n = clock64(); atomicAdd(&g_gemm_prof[i], static_cast<unsigned long long>(_n - _gp)); _gp = _n; } while (0)
-#else
 #define GP_T0() do {} while (0)
 #define GP_ADD(i) do {} while (0)
-#endif
 
 constexpr int kGemmRows = 128;     // weight rows per CTA = MMA M
 constexpr int kGemmTok = 64;       // token rows per chunk = max MMA N
@@ -166,9 +160,6 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
   const int m_e = off[e + 1] - row_off;
   if (m_e <= 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef SGR_PROFILE
-  const long long _k0 = clock64();
-#endif
   const int row0 = blockIdx.x * kGemmRows;
   const unsigned char* w = w_tab[e];
   if (w == nullptr) {                                      // absent expert: zero rows
@@ -492,9 +483,6 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (tid == 0 && *fail && status != nullptr) atomicExch(status, 6);
-#ifdef SGR_PROFILE
-  if (tid == 0) { atomicAdd(&g_gemm_prof[11], static_cast<unsigned long long>(clock64() - _k0)); atomicAdd(&g_gemm_prof[12], 1ull); atomicAdd(&g_gemm_prof[13], static_cast<unsigned long long>(jw.nb * ((m_e + kGemmTok - 1) / kGemmTok))); }
-#endif
   if (warp == 0) {
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
@@ -517,18 +505,11 @@ SGR_API int sgr_moe_grouped_gemm_i8(const void* const* w_tab, const int* off, co
   auto kern = grouped_gemm_i8_kernel;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
     return kErrLaunch;
+  int* status = status_word();
+  if (status == nullptr) return kErrLaunch;       // the kernel reports an expired wait through it
   kern<<<dim3((n_rows + kGemmRows - 1) / kGemmRows, n_expert), kGemmThreads, kGemmSmem, as_stream(stream)>>>(
       reinterpret_cast<const unsigned char* const*>(w_tab), off, static_cast<const unsigned char*>(xq), y,
-      n_rows, k / kQK, status_word());
+      n_rows, k / kQK, status);
   return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
-#ifdef SGR_PROFILE
-extern "C" __attribute__((visibility("default"))) int sgr_gemm_prof_read(unsigned long long* out) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, sgr::g_gemm_prof, 32 * 8);
-  unsigned long long z[32] = {0};
-  cudaMemcpyToSymbol(sgr::g_gemm_prof, z, 32 * 8);
-  return 0;
-}
-#endif

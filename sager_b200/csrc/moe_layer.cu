@@ -33,6 +33,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -48,6 +49,7 @@ namespace {
 constexpr int kMaxRows = 64;       // token rows per call (row masks are 64-bit)
 constexpr int kTokTile = 8;        // token rows per tile of the item kernel (one MMA n-tile)
 constexpr int kMaxGrid = 192;            // most CTAs the expert kernels are launched with
+constexpr int kTmapSlots = 6;            // patched TMA descriptor sets per CTA of the row-streaming kernel
 constexpr int kRowsKernelMinRows = 4;    // layers of at least this many token rows run the row-streaming kernel
                                          // (measured: 4 rows 8 % faster, 8 rows 16 %, 2 rows slower)
 constexpr int kRouteTok = 8;       // token rows per CTA of the route kernel
@@ -75,6 +77,7 @@ struct LayerDev {
   const float* router_w;
   const float* bias;
   const unsigned char* const* tab;
+  long long tab_stride;   // pointers between the gate, up and down slices of the table (E when packed)
   const unsigned char* sh[3];
   uint16_t* x_f16;
   float* out_f32;
@@ -103,7 +106,8 @@ struct LayerDev {
   const unsigned* wait_flags;   // expert parallelism over peer memory: arrival words to wait for before planning
   const unsigned* wait_step;
   int wait_count, wait_mul, wait_add;
-  unsigned char* tmaps;   // [grid][4][3][128] row-streaming kernel: patched TMA descriptors
+  unsigned wait_limit;          // polls before a wait for arrival words gives up
+  unsigned char* tmaps;   // [grid][kTmapSlots][3][128] row-streaming kernel: patched TMA descriptors
   // TMA descriptors (placeholder address) of a gate / up matrix and of a down matrix. Only ever
   // read with constant indices: a dynamic index would make every thread keep a local-memory
   // copy of the whole argument block.
@@ -113,17 +117,8 @@ struct LayerDev {
   float* ybuf;     // [(n_max*K + n_max)][H]
   int n_max;
   int* status;
-  long long* prof;   // SGR_PROFILE builds only: [grid][8] cycle totals
 };
 
-#ifdef SGR_PROFILE
-#define PROF_T0() long long _pt = clock64()
-#define PROF_ADD(slot) do { const long long _n = clock64(); if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == _pw) \
-    atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + blockIdx.x * 16 + (slot)), static_cast<unsigned long long>(_n - _pt)); _pt = _n; } while (0)
-#else
-#define PROF_T0() do {} while (0)
-#define PROF_ADD(slot) do {} while (0)
-#endif
 
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -153,7 +148,7 @@ inline WsLayout ws_layout(int n_max, int H, int FF, int E, int K) {
   l.items_total = p;
   l.hq = take(rows * (FF / kQK) * 288);     // padded Q8_K blocks (rs::kHq)
   l.xq16 = take(static_cast<size_t>(n_max) * (H / kQK) * 288);
-  l.tmaps = take(static_cast<size_t>(kMaxGrid) * 4 * 3 * 128);
+  l.tmaps = take(static_cast<size_t>(kMaxGrid) * kTmapSlots * 3 * 128);
   l.total = p;
   return l;
 }
@@ -342,9 +337,6 @@ __device__ __forceinline__ void route_tile_logits(const LayerDev& L, float* xs, 
   }
   asm volatile("cp.async.wait_all;" ::: "memory");     // this warp's two router rows have landed
   __syncthreads();
-#ifdef SGR_TRACE
-  if (threadIdx.x == 0) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); (L.prof + 4096 + (blockIdx.y * gridDim.x + blockIdx.x) * 8)[7] = t; }
-#endif
   float out[2][NT];
   router_rows2_dot_kmajor<NT>(ws + static_cast<size_t>(2 * warp) * L.H, ws + static_cast<size_t>(2 * warp + 1) * L.H, xs,
                               L.H, lane, out);
@@ -392,15 +384,6 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
   }
   pdl_wait();
   pdl_launch_dependents();
-#ifdef SGR_PROFILE
-  const int _pw = 0;
-#endif
-  PROF_T0();
-#ifdef SGR_TRACE
-  auto gt = []() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
-  long long* rt = L.prof + 4096 + (blockIdx.y * gridDim.x + blockIdx.x) * 8;
-  if (tid == 0) rt[0] = gt();
-#endif
 
   // Q8_K rows of the tile (packed, and padded for the row-streaming kernel): block
   // b of the tile goes to warp b / gridDim.x of CTA b % gridDim.x
@@ -426,57 +409,25 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
                              : L.xq16 + static_cast<size_t>(tok0 + t) * L.xq16_stride + blk * 288);
     }
   }
-#ifdef SGR_TRACE
-  __syncthreads();
-  if (tid == 0) rt[5] = gt();      // quantised (slot reused by the plan stamp in the planning CTA only)
-#endif
   if (nt > 4) route_tile_logits<8>(L, xs, ws, tok0, nt, row0, warp, lane);
   else if (nt > 2) route_tile_logits<4>(L, xs, ws, tok0, nt, row0, warp, lane);
   else if (nt > 1) route_tile_logits<2>(L, xs, ws, tok0, nt, row0, warp, lane);
   else route_tile_logits<1>(L, xs, ws, tok0, nt, row0, warp, lane);
-#ifdef SGR_TRACE
-  if (tid == 0) rt[1] = gt();
-#endif
   // last CTA of this token tile selects (the counter's release covers the logits of all
   // warps, which the barrier ordered before it; its acquire covers the reads that follow)
   __syncthreads();
-#ifdef SGR_TRACE
-  if (tid == 0) rt[2] = gt();
-#endif
   if (tid == 0) last_sh = atom_add_acq_rel(&L.cnt[blockIdx.y], 1u) == gridDim.x - 1 ? 1 : 0;
   __syncthreads();
   if (!last_sh) return;
   if (tid == 0) L.cnt[blockIdx.y] = 0u;       // every CTA of the tile has counted in: ready for the next launch
-#ifdef SGR_TRACE
-  if (tid == 0) rt[3] = gt();
-#endif
-#ifdef SGR_PROFILE
-  if (tid == 0) atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + 11), static_cast<unsigned long long>(clock64() - _pt));
-  _pt = clock64();
-#endif
   float* prob = reinterpret_cast<float*>(smem) + static_cast<size_t>(warp % kRouteTok) * L.E;
-#ifdef SGR_TRACE
-  if (tid == 0) (L.prof + 8192 + blockIdx.y * 8)[6] = clock64();
-#endif
   for (int t = warp; t < nt; t += kRouteWarps) {
     for (int i = lane; i < L.E; i += 32) prob[i] = __ldcg(L.logits + static_cast<size_t>(tok0 + t) * L.E + i);
     __syncwarp();
-#ifdef SGR_TRACE
-    long long* stamps = warp == 0 ? L.prof + 8192 + blockIdx.y * 8 : nullptr;
-    if (warp == 0 && lane == 0) stamps[7] = clock64();
-    router_select_warp(prob, L.E, L.K, L.idx + static_cast<size_t>(tok0 + t) * L.rstride,
-                       L.w + static_cast<size_t>(tok0 + t) * L.rstride, L.shared_w, true, lane, stamps);
-    if (warp == 0 && lane == 0) stamps[5] = clock64();
-#else
     router_select_warp(prob, L.E, L.K, L.idx + static_cast<size_t>(tok0 + t) * L.rstride,
                        L.w + static_cast<size_t>(tok0 + t) * L.rstride, L.shared_w, true, lane);
-#endif
     __syncwarp();
   }
-#ifdef SGR_TRACE
-  __syncthreads();
-  if (tid == 0) rt[4] = gt();
-#endif
   if (L.skip_plan) return;
   // last token tile plans
   __syncthreads();
@@ -484,32 +435,18 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
   __syncthreads();
   if (!last_sh) return;
   if (tid == 0) L.cnt[8] = 0u;
-#ifdef SGR_PROFILE
-  if (tid == 0) atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + 12), static_cast<unsigned long long>(clock64() - _pt));
-  _pt = clock64();
-#endif
-#ifdef SGR_TRACE
-  if (tid == 0) rt[5] = gt();
-#endif
   build_plan(L, smem);
-#ifdef SGR_PROFILE
-  __syncthreads();
-  if (tid == 0) atomicAdd(reinterpret_cast<unsigned long long*>(L.prof + 13), static_cast<unsigned long long>(clock64() - _pt));
-#endif
-#ifdef SGR_TRACE
-  __syncthreads();
-  if (tid == 0) rt[6] = gt();
-#endif
 }
 
-// Bounded wait until n arrival words (written by peers over NVLink) reach `want`.
-__device__ __forceinline__ bool wait_arrivals(const unsigned* flags, int n, unsigned want, int tid) {
+// Bounded wait until n arrival words (written by peers over NVLink) reach `want`: at most
+// `limit` polls, 64 ns apart, per word (sgr_ep_set_wait_limit).
+__device__ __forceinline__ bool wait_arrivals(const unsigned* flags, int n, unsigned want, int tid, unsigned limit) {
   bool ok = true;
   if (tid < n) {
     unsigned it = 0, v;
     do {
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + tid) : "memory");
-    } while (static_cast<int>(v - want) < 0 && ++it < (1u << 22) && (__nanosleep(64), true));
+    } while (static_cast<int>(v - want) < 0 && ++it < limit && (__nanosleep(64), true));
     ok = static_cast<int>(v - want) >= 0;
   }
   return __syncthreads_and(ok ? 1 : 0) != 0;
@@ -521,9 +458,10 @@ __global__ void __launch_bounds__(256) plan_kernel(const LayerDev L) {
   pdl_wait();
   pdl_launch_dependents();
   if (L.wait_flags != nullptr &&
-      !wait_arrivals(L.wait_flags, L.wait_count, *L.wait_step * L.wait_mul + L.wait_add, threadIdx.x) &&
+      !wait_arrivals(L.wait_flags, L.wait_count, *L.wait_step * L.wait_mul + L.wait_add, threadIdx.x, L.wait_limit) &&
       threadIdx.x == 0)
-    atomicExch(L.status, 8);                  // a peer's records did not arrive: the plan below reads stale rows
+    atomicExch(L.status, 8);                  // a peer's records did not arrive: the plan below reads the rows
+                                              // of an earlier step (valid memory, wrong step)
   if (L.tok_tile != kTokTile && !L.xq_padded) pad_xq_rows(L, 0, L.n, threadIdx.x, blockDim.x);
   build_plan(L, smem);
 }
@@ -634,10 +572,6 @@ template <int NMAT, typename Emit>
 __device__ __forceinline__ void item_compute(const LayerDev& L, const unsigned char* w, int wstride,
                                              int mat_stride, const XTile& xt, float* red, int nrows,
                                              int nb, int ntok, int team, uint64_t* release, Emit emit) {
-#ifdef SGR_PROFILE
-  const int _pw = 0;
-#endif
-  PROF_T0();
   const int tw = (threadIdx.x >> 5) & (kTeamWarps - 1), lane = threadIdx.x & 31;
   const int ttid = threadIdx.x & (kTeamThreads - 1);
   const int groups = (nrows + 15) / 16;
@@ -667,9 +601,7 @@ __device__ __forceinline__ void item_compute(const LayerDev& L, const unsigned c
   }
   __syncwarp();
   if (lane == 0) mbar_arrive(release);     // this warp no longer reads the weight stage
-  PROF_ADD(8);
   team_sync(team);
-  PROF_ADD(9);
   // element q of a group: fragment slot j = q / 32 of lane q % 32
   const int per_group = units <= kTeamWarps ? nb : 0;       // warps of group g start at g * per_group
   for (int o = ttid; o < groups * 128; o += kTeamThreads) {
@@ -688,7 +620,6 @@ __device__ __forceinline__ void item_compute(const LayerDev& L, const unsigned c
       emit(r, t, v);
     }
   }
-  PROF_ADD(10);
 }
 
 // The same item for tiles of one or two token rows: dp4a, one thread per
@@ -792,10 +723,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
     // All of them walk the same item list; the first one also publishes the item
     // descriptor and arms the stage's barrier, every one issues its share of the rows.
     const int pw = warp - kConsumers / 32;
-#ifdef SGR_PROFILE
-    const int _pw = kConsumers / 32;
-#endif
-    PROF_T0();
     int cached_tile = -1;
     int4 rc = make_int4(0, 0, 0, 0);
     const unsigned char *w0 = nullptr, *w1 = nullptr, *w2 = nullptr;
@@ -810,16 +737,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
         rc = __ldcg(L.rec + tile);
         const bool shared = rc.x == L.E;
         w0 = shared ? L.sh[0] : L.tab[rc.x];
-        w1 = shared ? L.sh[1] : L.tab[L.E + rc.x];
-        w2 = shared ? L.sh[2] : L.tab[2 * L.E + rc.x];
+        w1 = shared ? L.sh[1] : L.tab[L.tab_stride + rc.x];
+        w2 = shared ? L.sh[2] : L.tab[2 * L.tab_stride + rc.x];
         cached_tile = tile;
       }
-      PROF_ADD(6);
       if (!mbar_wait(&empty[s], ph ^ 1u)) {
         if (lane == 0) atomicExch(L.status, 2);
         return;
       }
-      PROF_ADD(5);
       const bool absent = w0 == nullptr || w1 == nullptr || w2 == nullptr;
       const bool aligned = ((reinterpret_cast<uintptr_t>(w0) | reinterpret_cast<uintptr_t>(w1) |
                              reinterpret_cast<uintptr_t>(w2)) & 15u) == 0;
@@ -875,10 +800,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
   int cur_kind = -1, cur_tile = -1, pending = 0, parity = 0;
   XTile xt = xtile_at(xbase, kTokTile, L.nbh);
   bool ok = true;
-#ifdef SGR_PROFILE
-  const int _pw = 0;
-#endif
-  PROF_T0();
   // publish the gate/up chunks this team finished for its current tile
   auto publish = [&]() {
     if (cur_kind == 0 && pending > 0) {
@@ -896,7 +817,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
       ok = false;                              // the whole team sees the same expiry
       break;
     }
-    PROF_ADD(0);
     const ItemDesc d = desc[s];
     unsigned char* st = stages + static_cast<size_t>(s) * G.stage_bytes;
     if (d.kind != cur_kind || d.tile != cur_tile) {
@@ -931,20 +851,19 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
           stage_quantized_f32(xt, d.ntok, L.hbuf + static_cast<size_t>(d.hrow0) * L.FF, L.FF, tw, kTeamWarps);
       }
       team_sync(team);
-      PROF_ADD(1);
     }
     if (d.mode == 2) {                         // unaligned weights: copy them here
       if (d.kind == 0) {
         const bool shared = d.e == L.E;
         const unsigned char* w0 = shared ? L.sh[0] : L.tab[d.e];
-        const unsigned char* w1 = shared ? L.sh[1] : L.tab[L.E + d.e];
+        const unsigned char* w1 = shared ? L.sh[1] : L.tab[L.tab_stride + d.e];
         for (int r = 0; r < d.nrows; ++r) {
           copy_unaligned(st + r * G.ws_gu, w0 + (d.row0 + r) * rb_h, static_cast<int>(rb_h), ttid, kTeamThreads);
           copy_unaligned(st + G.rows_gu * G.ws_gu + r * G.ws_gu, w1 + (d.row0 + r) * rb_h,
                          static_cast<int>(rb_h), ttid, kTeamThreads);
         }
       } else {
-        const unsigned char* w2 = d.e == L.E ? L.sh[2] : L.tab[2 * L.E + d.e];
+        const unsigned char* w2 = d.e == L.E ? L.sh[2] : L.tab[2 * L.tab_stride + d.e];
         for (int r = 0; r < d.nrows; ++r)
           copy_unaligned(st + r * G.ws_dn, w2 + (d.row0 + r) * rb_f, static_cast<int>(rb_f), ttid, kTeamThreads);
       }
@@ -992,10 +911,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
                       });
     }
     if (d.kind == 0) ++pending;
-    PROF_ADD(2);
   }
   if (ok) publish();
-  PROF_ADD(3);
 
   // ---- all down rows written everywhere: blend ------------------------------------------------
   __threadfence();
@@ -1017,13 +934,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const 
     combine_rows(L, c * G.rows_dn, min(G.rows_dn, L.H - c * G.rows_dn), tg * 16, min(L.n, tg * 16 + 16), tid,
                  kConsumers);
   }
-  PROF_ADD(4);
 }
 
 // Scratch of the allocation-free entry point (sgr_moe_layer_decode_static): the
 // same layout a caller-provided workspace has, held by every device that loads
 // the library until the process exits.
-constexpr size_t kStaticWsBytes = 1u << 20;
+constexpr size_t kStaticWsBytes = 2u << 20;
 static __device__ __align__(256) unsigned char g_static_ws[kStaticWsBytes];
 constexpr int kStaticMaxDevices = 64;
 unsigned char* g_static_ws_addr[kStaticMaxDevices];     // per-device address of g_static_ws
@@ -1055,12 +971,16 @@ __global__ void ep_reduce_add_kernel(uint16_t* __restrict__ x, const float* __re
 }
 
 // ep_reduce_add_kernel after the arrival words of all parts have reached `want` (every CTA waits).
+// A CTA whose wait runs out raises status 8 and leaves its share of x as it was.
 __global__ void ep_reduce_add_wait_kernel(uint16_t* __restrict__ x, const float* __restrict__ parts,
                                           int n_parts, size_t part_stride, size_t count, const unsigned* flags,
-                                          const unsigned* step, int mul, int add, int* status) {
+                                          const unsigned* step, int mul, int add, unsigned limit, int* status) {
   pdl_wait();
   pdl_launch_dependents();
-  if (!wait_arrivals(flags, n_parts, *step * mul + add, threadIdx.x) && threadIdx.x == 0) atomicExch(status, 8);
+  if (!wait_arrivals(flags, n_parts, *step * mul + add, threadIdx.x, limit)) {
+    if (threadIdx.x == 0) atomicExch(status, 8);
+    return;
+  }
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     float acc = h2f(x[i]);
@@ -1102,9 +1022,6 @@ __global__ void ep_step_kernel(unsigned* step) {
   if (threadIdx.x == 0) *step += 1u;
 }
 
-#if defined(SGR_PROFILE) || defined(SGR_TRACE)
-long long* g_prof_buf = nullptr;
-#endif
 
 // A 2-D TMA descriptor over a Q4_K matrix seen as bytes, [rows][row_bytes], with boxes of
 // one super-block column (144 bytes) x 128 rows, encoded for a placeholder address: the
@@ -1153,6 +1070,9 @@ bool matrix_tmap(int row_bytes, int rows, const void* placeholder, uint32_t* out
   return true;
 }
 
+// Polls (64 ns apart) after which a kernel that waits for a peer's arrival words gives up.
+std::atomic<unsigned> g_wait_limit{1u << 22};
+
 template <typename Kern>
 int launch_pdl(Kern kern, dim3 grid, int threads, size_t smem, cudaStream_t stream,
                const LayerDev& L) {
@@ -1183,6 +1103,24 @@ SGR_API size_t sgr_moe_layer_workspace_bytes(int n_max, int hidden, int n_ff, in
       n_expert <= 0 || n_used <= 0)
     return 0;
   return ws_layout(n_max, hidden, n_ff, n_expert, n_used).total;
+}
+
+// Diagnostics (sager_b200_diag.h): where a region of the workspace starts, so that a test can read
+// the intermediate rows a finished call left there. which: 0 fp32 h rows, 1 fp32 y rows, 2 gslot,
+// 3 grows, 4 plan records, 5 meta.
+SGR_API long long sgr_moe_layer_workspace_offset(int n_max, int hidden, int n_ff, int n_expert, int n_used,
+                                                 int which) {
+  if (sgr_moe_layer_workspace_bytes(n_max, hidden, n_ff, n_expert, n_used) == 0) return -1;
+  const WsLayout l = ws_layout(n_max, hidden, n_ff, n_expert, n_used);
+  switch (which) {
+    case 0: return static_cast<long long>(l.hbuf);
+    case 1: return static_cast<long long>(l.ybuf);
+    case 2: return static_cast<long long>(l.gslot);
+    case 3: return static_cast<long long>(l.grows);
+    case 4: return static_cast<long long>(l.rec);
+    case 5: return static_cast<long long>(l.meta);
+    default: return -1;
+  }
 }
 
 SGR_API int sgr_moe_layer_workspace_init(void* workspace, size_t bytes, void* stream) {
@@ -1227,6 +1165,8 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   L.router_w = a->router_w;
   L.bias = a->router_bias;
   L.tab = reinterpret_cast<const unsigned char* const*>(a->w_tab);
+  L.tab_stride = a->tab_stride > 0 ? a->tab_stride : a->n_expert;
+  if (L.tab_stride < a->n_expert) return kErrArg;
   L.sh[0] = static_cast<const unsigned char*>(a->shared_gate);
   L.sh[1] = static_cast<const unsigned char*>(a->shared_up);
   L.sh[2] = static_cast<const unsigned char*>(a->shared_down);
@@ -1258,9 +1198,13 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   L.hbuf = reinterpret_cast<float*>(ws + lay.hbuf);
   L.ybuf = reinterpret_cast<float*>(ws + lay.ybuf);
   L.n_max = a->n_max;
+  // (null: the address lookup failed - a first call on this device made inside stream capture, or a
+  // device ordinal beyond the table; the kernels write through this pointer when a wait gives up)
   L.status = status_word();
+  if (L.status == nullptr) return kErrLaunch;
   L.wait_flags = a->wait_flags; L.wait_step = a->wait_step;
   L.wait_count = a->wait_count; L.wait_mul = a->wait_mul; L.wait_add = a->wait_add;
+  L.wait_limit = g_wait_limit.load(std::memory_order_relaxed);
   if (L.wait_flags != nullptr && (!a->routing_given || !L.wait_step || L.wait_count < 0 || L.wait_count > 128)) return kErrArg;
   // Which expert kernel: the row-streaming one pays once a layer has enough tiles to
   // give every SM whole groups (bit 4 of `stages` forces it, bit 5 forces the item
@@ -1298,13 +1242,6 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
       return kErrLaunch;
     L.grid = std::min(sms, kMaxGrid);
   }
-#if defined(SGR_PROFILE) || defined(SGR_TRACE)
-  if (g_prof_buf == nullptr) {
-    cudaMalloc(&g_prof_buf, (1024 * 16 + 160 * 512 + 160 * 256) * sizeof(long long));
-    cudaMemset(g_prof_buf, 0, (1024 * 16 + 160 * 512 + 160 * 256) * sizeof(long long));
-  }
-  L.prof = g_prof_buf;
-#endif
   cudaStream_t s = as_stream(stream);
 
   int rc = kOk;
@@ -1351,29 +1288,6 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   return rc;
 }
 
-#if defined(SGR_PROFILE) || defined(SGR_TRACE)
-// profiling builds: copy out (and clear) the per-CTA cycle totals [grid][8]
-// the per-stage trace of the last expert_rows_kernel launch: [grid][512] (see expert_rows.cuh)
-extern "C" __attribute__((visibility("default"))) int sgr_trace2_read(long long* host_out, int n) {
-  if (g_prof_buf == nullptr) return -1;
-  cudaDeviceSynchronize();
-  cudaMemcpy(host_out, g_prof_buf + 1024 * 16 + 160 * 512, static_cast<size_t>(n) * sizeof(long long), cudaMemcpyDeviceToHost);
-  return 0;
-}
-extern "C" __attribute__((visibility("default"))) int sgr_trace_read(long long* host_out, int n) {
-  if (g_prof_buf == nullptr) return -1;
-  cudaDeviceSynchronize();
-  cudaMemcpy(host_out, g_prof_buf + 1024 * 16, static_cast<size_t>(n) * sizeof(long long), cudaMemcpyDeviceToHost);
-  return 0;
-}
-extern "C" __attribute__((visibility("default"))) int sgr_prof_read(long long* host_out, int n) {
-  if (g_prof_buf == nullptr) return -1;
-  cudaDeviceSynchronize();
-  cudaMemcpy(host_out, g_prof_buf, static_cast<size_t>(n) * sizeof(long long), cudaMemcpyDeviceToHost);
-  cudaMemset(g_prof_buf, 0, 1024 * 16 * sizeof(long long));
-  return 0;
-}
-#endif
 
 SGR_API int sgr_moe_layer_decode(const sgr_moe_layer* a, void* stream) {
   return sgr_moe_layer_decode_stages(a, 7, stream);
@@ -1425,9 +1339,17 @@ SGR_API int sgr_ep_reduce_add_f16_wait(uint16_t* x_f16, const float* parts, int 
   if (count <= 0 || n_parts <= 0) return kOk;
   if (!x_f16 || !parts || part_stride < count || !flags || !step || n_parts > 128) return kErrArg;
   const int blocks = static_cast<int>(std::min<long long>((count + 255) / 256, 148 * 2));
+  int* status = status_word();
+  if (status == nullptr) return kErrLaunch;
   return launch_pdl_args(ep_reduce_add_wait_kernel, dim3(blocks), 256, as_stream(stream), x_f16, parts, n_parts,
                          static_cast<size_t>(part_stride), static_cast<size_t>(count), flags, step, mul, add,
-                         status_word());
+                         g_wait_limit.load(std::memory_order_relaxed), status);
+}
+
+SGR_API int sgr_ep_set_wait_limit(int polls) {
+  if (polls <= 0) return kErrArg;
+  g_wait_limit.store(static_cast<unsigned>(polls), std::memory_order_relaxed);
+  return kOk;
 }
 
 SGR_API int sgr_ep_step_advance(unsigned* step, void* stream) {
@@ -1455,9 +1377,9 @@ SGR_API int sgr_moe_layer_decode_static(const sgr_moe_layer* a, void* stream) {
       a->n_used <= 0 || a->n_max < a->n || a->n_max > kMaxRows)
     return kErrGeometry;
   const WsLayout lay = ws_layout(a->n_max, a->hidden, a->n_ff, a->n_expert, a->n_used);
-  // the shape needs more scratch than the array holds (the item kernel's regions at least; the
-  // row-streaming kernel is used when its regions fit as well)
-  if (lay.items_total > kStaticWsBytes) return kErrStaticLimit;
+  // The whole layout must fit, so that the call picks its expert kernel exactly as a call on a
+  // caller's workspace of sgr_moe_layer_workspace_bytes() does.
+  if (lay.total > kStaticWsBytes) return kErrStaticLimit;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) return kErrLaunch;
   if (g_static_ws_addr[dev] == nullptr) {
@@ -1466,7 +1388,8 @@ SGR_API int sgr_moe_layer_decode_static(const sgr_moe_layer* a, void* stream) {
     g_static_ws_addr[dev] = static_cast<unsigned char*>(p);
   }
   unsigned char* ws = g_static_ws_addr[dev];
-  // counters of the route and expert kernels: [cnt, tile_cnt) is one contiguous span
+  // what must start at zero: the counters of the route and expert kernels, [cnt, hbuf) of the layout
+  // (cnt, tile_cnt, blk_cnt, ready are adjacent)
   if (cudaMemsetAsync(ws + lay.cnt, 0, lay.hbuf - lay.cnt, as_stream(stream)) != cudaSuccess)
     return kErrLaunch;
   sgr_moe_layer b = *a;

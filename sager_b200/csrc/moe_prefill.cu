@@ -1,0 +1,77 @@
+// moe_prefill.cu - one MoE layer over a prefill chunk behind one call.
+//
+// The sequence is the one Session::moe_dispatch_device of the reference runs for a
+// chunk (src/core/session.cpp:2482-3030): quantize_q8_k -> gemv_f32_out_f16x_mtok ->
+// router_topk_batched -> moe_dispatch_scan -> gather_rows_q8_n -> gate / up ->
+// silu_mul_f16_n -> quantize_q8_k_n -> down -> scatter_routed_f16 -> shared expert
+// (gemv2 mtok, silu_mul, quantize, gemv mtok, strided copy into slot K of the combine
+// slab) -> moe_combine_batched_f16, on the caller's scratch buffers
+// (src/core/session.cpp:207-257). The routed expert projections run on the int8
+// tensor-core grouped GEMM (grouped_gemm_i8.cu) where the reference dequantises to fp16
+// and calls a library GEMM per expert (src/core/session.cpp:2643-2760); every other
+// step is the launcher the reference calls. Stream-ordered, no host synchronisation,
+// nothing allocated: legal inside stream capture.
+#include "api_util.cuh"
+#include "q4k_common.cuh"
+
+using namespace sgr;
+
+SGR_API int sgr_moe_layer_prefill(const sgr_moe_prefill* a, void* stream) {
+  if (a == nullptr) return kErrArg;
+  if (a->n <= 0) return kOk;
+  const int n = a->n, H = a->hidden, F = a->n_ff, E = a->n_expert, K = a->n_used;
+  if (H <= 0 || H % kQK || F <= 0 || F % kQK || E <= 0 || K <= 0 || K > E || a->n_max < n) return kErrGeometry;
+  if (!a->xn || !a->x_f16 || !a->w_tab || !a->xq || !a->route_idx || !a->route_w || !a->gslot || !a->grows ||
+      !a->off || !a->toff || !a->meta || !a->mail || !a->mail_n || !a->xqg || !a->g || !a->u || !a->hq ||
+      !a->y_grouped || !a->expert_y)
+    return kErrArg;
+  if (!a->logits_in && (!a->router_w || !a->logits)) return kErrArg;
+  const bool shared = a->shared_gate && a->shared_up && a->shared_down;
+  if (shared && (!a->sh_g || !a->sh_u || !a->sh_q || !a->sh_y)) return kErrArg;
+  const long long ts = a->tab_stride > 0 ? a->tab_stride : E;
+  if (ts < E) return kErrArg;
+  const int tok_per = a->tok_per > 0 ? a->tok_per : 16;
+  const void* const* tab_g = a->w_tab;
+  const void* const* tab_u = a->w_tab + ts;
+  const void* const* tab_d = a->w_tab + 2 * ts;
+  const long long R = static_cast<long long>(a->n_max) * K;
+  if (R > 0x7FFFFFFF / (F / kQK)) return kErrUnsupported;
+  int rc;
+#define SGR_STEP(call) do { rc = (call); if (rc != kOk) return rc; } while (0)
+  SGR_STEP(sgr_quantize_q8_k(a->xn, a->xq, static_cast<long long>(n) * H, stream));
+  const float* logits = a->logits_in;
+  if (logits == nullptr) {
+    SGR_STEP(sgr_gemv_f32_out_f16x_mtok(a->router_w, a->xn, a->logits, E, H, n, stream));
+    logits = a->logits;
+  }
+  SGR_STEP(sgr_router_topk_batched(logits, a->route_idx, a->route_w, E, K, K + 1, n,
+                                   shared ? a->shared_w : 0.f, stream));
+  SGR_STEP(sgr_moe_dispatch_scan(a->route_idx, a->route_w, a->gslot, a->grows, a->off, a->toff, a->meta,
+                                 a->mail, a->mail_n, n, K, E, tok_per, stream));
+  SGR_STEP(sgr_gather_rows_q8_n(a->xqg, a->xq, a->grows, a->meta, static_cast<int>(R), H / kQK, stream));
+  SGR_STEP(sgr_moe_grouped_gemm_i8(tab_g, a->off, a->xqg, a->g, F, H, E, stream));
+  SGR_STEP(sgr_moe_grouped_gemm_i8(tab_u, a->off, a->xqg, a->u, F, H, E, stream));
+  SGR_STEP(sgr_silu_mul_f16_n(a->g, a->g, a->u, a->meta, static_cast<int>(R), F, stream));
+  SGR_STEP(sgr_quantize_q8_k_n(a->g, a->hq, a->meta, F, static_cast<int>(R * (F / kQK)), stream));
+  SGR_STEP(sgr_moe_grouped_gemm_i8(tab_d, a->off, a->hq, a->y_grouped, H, F, E, stream));
+  SGR_STEP(sgr_scatter_routed_f16(a->expert_y, a->y_grouped, a->gslot, n, K, H, stream));
+  if (shared) {
+    SGR_STEP(sgr_gemv2_q4_k_q8_f16out_mtok(a->shared_gate, a->shared_up, a->xq, a->sh_g, a->sh_u, F, H, n, stream));
+    SGR_STEP(sgr_silu_mul_f16(a->sh_g, a->sh_g, a->sh_u, n, F, stream));
+    SGR_STEP(sgr_quantize_q8_k(a->sh_g, a->sh_q, static_cast<long long>(n) * F, stream));
+    SGR_STEP(sgr_gemv_q4_k_q8_f16out_mtok(a->shared_down, a->sh_q, a->sh_y, H, F, n, stream));
+    if (a->shared_gate_w != nullptr) {           // scalar gate sigmoid(w_sg . x) on the shared rows (layer.cpp:128-134)
+      if (a->sgate == nullptr) return kErrArg;
+      SGR_STEP(sgr_gemv_f32_out_f16x_batched(a->shared_gate_w, a->xn, a->sgate, 1, H, n, stream));
+      SGR_STEP(sgr_sigmoid_gate_scalar_batched_f16(a->sh_y, a->sgate, n, H, stream));
+    }
+    // slot K of every row of the combine slab (the reference's strided copy, src/core/session.cpp:2911-2916)
+    if (cudaMemcpy2DAsync(a->expert_y + static_cast<size_t>(K) * H, static_cast<size_t>(K + 1) * H * 2, a->sh_y,
+                          static_cast<size_t>(H) * 2, static_cast<size_t>(H) * 2, n, cudaMemcpyDeviceToDevice,
+                          as_stream(stream)) != cudaSuccess)
+      return kErrLaunch;
+  }
+  SGR_STEP(sgr_moe_combine_batched_f16(a->x_f16, a->expert_y, a->route_w, K, H, n, stream));
+#undef SGR_STEP
+  return kOk;
+}

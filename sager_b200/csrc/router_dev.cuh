@@ -112,13 +112,7 @@ __device__ __forceinline__ void router_rows2_dot_kmajor(const float* __restrict_
 // memory that already hold the logits; it is overwritten.
 __device__ __forceinline__ void router_select_warp(float* prob, int n_expert, int k, int* out_idx,
                                                    float* out_w, float shared_w, bool write_shared,
-                                                   int lane, long long* stamps = nullptr) {
-#ifdef SGR_TRACE
-#define SEL_STAMP(i) do { if (stamps != nullptr && lane == 0) stamps[i] = clock64(); } while (0)
-#else
-#define SEL_STAMP(i) do {} while (0)
-#endif
-  SEL_STAMP(0);
+                                                   int lane) {
   if (n_expert <= 256 && k <= 32) {
     // Up to 256 experts: a lane keeps its eight values (experts lane, lane + 32, ...) in
     // registers from the logits to the picks. Same arithmetic as the general path below.
@@ -140,7 +134,6 @@ __device__ __forceinline__ void router_select_warp(float* prob, int n_expert, in
       if (lane + 32 * j < n_expert) prob[lane + 32 * j] = pr[j];
     }
     __syncwarp();
-    SEL_STAMP(1);
     float z = 0.f;
     if (lane == 0) {                             // strictly in index order, loads ahead of the adds
       int i = 0;
@@ -152,13 +145,11 @@ __device__ __forceinline__ void router_select_warp(float* prob, int n_expert, in
       for (; i < n_expert; ++i) z += prob[i];
     }
     z = __shfl_sync(0xFFFFFFFFu, z, 0);
-    SEL_STAMP(2);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float p = pr[j] / z;
       pr[j] = (lane + 32 * j < n_expert && p == p) ? p : -1.f;     // absent or NaN: never picked
     }
-    SEL_STAMP(3);
     float wsum = 0.f, my_w = 0.f;
     int my_i = 0;
     for (int kk = 0; kk < k; ++kk) {
@@ -181,7 +172,6 @@ __device__ __forceinline__ void router_select_warp(float* prob, int n_expert, in
       wsum += best;
       if (lane == kk) { my_w = best; my_i = bi; }
     }
-    SEL_STAMP(4);
     if (lane < k) {
       out_idx[lane] = my_i;
       out_w[lane] = wsum > 0.f ? my_w / wsum : my_w;
@@ -195,7 +185,6 @@ __device__ __forceinline__ void router_select_warp(float* prob, int n_expert, in
   for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
   for (int i = lane; i < n_expert; i += 32) prob[i] = expf(prob[i] - mx);
   __syncwarp();
-  SEL_STAMP(1);
   float z = 0.f;
   if (lane == 0) {
     int i = 0;
@@ -209,10 +198,8 @@ __device__ __forceinline__ void router_select_warp(float* prob, int n_expert, in
     for (; i < n_expert; ++i) z += prob[i];
   }
   z = __shfl_sync(0xFFFFFFFFu, z, 0);
-  SEL_STAMP(2);
   for (int i = lane; i < n_expert; i += 32) prob[i] = prob[i] / z;
   __syncwarp();
-  SEL_STAMP(3);
 
   // Every lane learns each pick (butterfly reduction); lane kk keeps pick kk in
   // registers, so the results reach global memory once, in parallel, already
@@ -267,7 +254,6 @@ __device__ __forceinline__ void router_select_warp(float* prob, int n_expert, in
     }
     __syncwarp();
   }
-  SEL_STAMP(4);
   if (k <= 32) {
     if (lane < k) {
       out_idx[lane] = my_i;

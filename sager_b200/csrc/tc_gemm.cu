@@ -348,12 +348,9 @@ int launch_tc_gemm(const void* w16, const void* x16, void* y, int n_rows, int k,
   if (!operand_map(&mw, w16, n_rows, k, layout, kBM) || !operand_map(&mx, x16, n_tokens, k, layout, bn))
     return kErrUnsupported;
   auto kern = tc_gemm_kernel<F32OUT>;
-  static std::atomic<bool> attr_set{false};
-  if (!attr_set.load(std::memory_order_acquire)) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess)
-      return kErrLaunch;
-    attr_set.store(true, std::memory_order_release);
-  }
+  // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess)
+    return kErrLaunch;
   TcArgs a{y, n_rows, k, n_tokens, layout, bn, status_word()};
   kern<<<dim3(row_tiles, (n_tokens + bn - 1) / bn), kTcThreads, kTcSmem, s>>>(mw, mx, a);
   return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;

@@ -35,13 +35,60 @@ def record_layout(hidden: int, k: int, padded: bool = False):
     return rec, idx_off, w_off
 
 
+class ExchangeTimeout(RuntimeError):
+    """A peer did not take part in an exchange within the time limit. The process group has
+    been aborted (its communicators are gone): the caller re-forms the group or stops."""
+
+
+def abort_group(group=None):
+    """Tear an NCCL group's communicators down without waiting for the peers (ncclCommAbort): no
+    collective of this rank stays enqueued behind the one that will never complete. After it the
+    group is unusable. gloo has no such call - its shutdown would itself wait for the pending
+    operation - so a gloo group is left as it is and the caller just stops using it."""
+    try:
+        if dist.get_backend(group) != "nccl":
+            return
+        fn = getattr(dist.distributed_c10d, "_abort_process_group", None)
+        if fn is not None:
+            fn(group)
+        else:
+            dist.destroy_process_group(group)
+    except Exception:                        # already gone, or nothing to abort
+        pass
+
+
+def guarded_wait(work, timeout_s, what, group=None):
+    """Host-side bounded wait for one asynchronous collective. On expiry - or when the backend
+    reports an asynchronous error (a peer died: ncclCommGetAsyncError through the watchdog) -
+    the group is aborted and ExchangeTimeout raised, so a rank that never posts becomes an
+    error on the other ranks and not a hang."""
+    import time
+    deadline = time.monotonic() + timeout_s
+    try:
+        while not work.is_completed():        # non-blocking: an event query (NCCL) / a flag (gloo)
+            if time.monotonic() > deadline:
+                abort_group(group)
+                raise ExchangeTimeout(f"{what}: no completion within {timeout_s} s")
+            time.sleep(0.0005)
+        work.wait()                           # completed: surfaces an error the backend recorded
+    except ExchangeTimeout:
+        raise
+    except RuntimeError as exc:
+        abort_group(group)
+        raise ExchangeTimeout(f"{what}: {str(exc).splitlines()[0][:200]}") from exc
+
+
 class EpExchange:
     """The two fixed-capacity all-to-alls of a layer, on whatever device the buffers
-    live (NCCL on GPUs; gloo on CPU in the host-logic tests)."""
+    live (NCCL on GPUs; gloo on CPU in the host-logic tests). With timeout_s the
+    collectives are issued asynchronously and waited for on the host with that limit
+    (eager steps only: inside a captured graph there is no host wait, and the limit
+    that applies is the process group's own, enforced by its watchdog)."""
 
-    def __init__(self, world, rank, n_home, hidden, k, device, padded=False):
+    def __init__(self, world, rank, n_home, hidden, k, device, padded=False, timeout_s=None):
         self.world, self.rank, self.n_home, self.hidden, self.k = world, rank, n_home, hidden, k
         self.padded = padded
+        self.timeout_s = timeout_s
         self.rec, self.idx_off, self.w_off = record_layout(hidden, k, padded)
         self.send = torch.zeros(world, n_home, self.rec, dtype=torch.uint8, device=device)
         self.recv = torch.zeros(world, n_home, self.rec, dtype=torch.uint8, device=device)
@@ -52,12 +99,19 @@ class EpExchange:
         """send[0] holds this rank's home records; afterwards recv[p] holds rank p's."""
         if self.world > 1:
             self.send[1:] = self.send[0]
-        dist.all_to_all_single(self.recv.view(-1), self.send.view(-1))
+        self._all_to_all(self.recv, self.send, "dispatch all-to-all")
 
     def combine(self):
         """part[p] holds this rank's partial sums for rank p's home rows; afterwards
         back[p] holds rank p's partial sums for this rank's home rows."""
-        dist.all_to_all_single(self.back.view(-1), self.part.view(-1))
+        self._all_to_all(self.back, self.part, "return all-to-all")
+
+    def _all_to_all(self, dst, src, what):
+        if self.timeout_s is None:
+            dist.all_to_all_single(dst.view(-1), src.view(-1))
+            return
+        work = dist.all_to_all_single(dst.view(-1), src.view(-1), async_op=True)
+        guarded_wait(work, self.timeout_s, f"rank {self.rank}: {what}")
 
 
 class PeerExchange:
@@ -281,24 +335,34 @@ def run_ep_bench(args, rank, world, device):
 
     for _ in range(args.warmup):
         step()
+    # parity inside the line: a step of a sub-stack (the first 2 layers; with --check the whole
+    # stack that --layers gives) against the single-GPU fused layers on rank 0
+    n_chk = layers_n if getattr(args, "check", False) else min(2, layers_n)
+    if n_chk == layers_n:
+        chk = st
+    else:
+        chk = EpStack(ws[:n_chk], tokens, K, device, rank, world, biases[:n_chk], inputs[:n_chk], x0)
+        chk.capture()
+    chk.x.copy_(chk.x0)
+    chk.replay()
+    torch.cuda.synchronize()
+    parts = [torch.empty_like(chk.x) for _ in range(world)]
+    dist.all_gather(parts, chk.x)
     check = None
-    if getattr(args, "check", False):
-        # every rank's home rows after one step, against the single-GPU fused layer on rank 0
-        step()
+    if rank == 0:
+        from .layer import MoeStack
+        full = [synth.MoeWeights(H, FF, E, device, seed=bench.SEED + li) for li in range(n_chk)]
+        ref = MoeStack(full, tokens, K, device, biases=biases[:n_chk], inputs=inputs[:n_chk])
+        ref.x.copy_(x0)
+        ref.step_eager(tokens)
         torch.cuda.synchronize()
-        parts = [torch.empty_like(st.x) for _ in range(world)]
-        dist.all_gather(parts, st.x)
-        if rank == 0:
-            from .layer import MoeStack
-            full = [synth.MoeWeights(H, FF, E, device, seed=bench.SEED + li) for li in range(layers_n)]
-            ref = MoeStack(full, tokens, K, device, biases=biases, inputs=inputs)
-            ref.x.copy_(x0)
-            ref.step_eager(tokens)
-            torch.cuda.synchronize()
-            got = torch.cat(parts).float()
-            want = ref.x.float()
-            check = float((got - want).abs().max() / want.abs().max())
-            del full, ref
+        got = torch.cat(parts).float()
+        want = ref.x.float()
+        check = float((got - want).abs().max() / want.abs().max())
+        del full, ref
+    if chk is not st:
+        del chk
+    nvlink = nvlink_bytes(ws, inputs, biases, tokens, world, K, H, st)
     sampler = bench.ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
     sampler.start()
     ms_step = timed(step, args.steps)
@@ -344,4 +408,33 @@ def run_ep_bench(args, rank, world, device):
         line["device_status"] = "a bounded device-side wait gave up"
     if check is not None:
         line["check_max_rel_err_vs_single_gpu"] = check
+        line["check_layers"] = n_chk
+    line["nvlink_bytes_per_layer"] = nvlink
     return line
+
+
+def nvlink_bytes(ws, inputs, biases, tokens, world, k, hidden, st):
+    """Bytes that cross NVLink per layer, whole job (mean over the layers), counted from the
+    routing: algorithmic = one Q8_K row (hidden/256 * 276 B) per (token, owner rank other than its
+    home that holds at least one of its top-k) and one fp32 row back per such pair; moved = what
+    the exchange kernels store into other ranks' memory (every record to every other rank, every
+    rank's partial rows back)."""
+    n_exp = ws[0].n_expert
+    per = n_exp // world
+    n_home = tokens // world
+    pairs = []
+    for li in range(len(ws)):
+        lg = inputs[li].float() @ ws[li].router.t()
+        if biases is not None:
+            lg = lg + biases[li]
+        owner = lg.topk(k, dim=1).indices // per                       # [tokens][k] owner rank of each pick
+        home = torch.arange(tokens, device=lg.device) // n_home
+        hit = torch.zeros(tokens, world, dtype=torch.bool, device=lg.device)
+        hit.scatter_(1, owner, True)
+        hit[torch.arange(tokens), home] = False
+        pairs.append(int(hit.sum().item()))
+    p = float(np.mean(pairs))
+    rec = st.peer.rec if st.peer is not None else st.ex.rec
+    return {"dispatch_algorithmic": p * (hidden // 256 * Q8K_BYTES), "return_algorithmic": p * hidden * 4,
+            "dispatch_moved": float(tokens * (world - 1) * rec), "return_moved": float(tokens * (world - 1) * hidden * 4),
+            "remote_token_owner_pairs": p}

@@ -13,7 +13,7 @@ import ctypes as C
 
 import torch
 
-from .capi import MoeLayerArgs, lib
+from .capi import MoeLayerArgs, MoePrefillArgs, lib
 from .ops import stream_ptr
 
 
@@ -186,33 +186,38 @@ class PrefillLayer:
         self.sh_q = torch.empty(n_max, n_ff // 256 * 276, dtype=u8, device=d)
         self.sh_y = torch.empty(n_max, hidden, dtype=f16, device=d)
 
+    def args(self, n, xn, x, weights, table, logits=None, shared=True):
+        """The argument block of sgr_moe_layer_prefill over this object's buffers; `table` is
+        the [3][E] pointer table (any slice stride: a [3][Lm][E] table is passed as the layer's
+        slice of matrix 0 with tab_stride = Lm * E)."""
+        a = MoePrefillArgs()
+        a.n, a.n_max = n, self.n_max
+        a.hidden, a.n_ff, a.n_expert, a.n_used = self.H, self.F, self.E, self.K
+        a.tok_per, a.shared_w = self.TOK_PER, 1.0
+        a.xn, a.router_w, a.logits_in = _p(xn), _p(weights.router), _p(logits)
+        a.w_tab, a.tab_stride = _p(table), table.stride(0) if table.dim() == 2 else 0
+        if shared:
+            a.shared_gate, a.shared_up, a.shared_down = weights.shared_ptrs()
+        a.x_f16, a.xq, a.logits = _p(x), _p(self.xq), _p(self.logits)
+        a.route_idx, a.route_w, a.gslot, a.grows = _p(self.idx), _p(self.w), _p(self.gslot), _p(self.grows)
+        a.off, a.toff, a.meta, a.mail, a.mail_n = _p(self.off), _p(self.toff), _p(self.meta), _p(self.mail), _p(self.mail_n)
+        a.xqg, a.g, a.u, a.hq, a.y_grouped = _p(self.xqg), _p(self.g), _p(self.u), _p(self.hq), _p(self.yg)
+        a.expert_y = _p(self.expert_y)
+        a.sh_g, a.sh_u, a.sh_q, a.sh_y = _p(self.sh_g), _p(self.sh_u), _p(self.sh_q), _p(self.sh_y)
+        return a
+
     def run(self, n, xn, x, weights, table, logits=None, shared=True, experts_only=False):
-        """x [n][H] fp16 residual, combined in place. `logits` replaces the router GEMV
-        (the prefill benchmark draws them directly). experts_only stops after the three
-        grouped GEMMs (timing)."""
+        """x [n][H] fp16 residual, combined in place: one call of sgr_moe_layer_prefill.
+        `logits` replaces the router GEMV (the prefill benchmark draws them directly).
+        experts_only re-issues the routed expert stage alone (gate, up, SwiGLU, requantise,
+        down) on the plan a full call left behind (timing)."""
         o, H, F, E, K = self.ops, self.H, self.F, self.E, self.K
         if not experts_only:
-            o.quantize_q8_k(xn, self.xq, n * H)
-            if logits is None:
-                o.gemv_f32_out_f16x_mtok(weights.router, xn, self.logits, E, H, n)
-                logits = self.logits
-            o.router_topk_batched(logits, self.idx, self.w, E, K, K + 1, n, 1.0 if shared else 0.0)
-            o.moe_dispatch_scan(self.idx, self.w, self.gslot, self.grows, self.off, self.toff, self.meta,
-                                self.mail, self.mail_n, n, K, E, self.TOK_PER)
-            o.gather_rows_q8_n(self.xqg, self.xq, self.grows, self.meta, n * K, H // 256)
+            a = self.args(n, xn, x, weights, table, logits=logits, shared=shared)
+            lib().call("sgr_moe_layer_prefill", C.byref(a), stream_ptr())
+            return
         o.moe_grouped_gemm_i8(table[0], self.off, self.xqg, self.g, F, H, E)
         o.moe_grouped_gemm_i8(table[1], self.off, self.xqg, self.u, F, H, E)
         o.silu_mul_f16_n(self.g, self.g, self.u, self.meta, n * K, F)
         o.quantize_q8_k_n(self.g, self.hq, self.meta, F, n * K * (F // 256))
         o.moe_grouped_gemm_i8(table[2], self.off, self.hq, self.yg, H, F, E)
-        if experts_only:
-            return
-        o.scatter_routed_f16(self.expert_y, self.yg, self.gslot, n, K, H)
-        if shared:
-            sg, su, sd = weights.shared_ptrs()
-            o.gemv2_q4_k_q8_f16out_mtok(sg, su, self.xq, self.sh_g, self.sh_u, F, H, n)
-            o.silu_mul_f16(self.sh_g, self.sh_g, self.sh_u, n, F)
-            o.quantize_q8_k(self.sh_g, self.sh_q, n * F)
-            o.gemv_q4_k_q8_f16out_mtok(sd, self.sh_q, self.sh_y, H, F, n)
-            self.expert_y[:n, K, :].copy_(self.sh_y[:n])
-        o.moe_combine_batched_f16(x, self.expert_y, self.w, K, H, n)

@@ -14,7 +14,7 @@ def test_library_builds_and_exports_header_symbols():
     assert os.path.exists(path)
     lib = capi.Lib(path)            # raises if a declared symbol is missing
     assert len(lib.protos) >= 39
-    assert lib.raw("sgr_abi_version")() == 1
+    assert lib.raw("sgr_abi_version")() == 2
     out = subprocess.run(["nm", "-D", "--defined-only", path], capture_output=True, text=True).stdout
     exported = {ln.split()[-1] for ln in out.splitlines() if " T " in ln}
     assert set(lib.protos) <= exported
@@ -53,15 +53,21 @@ def test_shim_defines_exactly_the_reference_launchers(tmp_path):
     shim claims to provide; it links only if the shim defines those exact
     signatures. Needs the reference tree and the CUDA headers."""
     import pytest
-    ref_inc = "/root/reference/include"
-    cuda_inc = "/usr/local/cuda/include"
+    from oracle.oracle import reference_root
+    import shutil
+    ref_inc = os.path.join(reference_root(), "include")
+    nvcc = shutil.which("nvcc")
+    cuda_home = os.environ.get("CUDA_HOME") or (os.path.dirname(os.path.dirname(os.path.realpath(nvcc))) if nvcc else "")
+    cuda_inc = os.path.join(cuda_home, "include")
     if not (os.path.isdir(ref_inc) and os.path.isdir(cuda_inc)):
         pytest.skip("reference tree or CUDA headers not present")
     import re
     shim = open(os.path.join(ROOT, "include", "sager_b200_shim.hpp")).read()
     body = shim.split("int b200_last_error();", 1)[1].split("#ifdef SAGER_B200_SHIM_IMPLEMENTATION", 1)[0]
-    names = re.findall(r"^void (\w+)\(", body, flags=re.M)
-    assert len(names) >= 36
+    # every launcher the shim declares, whatever it returns (void, bool, void*, size_t)
+    names = re.findall(r"^(?:void|bool|void\*|size_t) (\w+)\(", body, flags=re.M)
+    assert len(names) >= 41 and {"tc_gemm_q4_k_f16", "tc_handle", "tc_scratch_elems", "tc_gemm_f16_raw",
+                                 "tc_gemm_f16_f32out_raw"} <= set(names)
     user = tmp_path / "user.cpp"
     user.write_text('#include "sager/kernels/cuda_ops.hpp"\n'
                     "const void* volatile sink[] = {\n" +

@@ -84,3 +84,39 @@ def test_two_rank_exchange_reproduces_single_rank_layer(tmp_path, oracle, golden
     ex_w = (golden["ffn_wg"], golden["ffn_wu"], golden["ffn_wd"])
     want = oracle.moe_layer(x16, router, [ex_w] * E, ex_w, x16.astype(np.float32), K, F)["out"]
     assert np.abs(got - want).max() / np.abs(want).max() < 1e-6
+
+
+def _silent_peer_worker(rank, world, port, out_dir):
+    """Rank 1 joins the group and then never posts its side of the dispatch; rank 0 must get an
+    error within its time limit instead of waiting for ever."""
+    import time
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from sager_b200.ep import EpExchange, ExchangeTimeout
+    ex = EpExchange(world, rank, 2, 512, 2, "cpu", timeout_s=2.0)
+    dist.barrier()
+    if rank == 1:
+        time.sleep(8.0)                       # alive, but takes no part in the exchange
+        os._exit(0)
+    t0 = time.time()
+    try:
+        ex.dispatch()
+        result = "completed"
+    except ExchangeTimeout as exc:
+        result = f"timeout after {time.time() - t0:.1f} s: {exc}"
+    with open(os.path.join(out_dir, "rank0.txt"), "w") as f:
+        f.write(result)
+    os._exit(0)                               # the group is aborted: no orderly shutdown to wait for
+
+
+def test_a_rank_that_never_posts_becomes_an_error_not_a_hang(tmp_path):
+    world = 2
+    ctx = mp.spawn(_silent_peer_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=False)
+    import time
+    deadline = time.time() + 60
+    while not ctx.join(timeout=1.0):
+        assert time.time() < deadline, "the ranks are still running: the wait was not bounded"
+    text = (tmp_path / "rank0.txt").read_text()
+    assert text.startswith("timeout after"), text
+    assert float(text.split()[2]) < 6.0

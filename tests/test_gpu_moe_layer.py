@@ -15,9 +15,16 @@ from tests.util import DEV, LAYER_TOL, dev, f16_close, rel
 pytestmark = pytest.mark.gpu
 
 
-def oracle_layer(oracle, w, x16_np, resid_np, k, absent=(), bias=None, n_threads=8, use_shared=True):
-    """Run the oracle on the experts the routing needs only (the rest stay None)."""
+def oracle_layer(oracle, w, x16_np, resid_np, k, absent=(), bias=None, n_threads=8, use_shared=True,
+                 blob_np=None):
+    """Run the oracle on the experts the routing needs only (the rest stay None). blob_np: a host
+    copy of w.blob to slice the matrices from (saves one device copy per matrix)."""
     E = w.n_expert
+    if blob_np is not None:
+        o3 = [0, w.gu_bytes, 2 * w.gu_bytes, w.expert_bytes]
+        mat = lambda e, m: blob_np[w.slot(e), o3[m]:o3[m + 1]]
+    else:
+        mat = lambda e, m: w.matrix(e, m).cpu().numpy()
     logits = np.stack([oracle.router_logits(w.router.cpu().numpy(), x16_np[t]) for t in range(x16_np.shape[0])])
     if bias is not None:
         logits = logits + bias[None, :]
@@ -28,8 +35,8 @@ def oracle_layer(oracle, w, x16_np, resid_np, k, absent=(), bias=None, n_threads
     for e in need:
         if e in absent:
             continue
-        experts[e] = tuple(w.matrix(e, m).cpu().numpy() for m in range(3))
-    shared = tuple(w.matrix(E, m).cpu().numpy() for m in range(3)) if use_shared else None
+        experts[e] = tuple(mat(e, m) for m in range(3))
+    shared = tuple(mat(E, m) for m in range(3)) if use_shared else None
     router = w.router.cpu().numpy()
     if bias is not None:
         # the oracle computes logits itself: fold the bias in by routing on biased logits
@@ -321,3 +328,103 @@ def test_peer_memory_entry_points_with_one_rank():
     torch.cuda.synchronize()
     assert torch.all(x == 2.0) and int(step.item()) == 4
     assert lib().raw("sgr_status")(0) == 0
+
+
+# ---- seed sweep at the benchmark geometry ---------------------------------------------------------
+def _h_code_flips(oracle, w, blob_np, runner, x16_np, idx_row, t, k):
+    """For token row t of a finished call: the Q8_K codes of h (the SwiGLU output that is
+    requantised between the projections) as the device's fp32 h rows give them, against the codes
+    the CPU path's h gives. -> (codes compared, codes that differ)."""
+    H, F, E, n_max = w.hidden, w.n_ff, w.n_expert, runner.n_max
+    off = lambda which: lib().raw("sgr_moe_layer_workspace_offset")(n_max, H, F, E, k, which)
+    rows = n_max * k + n_max
+    ws = runner.ws
+    hbuf = ws[off(0):off(0) + rows * F * 4].view(torch.float32).view(rows, F)
+    gslot = ws[off(2):off(2) + n_max * k * 4].view(torch.int32).cpu().numpy()
+    o3 = [0, w.gu_bytes, 2 * w.gu_bytes]
+    xq = oracle.quantize_q8k(x16_np[t].astype(np.float32)[None])[0]
+    total = flips = 0
+    for kk in range(k + 1):
+        e = int(idx_row[kk]) if kk < k else E
+        row = int(gslot[t * k + kk]) if kk < k else n_max * k + t
+        g = oracle.gemv(blob_np[w.slot(e), o3[0]:o3[1]], xq, F, H)
+        u = oracle.gemv(blob_np[w.slot(e), o3[1]:o3[2]], xq, F, H)
+        h_cpu = (g / (np.float32(1) + np.exp(-g, dtype=np.float32)) * u).astype(np.float32)
+        h_dev = hbuf[row].cpu().numpy()
+        qa = oracle.quantize_q8k(h_cpu[None])[0].reshape(-1, 276)[:, 4:260]
+        qb = oracle.quantize_q8k(h_dev[None])[0].reshape(-1, 276)[:, 4:260]
+        total += qa.size
+        flips += int((qa != qb).sum())
+    return total, flips
+
+
+@pytest.mark.parametrize("kernel", ["items", "rows"])
+def test_benchmark_geometry_seed_sweep(oracle, kernel):
+    """32 seeded cases (4 weight sets x 8 input sets) x 1, 4 and 64 token rows, none of them picked:
+    every case must meet the stated bound of 1e-3 against the CPU expert path, and the distribution
+    is printed. Where a case is far from the typical 1e-7, the cause is counted, not assumed: h is
+    requantised to Q8_K between the projections, and a value that sits on a rounding boundary can
+    take another code on the device (other fp32 summation order, expf) than on the CPU."""
+    k = 8
+    errs = {1: [], 4: [], 64: []}
+    worst = (0.0, None)
+    for wi, wseed in enumerate((20260718, 11, 12, 13)):
+        w = synth.MoeWeights(2048, 512, 256, DEV, seed=wseed)
+        blob_np = w.blob.cpu().numpy()
+        for xi in range(8):
+            for n in (1, 4, 64):
+                seed = 5000 + 100 * wi + 10 * xi + n
+                bias = synth.zipf_bias(256, seed=seed, alpha=0.6) if n == 64 else None
+                x16 = synth.normal_fp16((n, w.hidden), seed, DEV)
+                x_np = x16.cpu().numpy()
+                runner, _, out32 = run_layer(w, n, k, x16, n_max=64, bias=bias, kernel=kernel)
+                want = oracle_layer(oracle, w, x_np, x_np.astype(np.float32), k, bias=bias, blob_np=blob_np,
+                                    n_threads=16)
+                idx = runner.route_idx.cpu().numpy()[:n]
+                assert np.array_equal(idx[:, :k], want["idx"][:, :k]), (wseed, xi, n)
+                got = out32.cpu().numpy()
+                err = rel(got, want["out"])
+                errs[n].append(err)
+                if err > worst[0]:
+                    t = int(np.abs(got - want["out"]).max(axis=1).argmax())
+                    worst = (err, (wseed, xi, n, t) + _h_code_flips(oracle, w, blob_np, runner, x_np, idx[t], t, k))
+        del w
+    for n, v in errs.items():
+        print(f"{kernel} kernel, {n:2d} rows: {len(v)} cases, max relative error median {np.median(v):.2e}, "
+              f"max {np.max(v):.2e}")
+    wseed, xi, n, t, total, flips = worst[1]
+    print(f"worst case (weights {wseed}, inputs {xi}, {n} rows, row {t}): {worst[0]:.2e}; "
+          f"{flips} of {total} Q8_K codes of h differ from the CPU path's")
+    assert max(max(v) for v in errs.values()) <= LAYER_TOL
+
+
+def test_strided_pointer_table_is_used_in_place(small_w):
+    """The reference's decode table is [3][Lm][E] (src/core/session.cpp:3596-3598): a layer's
+    gate / up / down slices are Lm * E pointers apart. tab_stride takes them where they are."""
+    n, k, Lm, li = 9, 4, 3, 2
+    E = small_w.n_expert
+    x16 = synth.normal_fp16((n, small_w.hidden), 431, DEV)
+    for kernel in ("items", "rows"):
+        _, _, want = run_layer(small_w, n, k, x16, n_max=16, kernel=kernel)
+        big = torch.zeros(3, Lm, E, dtype=torch.int64, device=DEV)
+        big[:, li, :] = small_w.table()
+        runner = MoeLayerRunner(16, small_w.hidden, small_w.n_ff, E, k, DEV)
+        out32 = torch.zeros(n, small_w.hidden, dtype=torch.float32, device=DEV)
+        a = runner.args(n, x16, small_w.router, big[0, li], small_w.shared_ptrs(), x_f16=x16.clone(), out_f32=out32)
+        a.tab_stride = Lm * E
+        runner.run(a, kernel=kernel)
+        torch.cuda.synchronize()
+        assert torch.equal(out32, want)
+    assert lib().raw("sgr_status")(0) == 0
+
+
+@pytest.mark.parametrize("hidden,n_ff", [(256, 2048), (2048, 256)])
+def test_rows_kernel_with_one_block_column_per_group(oracle, hidden, n_ff):
+    """hidden == 256 (gate / up groups) or n_ff == 256 (down groups) makes a group a single stage, so
+    a CTA that draws several groups changes tile with every stage: more tiles than descriptor
+    slots pass through a CTA while earlier copies are still in flight. 64 rows x top-8 over 64
+    experts are about 70 tiles and several hundred single-stage groups, a handful per CTA."""
+    E, k, n = 64, 8, 64
+    w = synth.MoeWeights(hidden, n_ff, E, DEV, seed=77, std=0.05)
+    for seed in (1, 2):
+        check(oracle, w, n, k, seed=900 + seed, n_max=64, kernel="rows", tol=1e-3)

@@ -9,6 +9,7 @@ import torch
 from oracle import ref_cuda
 from sager_b200 import synth
 from sager_b200.layer import MoeLayerRunner
+from tests.test_gpu_moe_layer import oracle_layer
 from tests.util import DEV, f16_ulp_diff, make_q4k, make_x16, rel
 
 pytestmark = [pytest.mark.gpu,
@@ -66,30 +67,55 @@ def test_dense_gemv_family_matches_the_reference_kernels(both):
 
 
 @pytest.mark.parametrize("n,hidden,n_ff,E,K", [(64, 2048, 512, 256, 8), (9, 512, 256, 16, 4)])
-def test_device_moe_path_and_fused_layer_against_the_reference_sequence(both, n, hidden, n_ff, E, K):
+def test_device_moe_path_and_fused_layer_against_the_reference_sequence(both, oracle, n, hidden, n_ff, E, K):
+    """The reference's device MoE sequence on its own kernels against (a) the same sequence on this
+    library's launchers and (b) the fused layer. Measured on the MoE half's own output (zero
+    residual), where nothing masks a difference, and on top of a residual stream, the layer output
+    as the session sees it. Both are held to the stated 1e-3 of the largest output."""
     ref, mine = both
     w = synth.MoeWeights(hidden, n_ff, E, DEV, seed=5, std=0.02 if hidden == 2048 else 0.05)
     xn = synth.normal_fp16((n, hidden), 6, DEV)
-    resid = synth.normal_fp16((n, hidden), 7, DEV)
     table, shared = w.table(), w.shared_ptrs()
+    zero = torch.zeros(n, hidden, dtype=torch.float16, device=DEV)
+    resid = synth.normal_fp16((n, hidden), 7, DEV)
     res = {}
     for name, o in (("ref", ref), ("mine", mine)):
         path = ref_cuda.DeviceMoePath(o, n, hidden, n_ff, E, K, DEV)
-        x = resid.clone()
+        y, x = zero.clone(), resid.clone()
+        path.run(n, xn, y, w.router, table, shared)
         path.run(n, xn, x, w.router, table, shared)
         torch.cuda.synchronize()
-        res[name] = (x.cpu().numpy(), path.idx.cpu().numpy(), path.off.cpu().numpy(), path.meta.cpu().numpy())
+        res[name] = (y.cpu().numpy(), path.idx.cpu().numpy(), path.off.cpu().numpy(), path.meta.cpu().numpy(),
+                     x.cpu().numpy())
     assert np.array_equal(res["ref"][1][:, :K], res["mine"][1][:, :K])
     assert np.array_equal(res["ref"][2], res["mine"][2])                       # expert-major plan
     assert np.array_equal(res["ref"][3][:2], res["mine"][3][:2])
-    # launch for launch the same arithmetic up to fp32 summation order inside a GEMV:
+    # (a) launch for launch the same arithmetic up to the fp32 summation order inside a GEMV;
     # g, u, y pass through fp16 and h through Q8, so single elements may move by an fp16 step
     want = res["ref"][0].astype(np.float32)
-    assert rel(res["mine"][0].astype(np.float32), want) < 2e-3
-    # the fused layer (fp32 intermediates) against the reference's fp16-staged sequence
+    err_seq = rel(res["mine"][0].astype(np.float32), want)
+    err_seq_x = rel(res["mine"][4].astype(np.float32), res["ref"][4].astype(np.float32))
+    print(f"n={n} H={hidden}: the reference's device sequence on this library's launchers vs on the reference's own "
+          f"kernels: MoE output {err_seq:.2e}, with a residual stream {err_seq_x:.2e}")
+    assert max(err_seq, err_seq_x) <= 1e-3, (err_seq, err_seq_x)
+    # (b) The fused layer keeps g, u, h, y in fp32, as the reference's CPU path does
+    # (src/kernels/cpu/q4_avx2.cpp:175-196), where the reference's device sequence rounds each of
+    # them to fp16. The reference's two implementations are themselves a few 1e-3 apart for that
+    # reason (h is requantised to Q8_K from differently rounded values), so no single result can be
+    # within 1e-3 of both. The fused layer is held to the CPU path (the stated 1e-3; 1e-7 typical), and
+    # must be no further from the reference's CUDA path than the reference's own CPU path is.
     runner = MoeLayerRunner(n, hidden, n_ff, E, K, DEV)
-    x = resid.clone()
-    runner.run(runner.args(n, xn, w.router, table, shared, x_f16=x))
+    y = zero.clone()
+    out32 = torch.zeros(n, hidden, dtype=torch.float32, device=DEV)
+    runner.run(runner.args(n, xn, w.router, table, shared, x_f16=y, out_f32=out32))
     torch.cuda.synchronize()
     assert np.array_equal(runner.route_idx.cpu().numpy()[:n, :K], res["ref"][1][:, :K])
-    assert rel(x.cpu().numpy().astype(np.float32), want) < 4e-3
+    x_np = xn.cpu().numpy()
+    cpu = oracle_layer(oracle, w, x_np, np.zeros((n, hidden), dtype=np.float32), K, n_threads=16)["out"]
+    d_fused_cpu = rel(out32.cpu().numpy(), cpu)
+    d_fused_cuda = rel(y.cpu().numpy().astype(np.float32), want)
+    d_cpu_cuda = rel(cpu, want)
+    print(f"  fused layer vs the reference's CPU path {d_fused_cpu:.2e}; vs its CUDA sequence {d_fused_cuda:.2e}; "
+          f"the reference's CPU path vs its own CUDA sequence {d_cpu_cuda:.2e}")
+    assert d_fused_cpu <= 1e-3, d_fused_cpu
+    assert d_fused_cuda <= d_cpu_cuda * 1.05 + 5e-4, (d_fused_cuda, d_cpu_cuda)

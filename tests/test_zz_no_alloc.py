@@ -52,9 +52,35 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
     assert lib().raw("sgr_status")(0) == 0
 
 
+@pytest.mark.parametrize("n", [1, 4, 8])
+def test_static_scratch_at_the_decode_geometry_against_the_oracle(oracle, n):
+    """The use the entry point is documented for - hidden 2048, expert FFN 512, 256 experts, top-8, a
+    handful of token rows - against the CPU expert path, two calls in a row. At n = 4 and 8 a call
+    on a workspace runs the row-streaming expert kernel; the static call must make the same choice
+    (the whole layout fits the array) and give the same result."""
+    from tests.test_gpu_moe_layer import oracle_layer
+    hidden, n_ff, n_expert, k = 2048, 512, 256, 8
+    w = synth.MoeWeights(hidden, n_ff, n_expert, DEV, seed=20260718)
+    runner = MoeLayerRunner(8, hidden, n_ff, n_expert, k, DEV)
+    assert lib().raw("sgr_moe_layer_workspace_bytes")(8, hidden, n_ff, n_expert, k) <= \
+        lib().raw("sgr_moe_layer_static_limit")()
+    blob_np = w.blob.cpu().numpy()
+    for seed in (61 + n, 71 + n):
+        (o_ws, x_ws, i_ws, w_ws), (o_st, x_st, i_st, w_st) = _run_both(w, runner, n, k, seed)
+        x_np = synth.normal_fp16((n, hidden), seed, DEV).cpu().numpy()
+        want = oracle_layer(oracle, w, x_np, x_np.astype(np.float32), k, blob_np=blob_np)
+        assert np.array_equal(i_st, want["idx"][:, :k]) and np.array_equal(i_st, i_ws)
+        err = rel(o_st, want["out"])
+        print(f"static entry, {n} rows: max relative error vs the CPU path {err:.2e}")
+        assert err <= LAYER_TOL
+        assert np.array_equal(o_st, o_ws)              # same kernels, same arithmetic as the workspace call
+    assert lib().raw("sgr_status")(0) == 0
+
+
 def test_static_scratch_refuses_shapes_beyond_its_limit():
     limit = lib().raw("sgr_moe_layer_static_limit")()
-    assert limit == 1 << 20
+    assert limit == 2 << 20
+    assert lib().raw("sgr_moe_layer_workspace_bytes")(24, 2048, 512, 256, 8) > limit     # 24 rows: refused too
     need = lib().raw("sgr_moe_layer_workspace_bytes")(64, 2048, 512, 256, 8)
     assert need > limit
     w = synth.MoeWeights(2048, 512, 4, DEV, seed=5)        # few experts: cheap to make
