@@ -654,7 +654,7 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gemv", "tc"],
                     help="decode: the 40-layer stack (default); prefill: one layer over a 2048-row chunk; "
                          "gemv: the dense GEMV sweep; tc: the fp16 tensor-core GEMM of the tc_* entries")
-    ap.add_argument("--kernel", default=None, choices=["rows", "items"],
+    ap.add_argument("--kernel", default=None, choices=["rows", "items", "two_launch"],
                     help="decode: force the row-streaming or the item expert kernel (default: the library's choice)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--shape", default=None, help="gemv workload: only this ROWS,K shape; tc workload: ROWS,K,TOKENS (profiling captures)")
@@ -826,24 +826,37 @@ def decode_leg(ws, inputs, x0, biases, n, args, device, e2e):
     uniq = [len(np.unique(idx[li])) for li in range(layers)]
     ex_bytes = sum((u + 1) * EXPERT_BYTES for u in uniq)
     step_bytes = sum((u + 1) * EXPERT_BYTES + ROUTER_BYTES for u in uniq)
-    stage_ms = {}
-    for name, mask in (("route", 1), ("experts", 6)):
-        g = stack.capture_stage(n, mask)          # that stage of all layers, back to back
-        g.replay()
-        stage_ms[name] = timed(g.replay, 5)
     peak, peak_kind = load_peaks()
-    ex_gbs = ex_bytes / (stage_ms["experts"] * 1e-3) / 1e9
-    use_rows = args.kernel == "rows" or (args.kernel is None and n >= 4)
-    kernel = "expert_rows_kernel" if use_rows else "expert_stream_kernel"
-    traffic, traffic_source = traffic_per_launch(kernel, ex_bytes / layers)
-    out["roofline"] = {"kernel": kernel, "bound": "hbm", "achieved": ex_gbs, "peak": peak,
-                       "unit": "GB/s", "frac": ex_gbs / peak, "peak_source": f"{peak_kind} copy bandwidth (burst)",
-                       "frac_of_nominal_8tbs": ex_gbs / 8000.0,
-                       "traffic": traffic, "traffic_source": traffic_source,
-                       "bytes_per_launch": ex_bytes / layers, "us_per_launch": stage_ms["experts"] * 1e3 / layers,
-                       "stage_ms_per_step": stage_ms,
-                       "step": {"algorithmic_bytes": step_bytes, "gbs": step_bytes / (ms_step * 1e-3) / 1e9,
-                                "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak}}
+    if args.kernel is None and n <= 3:
+        # one persistent launch per layer does everything (router, selection, experts, combine): the
+        # launch is the layer, timed inside the step; its algorithmic bytes include the router matrix
+        gbs = step_bytes / (ms_step * 1e-3) / 1e9
+        out["roofline"] = {"kernel": "token_layer_kernel", "bound": "hbm", "achieved": gbs, "peak": peak,
+                           "unit": "GB/s", "frac": gbs / peak, "peak_source": f"{peak_kind} copy bandwidth (burst)",
+                           "frac_of_nominal_8tbs": gbs / 8000.0,
+                           "traffic": traffic_per_launch("token_layer_kernel", step_bytes / layers)[0],
+                           "traffic_source": traffic_per_launch("token_layer_kernel", step_bytes / layers)[1],
+                           "bytes_per_launch": step_bytes / layers, "us_per_launch": ms_step * 1e3 / layers,
+                           "stage_ms_per_step": {"layer": ms_step},
+                           "step": {"algorithmic_bytes": step_bytes, "gbs": gbs, "frac": gbs / peak}}
+    else:
+        stage_ms = {}
+        for name, mask in (("route", 1), ("experts", 6)):
+            g = stack.capture_stage(n, mask)          # that stage of all layers, back to back
+            g.replay()
+            stage_ms[name] = timed(g.replay, 5)
+        ex_gbs = ex_bytes / (stage_ms["experts"] * 1e-3) / 1e9
+        use_rows = args.kernel == "rows" or (args.kernel in (None, "two_launch") and n >= 4)
+        kernel = "expert_rows_kernel" if use_rows else "expert_stream_kernel"
+        traffic, traffic_source = traffic_per_launch(kernel, ex_bytes / layers)
+        out["roofline"] = {"kernel": kernel, "bound": "hbm", "achieved": ex_gbs, "peak": peak,
+                           "unit": "GB/s", "frac": ex_gbs / peak, "peak_source": f"{peak_kind} copy bandwidth (burst)",
+                           "frac_of_nominal_8tbs": ex_gbs / 8000.0,
+                           "traffic": traffic, "traffic_source": traffic_source,
+                           "bytes_per_launch": ex_bytes / layers, "us_per_launch": stage_ms["experts"] * 1e3 / layers,
+                           "stage_ms_per_step": stage_ms,
+                           "step": {"algorithmic_bytes": step_bytes, "gbs": step_bytes / (ms_step * 1e-3) / 1e9,
+                                    "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak}}
     out["uniq_mean"] = float(np.mean(uniq))
     out["hot"] = float(np.mean([synth.hot_share(idx[li], E) for li in range(layers)]))
     return out

@@ -55,6 +55,13 @@ int sgr_quantize_q8_k(const uint16_t* x_f16, void* out_q8, long long n, void* st
 int sgr_quantize_q8_k_n(const uint16_t* x_f16, void* out_q8, const int* d_rows, int row_mult,
                         int n_max, void* stream);
 
+/* cuda_ops.hpp:149  rmsnorm_quant_f16: out = f16(x * rsqrt(mean(x^2) + eps) * w) per row of n values and the
+ * Q8_K blocks of out, in one launch; bit-identical to the norm followed by the quantiser. n % 256 == 0
+ * (the reference's fallback for other n is its unfused norm kernel, which this library does not hold:
+ * SGR_EUNSUPPORTED). */
+int sgr_rmsnorm_quant_f16(uint16_t* out, const uint16_t* x, const uint16_t* w, void* xq, int n, float eps,
+                          int n_rows, void* stream);
+
 /* ---- Q4_K x Q8_K GEMV family --------------------------------------------------- */
 /* cuda_ops.hpp:41   gemv_q4_k_q8 (fp32 out) */
 int sgr_gemv_q4_k_q8(const void* w, const void* x_q8, float* y, int n_rows, int k, void* stream);
@@ -106,6 +113,18 @@ int sgr_gemv_grouped_tab_q4_k_q8_f16out_mtok(const void* const* w_tab, const int
                                              const int* toff, const int* meta, int tiles_max,
                                              const void* xq, uint16_t* y, int n_rows, int k,
                                              int n_expert, int tok_per, void* stream);
+/* cuda_ops.hpp:169  gemv_q4_k_q8_f16out_resadd: y as gemv_q4_k_q8_f16out, then
+ * res_inout[i] = f16(f32(res_inout[i]) + f32(y[i])); one token row. */
+int sgr_gemv_q4_k_q8_f16out_resadd(const void* w, const void* x_q8, uint16_t* y, uint16_t* res_inout,
+                                   int n_rows, int k, void* stream);
+/* cuda_ops.hpp:156  gemv2m_q4_k_q8_f16out: two projections of one token row in one launch
+ * (`slot` is accepted and ignored: there is no per-layer parameter block to key). */
+int sgr_gemv2m_q4_k_q8_f16out(const void* w1, const void* w2, const void* xq, uint16_t* y1, uint16_t* y2,
+                              int rows1, int rows2, int k, int slot, void* stream);
+/* cuda_ops.hpp:160  gemv3m_q4_k_q8_f16out: three projections. */
+int sgr_gemv3m_q4_k_q8_f16out(const void* w1, const void* w2, const void* w3, const void* xq, uint16_t* y1,
+                              uint16_t* y2, uint16_t* y3, int rows1, int rows2, int rows3, int k, int slot,
+                              void* stream);
 /* Parity probe, no counterpart launcher: the raw int32 sub-block dots of one
  * activation row, out[(row*nb + blk)*8 + s] - the unit src/kernels/cuda/q4_k.cu:38-53
  * and src/kernels/cpu/q4_avx2.cpp:99-119 both compute. */

@@ -65,6 +65,10 @@ void sigmoid_gate_scalar_batched_f16(uint16_t* out, const float* g, int n_rows, 
 void moe_combine_f16(uint16_t* out, const uint16_t* expert_out, const int* idx, const float* weight, int n_expert_used, int hidden, cudaStream_t stream);
 void moe_combine_batched_f16(uint16_t* out, const uint16_t* expert_y, const float* weight, int n_used, int hidden, int n_rows, cudaStream_t stream);
 void moe_combine_add_slots_f16(uint16_t* out, const uint16_t* expert_y, const float* weight, const int* rk, int n_used, int hidden, int n_list, cudaStream_t stream);
+void rmsnorm_quant_f16(uint16_t* out, const uint16_t* x, const uint16_t* w, q4k::BlockQ8K* xq, int n, float eps, int n_rows, cudaStream_t stream);
+void gemv2m_q4_k_q8_f16out(const q4k::BlockQ4K* w1, const q4k::BlockQ4K* w2, const q4k::BlockQ8K* xq, uint16_t* y1, uint16_t* y2, int rows1, int rows2, int k, int slot, cudaStream_t stream);
+void gemv3m_q4_k_q8_f16out(const q4k::BlockQ4K* w1, const q4k::BlockQ4K* w2, const q4k::BlockQ4K* w3, const q4k::BlockQ8K* xq, uint16_t* y1, uint16_t* y2, uint16_t* y3, int rows1, int rows2, int rows3, int k, int slot, cudaStream_t stream);
+void gemv_q4_k_q8_f16out_resadd(const q4k::BlockQ4K* w, const q4k::BlockQ8K* xq, uint16_t* y, uint16_t* res_inout, int n_rows, int k, cudaStream_t stream);
 bool tc_gemm_q4_k_f16(const q4k::BlockQ4K* w, const uint16_t* x, uint16_t* y, uint16_t* scratch, int n_rows, int k, int n_tokens, cudaStream_t stream);
 void* tc_handle();
 size_t tc_scratch_elems(int max_rows, int max_k);
@@ -187,6 +191,18 @@ void moe_combine_batched_f16(uint16_t* out, const uint16_t* expert_y, const floa
 }
 void moe_combine_add_slots_f16(uint16_t* out, const uint16_t* expert_y, const float* weight, const int* rk, int n_used, int hidden, int n_list, cudaStream_t stream) {
   b200_detail::note(sgr_moe_combine_add_slots_f16(out, expert_y, weight, rk, n_used, hidden, n_list, stream));
+}
+void rmsnorm_quant_f16(uint16_t* out, const uint16_t* x, const uint16_t* w, q4k::BlockQ8K* xq, int n, float eps, int n_rows, cudaStream_t stream) {
+  b200_detail::note(sgr_rmsnorm_quant_f16(out, x, w, xq, n, eps, n_rows, stream));
+}
+void gemv2m_q4_k_q8_f16out(const q4k::BlockQ4K* w1, const q4k::BlockQ4K* w2, const q4k::BlockQ8K* xq, uint16_t* y1, uint16_t* y2, int rows1, int rows2, int k, int slot, cudaStream_t stream) {
+  b200_detail::note(sgr_gemv2m_q4_k_q8_f16out(w1, w2, xq, y1, y2, rows1, rows2, k, slot, stream));
+}
+void gemv3m_q4_k_q8_f16out(const q4k::BlockQ4K* w1, const q4k::BlockQ4K* w2, const q4k::BlockQ4K* w3, const q4k::BlockQ8K* xq, uint16_t* y1, uint16_t* y2, uint16_t* y3, int rows1, int rows2, int rows3, int k, int slot, cudaStream_t stream) {
+  b200_detail::note(sgr_gemv3m_q4_k_q8_f16out(w1, w2, w3, xq, y1, y2, y3, rows1, rows2, rows3, k, slot, stream));
+}
+void gemv_q4_k_q8_f16out_resadd(const q4k::BlockQ4K* w, const q4k::BlockQ8K* xq, uint16_t* y, uint16_t* res_inout, int n_rows, int k, cudaStream_t stream) {
+  b200_detail::note(sgr_gemv_q4_k_q8_f16out_resadd(w, xq, y, res_inout, n_rows, k, stream));
 }
 bool tc_gemm_q4_k_f16(const q4k::BlockQ4K* w, const uint16_t* x, uint16_t* y, uint16_t* scratch, int n_rows, int k, int n_tokens, cudaStream_t stream) {
   return sgr_tc_gemm_q4_k_f16(w, x, y, scratch, n_rows, k, n_tokens, stream) == 0;

@@ -288,6 +288,42 @@ class Oracle(_Common, _Lib):
         return y
 
 
+def rmsnorm_quant_f16(oracle, x16: np.ndarray, w16: np.ndarray, eps: float):
+    """CPU restatement of the fused RMS norm + Q8_K quantiser of the reference
+    (src/kernels/cuda/mmq.cu:533-641): x16 [rows][n] fp16, w16 [n] fp16 ->
+    (out fp16 [rows][n], Q8_K blocks uint8 [rows][n/256*276]). The summation order of the
+    kernel is followed step for step (that is what fixes the bits): with b = min(1024,
+    n rounded up to 32) threads, thread t adds x[t]^2, x[t+b]^2, ... with FMA (the square of
+    an fp16 value is exact in fp32, so the FMA equals an fp32 add of the exact square), a warp
+    folds with shfl_down 16, 8, 4, 2, 1 (only lane 0's value is used), thread 0 adds the warp
+    sums in order; scale = rsqrt(sum / n + eps); out = f16((x * scale) * w). The device's rsqrtf is
+    an approximation within 2 ulp of the correctly rounded value used here, so `out` can differ
+    from the device's by one fp16 step in a few places; the Q8_K blocks are exactly those of `out`."""
+    rows, n = x16.shape
+    b = min(1024, (n + 31) // 32 * 32)
+    xf = x16.astype(np.float32)
+    wf = w16.astype(np.float32)
+    out = np.zeros((rows, n), dtype=np.float16)
+    f32 = np.float32
+    for r in range(rows):
+        acc = np.zeros(b, dtype=np.float32)
+        for i0 in range(0, n, b):
+            seg = xf[r, i0:i0 + b]
+            acc[:seg.size] = acc[:seg.size] + seg * seg
+        lanes = acc.reshape(b // 32, 32).copy()
+        for off in (16, 8, 4, 2, 1):                 # lane l += lane l + off (lanes >= 32 - off keep theirs)
+            shifted = np.zeros_like(lanes)
+            shifted[:, :32 - off] = lanes[:, off:]
+            shifted[:, 32 - off:] = lanes[:, 32 - off:]     # shfl_down past the end returns the lane's own value
+            lanes = (lanes + shifted).astype(np.float32)
+        s = f32(0)
+        for wsum in lanes[:, 0]:
+            s = f32(s + wsum)
+        scale = f32(1) / np.sqrt(f32(f32(s / f32(n)) + f32(eps)), dtype=np.float32)
+        out[r] = ((xf[r] * scale).astype(np.float32) * wf).astype(np.float32).astype(np.float16)
+    return out, oracle.quantize_q8k_f16(out)
+
+
 class Reference(_Common, _Lib):
     p = "ref_"
 

@@ -199,3 +199,35 @@ SGR_REF_API int sgr_moe_combine_add_slots_f16(uint16_t* out, const uint16_t* exp
   return 0;
 }
 
+SGR_REF_API int sgr_rmsnorm_quant_f16(uint16_t* out, const uint16_t* x, const uint16_t* w, void* xq, int n, float eps, int n_rows, void* stream) {
+  sager::cuda::rmsnorm_quant_f16((uint16_t*)out, (const uint16_t*)x, (const uint16_t*)w, (q4k::BlockQ8K*)xq, (int)n, (float)eps, (int)n_rows, (cudaStream_t)stream);
+  return 0;
+}
+
+SGR_REF_API int sgr_gemv2m_q4_k_q8_f16out(const void* w1, const void* w2, const void* xq, uint16_t* y1, uint16_t* y2, int rows1, int rows2, int k, int slot, void* stream) {
+  sager::cuda::gemv2m_q4_k_q8_f16out((const q4k::BlockQ4K*)w1, (const q4k::BlockQ4K*)w2, (const q4k::BlockQ8K*)xq, (uint16_t*)y1, (uint16_t*)y2, (int)rows1, (int)rows2, (int)k, (int)slot, (cudaStream_t)stream);
+  return 0;
+}
+
+SGR_REF_API int sgr_gemv3m_q4_k_q8_f16out(const void* w1, const void* w2, const void* w3, const void* xq, uint16_t* y1, uint16_t* y2, uint16_t* y3, int rows1, int rows2, int rows3, int k, int slot, void* stream) {
+  sager::cuda::gemv3m_q4_k_q8_f16out((const q4k::BlockQ4K*)w1, (const q4k::BlockQ4K*)w2, (const q4k::BlockQ4K*)w3, (const q4k::BlockQ8K*)xq, (uint16_t*)y1, (uint16_t*)y2, (uint16_t*)y3, (int)rows1, (int)rows2, (int)rows3, (int)k, (int)slot, (cudaStream_t)stream);
+  return 0;
+}
+
+SGR_REF_API int sgr_gemv_q4_k_q8_f16out_resadd(const void* w, const void* x_q8, uint16_t* y, uint16_t* res_inout, int n_rows, int k, void* stream) {
+  sager::cuda::gemv_q4_k_q8_f16out_resadd((const q4k::BlockQ4K*)w, (const q4k::BlockQ8K*)x_q8, (uint16_t*)y, (uint16_t*)res_inout, (int)n_rows, (int)k, (cudaStream_t)stream);
+  return 0;
+}
+
+
+// Reference-only pieces that the fused launchers are specified against (the two-kernel sequences
+// they replace): the unfused RMS norm and the fp16 add. No counterpart in include/sager_b200.h.
+SGR_REF_API int sgr_ref_rmsnorm_batched_f16(uint16_t* out, const uint16_t* x, const uint16_t* w, int n, float eps, int n_rows, void* stream) {
+  sager::cuda::rmsnorm_batched_f16(out, x, w, n, eps, n_rows, (cudaStream_t)stream);
+  return 0;
+}
+
+SGR_REF_API int sgr_ref_add_f16(uint16_t* in_out, const uint16_t* residual, int n, void* stream) {
+  sager::cuda::add_f16(in_out, residual, n, (cudaStream_t)stream);
+  return 0;
+}

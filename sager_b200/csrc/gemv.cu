@@ -10,7 +10,7 @@
 namespace sgr {
 namespace {
 
-enum Mode : int { kDense = 0, kPtrs = 1, kGrouped = 2, kTab = 3 };
+enum Mode : int { kDense = 0, kPtrs = 1, kGrouped = 2, kTab = 3, kMulti = 4 };
 
 struct GemvArgs {
   const unsigned char* w[2];            // dense: matrix bases
@@ -22,6 +22,11 @@ struct GemvArgs {
   const int *toff, *meta;                          // tab (device plan)
   int *mail, *mail_n;
   int* status;
+  uint16_t* res;                        // dense, one token, fp16 out: residual row updated in place
+  // multi: up to three matrices of the same k with their own outputs, one token row
+  const unsigned char* wm[3];
+  uint16_t* ym[3];
+  int rows_cum[3];                      // rows of matrices 0..m inclusive
 };
 
 // last e with toff[e] <= tile (toff is the E+1 exclusive prefix of tiles per expert)
@@ -40,13 +45,28 @@ __device__ __forceinline__ void store_out(void* y, size_t i, float v) {
   if constexpr (F16) reinterpret_cast<uint16_t*>(y)[i] = f2h(v);
   else reinterpret_cast<float*>(y)[i] = v;
 }
+// fp16 store followed by the residual add of the rounded value (add_kernel's semantics,
+// src/kernels/cuda/mmq.cu:870-876 of the reference): res = f16(f32(res) + f32(f16(v)))
+__device__ __forceinline__ void store_out_resadd(uint16_t* y, uint16_t* res, size_t i, float v) {
+  const uint16_t h = f2h(v);
+  y[i] = h;
+  res[i] = f2h(h2f(res[i]) + h2f(h));
+}
 
 template <int NMAT, int TT, int MODE, bool F16>
 __global__ void __launch_bounds__(kTileThreads) gemv_tile_kernel(const GemvArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int nb = a.nb;
   const int rc = tile_rows(nb);
-  const int row0 = blockIdx.x * rc;
+  int row0 = blockIdx.x * rc;
+  // plans and pointer tables may come from the kernel before this one; matrices named in the
+  // arguments are fixed, so their copies start first and the wait sits just before the
+  // activations are read (tile_run_staged's before_x hook)
+  if constexpr (MODE != kDense && MODE != kMulti) {
+    pdl_wait();
+    pdl_launch_dependents();
+  }
+  int mat = 0;                           // multi: which matrix this CTA works on
   const size_t row_bytes = static_cast<size_t>(nb) * kW4;
   const size_t xrow_bytes = static_cast<size_t>(nb) * kX8;
 
@@ -64,6 +84,20 @@ __global__ void __launch_bounds__(kTileThreads) gemv_tile_kernel(const GemvArgs 
     for (int m = 0; m < NMAT; ++m) wsrc[m] = a.w[m] + row0 * row_bytes;
     xbase = tok0;
     ybase = tok0;
+  } else if constexpr (MODE == kMulti) {
+    // tiles of matrix 0, then of matrix 1, then of matrix 2
+    const int t0 = (a.rows_cum[0] + rc - 1) / rc;
+    const int t1 = t0 + (a.rows_cum[1] - a.rows_cum[0] + rc - 1) / rc;
+    int tile = blockIdx.x, rows_m = a.rows_cum[0];
+    if (tile >= t1) { mat = 2; tile -= t1; rows_m = a.rows_cum[2] - a.rows_cum[1]; }
+    else if (tile >= t0) { mat = 1; tile -= t0; rows_m = a.rows_cum[1] - a.rows_cum[0]; }
+    row0 = tile * rc;
+    nrows = min(rc, rows_m - row0);
+    ntok = 1;
+    wsrc[0] = (mat == 0 ? a.wm[0] : (mat == 1 ? a.wm[1] : a.wm[2])) + row0 * row_bytes;
+    xbase = 0;
+    ybase = 0;
+    ncols = 0;
   } else if constexpr (MODE == kPtrs) {
     // y[e * rows_per + r]; every expert reads the SAME activation row, as the
     // reference kernel does (q4_k.cu:184-213 indexes xq[blk] only).
@@ -121,19 +155,56 @@ __global__ void __launch_bounds__(kTileThreads) gemv_tile_kernel(const GemvArgs 
   }
   if (nrows <= 0 || ntok <= 0) return;
 
-  tile_run<NMAT, TT>(
+  tile_run_staged<NMAT, TT>(
       smem, wsrc, nrows, nb, ntok,
-      [&](int t) { return a.xq + (xbase + t) * xrow_bytes; },
+      [] {
+        if constexpr (MODE == kDense || MODE == kMulti) {
+          pdl_wait();
+          pdl_launch_dependents();
+        }
+      },
+      [&](const XTile& xt, int t0, int nt) {
+        xtile_stage(xt, nt, [&](int t) { return a.xq + (xbase + t0 + t) * xrow_bytes; }, threadIdx.x, kTileThreads);
+      },
       [&](int r, int t, const float (&v)[NMAT]) {
+        if constexpr (MODE == kMulti) {
+          uint16_t* ym = mat == 0 ? a.ym[0] : (mat == 1 ? a.ym[1] : a.ym[2]);
+          ym[row0 + r] = f2h(v[0]);
+          return;
+        }
 #pragma unroll
         for (int m = 0; m < NMAT; ++m) {
           size_t oi;
           if constexpr (MODE == kPtrs) oi = static_cast<size_t>(blockIdx.y) * a.rows_per + row0 + r;
           else oi = (ybase + t) * ncols + row0 + r;
+          if constexpr (MODE == kDense && F16 && NMAT == 1) {
+            if (a.res != nullptr) {
+              store_out_resadd(reinterpret_cast<uint16_t*>(a.y[0]), a.res, oi, v[0]);
+              continue;
+            }
+          }
           store_out<F16>(a.y[m], oi, v[m]);
         }
       },
       a.status);
+}
+
+// Every launch of the family may start while the kernel before it in the stream drains
+// (programmatic dependent launch); the kernels wait for that kernel's results themselves,
+// just before they first read anything it could have written.
+template <typename Kern>
+int launch_dependent(Kern kern, dim3 grid, int threads, size_t smem, cudaStream_t stream, const GemvArgs& a) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, a) == cudaSuccess ? kOk : kErrLaunch;
 }
 
 template <int NMAT, int TT, int MODE, bool F16>
@@ -146,8 +217,7 @@ int launch_tile(const GemvArgs& a, dim3 grid, cudaStream_t stream) {
                              static_cast<int>(smem)) != cudaSuccess)
       return kErrLaunch;
   }
-  kern<<<grid, kTileThreads, smem, stream>>>(a);
-  return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
+  return launch_dependent(kern, grid, kTileThreads, smem, stream, a);
 }
 
 // ---- dense matrices far larger than the machine (the LM head): a persistent kernel ----------
@@ -205,6 +275,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const Ge
       }
     }
   } else {
+    pdl_wait();                                          // the weight stream above is already running
+    pdl_launch_dependents();
     xtile_stage(xt, a.n_tokens, [&](int t) { return a.xq + static_cast<size_t>(t) * nb * kX8; },
                 threadIdx.x, kStreamBlocks);
     asm volatile("bar.sync 1, %0;" ::"n"(kStreamBlocks) : "memory");
@@ -230,7 +302,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const Ge
         const long long row = b / nb;
 #pragma unroll
         for (int t = 0; t < TT; ++t)
-          if (t < a.n_tokens) store_out<F16>(a.y[0], static_cast<size_t>(t) * a.n_rows + row, acc[0][t]);
+          if (t < a.n_tokens) {
+            if constexpr (F16 && TT == 1) {
+              if (a.res != nullptr) {
+                store_out_resadd(reinterpret_cast<uint16_t*>(a.y[0]), a.res, static_cast<size_t>(row), acc[0][t]);
+                continue;
+              }
+            }
+            store_out<F16>(a.y[0], static_cast<size_t>(t) * a.n_rows + row, acc[0][t]);
+          }
       }
     }
   }
@@ -244,8 +324,7 @@ int launch_stream(const GemvArgs& a, int sms, cudaStream_t stream) {
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
       cudaSuccess)
     return kErrLaunch;
-  kern<<<sms, kStreamThreads, smem, stream>>>(a);
-  return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
+  return launch_dependent(kern, dim3(sms), kStreamThreads, smem, stream, a);
 }
 
 // The persistent kernel pays off when every SM gets several stages.
@@ -284,6 +363,7 @@ __global__ void __launch_bounds__(kDirectThreads) gemv_direct_kernel(const GemvA
   for (int m = 0; m < NMAT; ++m)
 #pragma unroll
     for (int t = 0; t < TT; ++t) acc[m][t] = 0.f;
+  bool waited = false;                     // the previous kernel is awaited once the first weights are requested
   for (int gi = lr; gi < groups; gi += lpr) {
     const int blk = gi >> 2, g = gi & 3;
     float d[NMAT], dmin[NMAT];
@@ -309,6 +389,11 @@ __global__ void __launch_bounds__(kDirectThreads) gemv_direct_kernel(const GemvA
         lo[m][i] = raw[i] & 0x0F0F0F0Fu;
         hi[m][i] = (raw[i] >> 4) & 0x0F0F0F0Fu;
       }
+    }
+    if (!waited) {
+      pdl_wait();
+      pdl_launch_dependents();
+      waited = true;
     }
 #pragma unroll
     for (int t = 0; t < TT; ++t) {
@@ -340,6 +425,10 @@ __global__ void __launch_bounds__(kDirectThreads) gemv_direct_kernel(const GemvA
       }
     }
   }
+  if (!waited) {
+    pdl_wait();
+    pdl_launch_dependents();
+  }
 #pragma unroll
   for (int m = 0; m < NMAT; ++m)
 #pragma unroll
@@ -360,9 +449,8 @@ int launch_direct(const GemvArgs& a, cudaStream_t stream) {
   const int lpr = a.nb * 4 < 32 ? a.nb * 4 : 32;
   const int rows_per_cta = (kDirectThreads / 32) * (32 / lpr);
   const int grid = (a.n_rows + rows_per_cta - 1) / rows_per_cta;
-  if (a.n_tokens == 2) gemv_direct_kernel<NMAT, 2, F16><<<grid, kDirectThreads, 0, stream>>>(a);
-  else gemv_direct_kernel<NMAT, 4, F16><<<grid, kDirectThreads, 0, stream>>>(a);
-  return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
+  if (a.n_tokens == 2) return launch_dependent(gemv_direct_kernel<NMAT, 2, F16>, dim3(grid), kDirectThreads, 0, stream, a);
+  return launch_dependent(gemv_direct_kernel<NMAT, 4, F16>, dim3(grid), kDirectThreads, 0, stream, a);
 }
 
 // Two to four token rows over a matrix of at most a few tiles per SM, 16-byte aligned.
@@ -379,7 +467,7 @@ constexpr int kDenseTokTile = 16;
 
 template <int NMAT, bool F16>
 int launch_dense(const void* w0, const void* w1, const void* xq, void* y0, void* y1, int n_rows,
-                 int k, int n_tokens, cudaStream_t stream) {
+                 int k, int n_tokens, cudaStream_t stream, uint16_t* res = nullptr) {
   if (n_tokens <= 0 || n_rows <= 0) return kOk;
   if (!w0 || !xq || !y0 || (NMAT == 2 && (!w1 || !y1)) || k <= 0 || k % kQK != 0) return kErrArg;
   if (reinterpret_cast<uintptr_t>(xq) & 3u) return kErrAlign;
@@ -393,6 +481,7 @@ int launch_dense(const void* w0, const void* w1, const void* xq, void* y0, void*
   a.nb = k / kQK;
   a.n_tokens = n_tokens;
   a.status = status_word();
+  a.res = res;
   const int rc = tile_rows(a.nb);
   if constexpr (NMAT == 1) {
     if (const int sms = stream_sms(a)) {
@@ -498,6 +587,68 @@ SGR_API int sgr_gemv_q4_k_q8(const void* w, const void* x_q8, float* y, int n_ro
 SGR_API int sgr_gemv_q4_k_q8_f16out(const void* w, const void* x_q8, uint16_t* y, int n_rows, int k,
                                     void* stream) {
   return launch_dense<1, true>(w, nullptr, x_q8, y, nullptr, n_rows, k, 1, as_stream(stream));
+}
+
+// cuda_ops.hpp:169-171 of the reference: the fp16 GEMV and, on the rounded result, the residual add.
+// Same kernels as sgr_gemv_q4_k_q8_f16out, so y is bit-identical to it and res_inout to an add after it.
+SGR_API int sgr_gemv_q4_k_q8_f16out_resadd(const void* w, const void* x_q8, uint16_t* y, uint16_t* res_inout,
+                                           int n_rows, int k, void* stream) {
+  if (n_rows > 0 && !res_inout) return kErrArg;
+  return launch_dense<1, true>(w, nullptr, x_q8, y, nullptr, n_rows, k, 1, as_stream(stream), res_inout);
+}
+
+namespace {
+// cuda_ops.hpp:156-164 of the reference: two or three projections of one token row in one launch.
+int launch_multi(int nmat, const void* const (&w)[3], const void* xq, uint16_t* const (&y)[3], const int (&rows)[3],
+                 int k, cudaStream_t stream) {
+  int total = 0;
+  for (int m = 0; m < nmat; ++m) {
+    if (rows[m] < 0) return kErrArg;
+    total += rows[m];
+  }
+  if (total == 0) return kOk;
+  if (!xq || k <= 0 || k % kQK != 0) return kErrArg;
+  for (int m = 0; m < nmat; ++m)
+    if (rows[m] > 0 && (!w[m] || !y[m])) return kErrArg;
+  if (reinterpret_cast<uintptr_t>(xq) & 3u) return kErrAlign;
+  GemvArgs a{};
+  int cum = 0, tiles = 0;
+  a.nb = k / kQK;
+  const int rc = tile_rows(a.nb);
+  for (int m = 0; m < 3; ++m) {
+    const int r = m < nmat ? rows[m] : 0;
+    a.wm[m] = m < nmat ? static_cast<const unsigned char*>(w[m]) : nullptr;
+    a.ym[m] = m < nmat ? y[m] : nullptr;
+    cum += r;
+    a.rows_cum[m] = cum;
+    tiles += (r + rc - 1) / rc;
+  }
+  a.xq = static_cast<const unsigned char*>(xq);
+  a.n_rows = total;
+  a.n_tokens = 1;
+  a.tok_tile = 1;
+  a.status = status_word();
+  return launch_tile<1, 1, kMulti, true>(a, dim3(tiles, 1), stream);
+}
+}  // namespace
+
+SGR_API int sgr_gemv2m_q4_k_q8_f16out(const void* w1, const void* w2, const void* xq, uint16_t* y1, uint16_t* y2,
+                                      int rows1, int rows2, int k, int slot, void* stream) {
+  (void)slot;                              // the reference keys a per-layer parameter block by it; nothing to key here
+  const void* const w[3] = {w1, w2, nullptr};
+  uint16_t* const y[3] = {y1, y2, nullptr};
+  const int rows[3] = {rows1, rows2, 0};
+  return launch_multi(2, w, xq, y, rows, k, as_stream(stream));
+}
+
+SGR_API int sgr_gemv3m_q4_k_q8_f16out(const void* w1, const void* w2, const void* w3, const void* xq, uint16_t* y1,
+                                      uint16_t* y2, uint16_t* y3, int rows1, int rows2, int rows3, int k, int slot,
+                                      void* stream) {
+  (void)slot;
+  const void* const w[3] = {w1, w2, w3};
+  uint16_t* const y[3] = {y1, y2, y3};
+  const int rows[3] = {rows1, rows2, rows3};
+  return launch_multi(3, w, xq, y, rows, k, as_stream(stream));
 }
 
 SGR_API int sgr_gemv_q4_k_q8_batched(const void* w, const void* x_q8, float* y, int n_rows, int k,

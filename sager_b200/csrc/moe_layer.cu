@@ -50,6 +50,9 @@ constexpr int kMaxRows = 64;       // token rows per call (row masks are 64-bit)
 constexpr int kTokTile = 8;        // token rows per tile of the item kernel (one MMA n-tile)
 constexpr int kMaxGrid = 192;            // most CTAs the expert kernels are launched with
 constexpr int kTmapSlots = 6;            // patched TMA descriptor sets per CTA of the row-streaming kernel
+constexpr int kTokenKernelMaxRows = 3;   // layers of up to this many token rows run as one persistent launch
+                                         // (measured per layer, us: 26.6 / 36.1 / 44.7 against 30.1 / 39.6 / 47.3 for
+                                         // route + expert kernel; at 4 rows 57 against 50)
 constexpr int kRowsKernelMinRows = 4;    // layers of at least this many token rows run the row-streaming kernel
                                          // (measured: 4 rows 8 % faster, 8 rows 16 %, 2 rows slower)
 constexpr int kRouteTok = 8;       // token rows per CTA of the route kernel
@@ -684,6 +687,7 @@ __device__ __forceinline__ void combine_rows(const LayerDev& L, int row0, int nr
 }
 
 #include "expert_rows.cuh"
+#include "token_layer.cuh"
 
 __global__ void __launch_bounds__(kStreamThreads, 1) expert_stream_kernel(const LayerDev L) {
   extern __shared__ __align__(16) unsigned char smem[];
@@ -1243,6 +1247,17 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
     L.grid = std::min(sms, kMaxGrid);
   }
   cudaStream_t s = as_stream(stream);
+
+  // A few token rows, whole layer on this device, all stages in one call: the single
+  // persistent launch (token_layer.cuh). Bit 6 of `stages` keeps the two-launch path.
+  if ((stages & 7) == 7 && !(stages & (8 | 16 | 32 | 64)) && a->n <= kTokenKernelMaxRows && a->n * a->n_used <= 32 &&
+      !a->routing_given && a->xq_in == nullptr && a->xq_out == nullptr && a->wait_flags == nullptr &&
+      L.e_lo == 0 && L.e_hi == L.E && L.sh_lo == 0 && L.sh_hi == L.n && L.nbh <= 16 && L.nbf <= 16 &&
+      a->workspace_bytes >= lay.items_total) {
+    const tk::Geom g = tk::geom(tk::kMaxTok, L.H, L.FF, L.E, L.grid);
+    if (g.total <= 227 * 1024 && g.rows_per_cta <= tk::kWarps)
+      return launch_pdl(tk::token_layer_kernel, dim3(L.grid), tk::kThreads, g.total, s, L);
+  }
 
   int rc = kOk;
   if (!(stages & 1)) {

@@ -21,7 +21,9 @@ def _p(t):
     return None if t is None else C.c_void_p(t.data_ptr())
 
 
-KERNEL_BITS = {None: 0, "rows": 16, "items": 32}
+# None = the library's choice (one persistent launch for up to three rows, else route + the expert kernel
+# picked by row count); "two_launch" = route + expert kernel by row count; "rows" / "items" force one of them
+KERNEL_BITS = {None: 0, "rows": 16, "items": 32, "two_launch": 64}
 
 
 class MoeLayerRunner:
@@ -99,7 +101,8 @@ class MoeStack:
         # per-layer routing records, so a finished step can be inspected
         self.idx = torch.zeros(len(layers), n_max, n_used + 1, dtype=torch.int32, device=device)
         self.w = torch.zeros(len(layers), n_max, n_used + 1, dtype=torch.float32, device=device)
-        self.launches_per_step = 2 * len(layers)     # route + experts
+        # one persistent launch per layer for up to three rows, else route + experts
+        self.launches_per_step = (1 if (kernel is None and n_max <= 3) else 2) * len(layers)
 
     def layer_args(self, li, n):
         w = self.layers[li]

@@ -115,8 +115,8 @@ def full_w():
     return synth.MoeWeights(2048, 512, 256, DEV, seed=20260718)
 
 
-@pytest.mark.parametrize("kernel", ["items", "rows"])
-@pytest.mark.parametrize("n", [1, 2, 5, 17, 64])
+@pytest.mark.parametrize("kernel", ["items", "rows", None])
+@pytest.mark.parametrize("n", [1, 2, 3, 4, 5, 17, 64])
 def test_small_layer_all_row_counts(oracle, small_w, n, kernel):
     check(oracle, small_w, n, 4, seed=100 + n, n_max=64, kernel=kernel)
 
@@ -160,8 +160,8 @@ def test_weight_pointers_with_only_block_alignment(oracle, small_w, kernel, shif
     check(oracle, w, 21, 4, seed=77, kernel=kernel)
 
 
-@pytest.mark.parametrize("kernel", ["items", "rows"])
-@pytest.mark.parametrize("n", [1, 4, 64])
+@pytest.mark.parametrize("kernel", ["items", "rows", None])
+@pytest.mark.parametrize("n", [1, 2, 4, 64])
 def test_benchmark_geometry(oracle, full_w, n, kernel):
     bias = synth.zipf_bias(256, seed=5, alpha=0.6) if n == 64 else None
     _, _, err = check(oracle, full_w, n, 8, seed=20260718 + n, bias=bias, n_max=64, kernel=kernel)
@@ -358,7 +358,7 @@ def _h_code_flips(oracle, w, blob_np, runner, x16_np, idx_row, t, k):
     return total, flips
 
 
-@pytest.mark.parametrize("kernel", ["items", "rows"])
+@pytest.mark.parametrize("kernel", ["items", "rows", None])
 def test_benchmark_geometry_seed_sweep(oracle, kernel):
     """32 seeded cases (4 weight sets x 8 input sets) x 1, 4 and 64 token rows, none of them picked:
     every case must meet the stated bound of 1e-3 against the CPU expert path, and the distribution
@@ -401,10 +401,10 @@ def test_benchmark_geometry_seed_sweep(oracle, kernel):
 def test_strided_pointer_table_is_used_in_place(small_w):
     """The reference's decode table is [3][Lm][E] (src/core/session.cpp:3596-3598): a layer's
     gate / up / down slices are Lm * E pointers apart. tab_stride takes them where they are."""
-    n, k, Lm, li = 9, 4, 3, 2
+    k, Lm, li = 4, 3, 2
     E = small_w.n_expert
-    x16 = synth.normal_fp16((n, small_w.hidden), 431, DEV)
-    for kernel in ("items", "rows"):
+    for kernel, n in (("items", 9), ("rows", 9), (None, 3)):
+        x16 = synth.normal_fp16((n, small_w.hidden), 431, DEV)
         _, _, want = run_layer(small_w, n, k, x16, n_max=16, kernel=kernel)
         big = torch.zeros(3, Lm, E, dtype=torch.int64, device=DEV)
         big[:, li, :] = small_w.table()
@@ -428,3 +428,51 @@ def test_rows_kernel_with_one_block_column_per_group(oracle, hidden, n_ff):
     w = synth.MoeWeights(hidden, n_ff, E, DEV, seed=77, std=0.05)
     for seed in (1, 2):
         check(oracle, w, n, k, seed=900 + seed, n_max=64, kernel="rows", tol=1e-3)
+
+
+# ---- the single persistent launch for up to three token rows (kernel=None; four rows covered too,
+# whichever path the library picks there) --------------------------------------------------------
+@pytest.mark.parametrize("n", [1, 2, 3, 4])
+def test_token_kernel_variants(oracle, small_w, n):
+    """Without the shared expert, with a router bias, with absent experts (zero contribution, id
+    mailed once), and with weight pointers that are only 2- or 4-byte aligned."""
+    import copy
+    k = 4
+    check(oracle, small_w, n, k, seed=600 + n, use_shared=False)
+    bias = synth.zipf_bias(16, seed=3, alpha=2.0)
+    check(oracle, small_w, n, k, seed=610 + n, bias=bias)
+    x16 = synth.normal_fp16((n, 512), 620 + n, DEV)
+    r0, _, _ = run_layer(small_w, n, k, x16)
+    used = sorted(set(r0.route_idx.cpu().numpy()[:n, :k].reshape(-1).tolist()))
+    absent = (used[0], used[-1])
+    runner, _, _ = check(oracle, small_w, n, k, seed=620 + n, absent=absent)
+    n_mail = int(runner.mail_n.item())
+    assert sorted(runner.mail.cpu().numpy()[:n_mail].tolist()) == sorted(absent)
+    for shift in (2, 4):
+        w = copy.copy(small_w)
+        big = torch.empty(small_w.blob.numel() + 16, dtype=torch.uint8, device=DEV)
+        w.blob = big[shift:shift + small_w.blob.numel()].view(small_w.blob.shape)
+        w.blob.copy_(small_w.blob)
+        check(oracle, w, n, k, seed=630 + n)
+
+
+def test_token_kernel_agrees_with_the_two_launch_path(full_w):
+    """Same routing bit for bit and the same layer to fp32 rounding as route + expert kernel, over
+    repeated calls on one workspace (the grid barrier's counter carries over from call to call)."""
+    k = 8
+    for n in (1, 2, 3, 4):
+        runner = MoeLayerRunner(4, full_w.hidden, full_w.n_ff, full_w.n_expert, k, DEV)
+        for rep in range(3):
+            x16 = synth.normal_fp16((n, full_w.hidden), 700 + 10 * n + rep, DEV)
+            res = []
+            for kernel in (None, "two_launch"):
+                out32 = torch.zeros(n, full_w.hidden, dtype=torch.float32, device=DEV)
+                x = x16.clone()
+                a = runner.args(n, x16, full_w.router, full_w.table(), full_w.shared_ptrs(), x_f16=x, out_f32=out32)
+                runner.run(a, kernel=kernel)
+                torch.cuda.synchronize()
+                res.append((out32.clone(), x.clone(), runner.route_idx.clone(), runner.route_w.clone()))
+            assert torch.equal(res[0][2][:n], res[1][2][:n])
+            assert torch.equal(res[0][3][:n], res[1][3][:n])
+            assert rel(res[0][0].cpu().numpy(), res[1][0].cpu().numpy()) < 1e-5
+    assert lib().raw("sgr_status")(0) == 0

@@ -234,3 +234,18 @@ def test_moe_layer_is_sum_of_ffns(oracle, golden):
         wsum = sum(r["w"][t, kk] for kk in range(K) if r["idx"][t, kk] != 1)
         assert rel(r["out"][t], res[t] + (wsum + 1.0) * y) < 1e-5
         assert np.array_equal(r["logits"][t], oracle.router_logits(router, x16[t]))
+
+
+def test_rmsnorm_quant_restatement(oracle):
+    """The CPU restatement of the fused norm + quantiser: the rows are the RMS norm (against a
+    float64 evaluation, to the fp16 store) and the blocks are the Q8_K blocks of those rows."""
+    from oracle.oracle import rmsnorm_quant_f16
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal((3, 2048)) * 1.7).astype(np.float16)
+    w = (1.0 + 0.1 * rng.standard_normal(2048)).astype(np.float16)
+    out, xq = rmsnorm_quant_f16(oracle, x, w, 1e-6)
+    xd = x.astype(np.float64)
+    want = xd / np.sqrt((xd ** 2).mean(axis=1, keepdims=True) + 1e-6) * w.astype(np.float64)
+    assert np.abs(out.astype(np.float64) - want).max() <= 2.0 ** -10 * np.abs(want).max() * 1.01
+    assert np.array_equal(xq, oracle.quantize_q8k_f16(out))
+    assert xq.shape == (3, 8 * 276)
