@@ -131,6 +131,17 @@ int sgr_gemv3m_q4_k_q8_f16out(const void* w1, const void* w2, const void* w3, co
 int sgr_q4k_subblock_dots(const void* w, const void* x_q8, int* out, int n_rows, int k,
                           void* stream);
 
+/* ---- LM head on Q6_K weights and the candidate selection after it -------------------- */
+/* cuda_ops.hpp:48   gemv_q6_k_q8: y[row] = W6[row] . x, W6 in raw block_q6_K bytes (210 per 256 weights) */
+int sgr_gemv_q6_k_q8(const void* w_q6, const void* x_q8, float* y, int n_rows, int k, void* stream);
+/* cuda_ops.hpp:181  gemv_q6_k_q8_smx: the same (bit-identical to sgr_gemv_q6_k_q8) */
+int sgr_gemv_q6_k_q8_smx(const void* w_q6, const void* x_q8, float* y, int n_rows, int k, void* stream);
+/* cuda_ops.hpp:436  topk_select_f32_2p: the k <= 64 largest logits in descending order, ties by lower
+ * index; seg_v / seg_i: scratch of at least ceil(n / 2048) * k slots (SGR_EUNSUPPORTED when smaller).
+ * The logits are left as they are. */
+int sgr_topk_select_f32_2p(const float* logits, float* seg_v, int* seg_i, int seg_slots, float* out_v,
+                           int* out_i, int n, int k, void* stream);
+
 /* ---- router --------------------------------------------------------------------- */
 /* cuda_ops.hpp:277  gemv_f32_out_f16x */
 int sgr_gemv_f32_out_f16x(const float* w_f32, const uint16_t* x_f16, float* y, int n_rows, int k,

@@ -65,6 +65,9 @@ void sigmoid_gate_scalar_batched_f16(uint16_t* out, const float* g, int n_rows, 
 void moe_combine_f16(uint16_t* out, const uint16_t* expert_out, const int* idx, const float* weight, int n_expert_used, int hidden, cudaStream_t stream);
 void moe_combine_batched_f16(uint16_t* out, const uint16_t* expert_y, const float* weight, int n_used, int hidden, int n_rows, cudaStream_t stream);
 void moe_combine_add_slots_f16(uint16_t* out, const uint16_t* expert_y, const float* weight, const int* rk, int n_used, int hidden, int n_list, cudaStream_t stream);
+void gemv_q6_k_q8(const void* w_q6, const q4k::BlockQ8K* x_q8, float* y, int n_rows, int k, cudaStream_t stream);
+void gemv_q6_k_q8_smx(const void* w_q6, const q4k::BlockQ8K* x_q8, float* y, int n_rows, int k, cudaStream_t stream);
+void topk_select_f32_2p(const float* logits, float* seg_v, int* seg_i, int seg_slots, float* out_v, int* out_i, int n, int k, cudaStream_t stream);
 void rmsnorm_quant_f16(uint16_t* out, const uint16_t* x, const uint16_t* w, q4k::BlockQ8K* xq, int n, float eps, int n_rows, cudaStream_t stream);
 void gemv2m_q4_k_q8_f16out(const q4k::BlockQ4K* w1, const q4k::BlockQ4K* w2, const q4k::BlockQ8K* xq, uint16_t* y1, uint16_t* y2, int rows1, int rows2, int k, int slot, cudaStream_t stream);
 void gemv3m_q4_k_q8_f16out(const q4k::BlockQ4K* w1, const q4k::BlockQ4K* w2, const q4k::BlockQ4K* w3, const q4k::BlockQ8K* xq, uint16_t* y1, uint16_t* y2, uint16_t* y3, int rows1, int rows2, int rows3, int k, int slot, cudaStream_t stream);
@@ -191,6 +194,15 @@ void moe_combine_batched_f16(uint16_t* out, const uint16_t* expert_y, const floa
 }
 void moe_combine_add_slots_f16(uint16_t* out, const uint16_t* expert_y, const float* weight, const int* rk, int n_used, int hidden, int n_list, cudaStream_t stream) {
   b200_detail::note(sgr_moe_combine_add_slots_f16(out, expert_y, weight, rk, n_used, hidden, n_list, stream));
+}
+void gemv_q6_k_q8(const void* w_q6, const q4k::BlockQ8K* x_q8, float* y, int n_rows, int k, cudaStream_t stream) {
+  b200_detail::note(sgr_gemv_q6_k_q8(w_q6, x_q8, y, n_rows, k, stream));
+}
+void gemv_q6_k_q8_smx(const void* w_q6, const q4k::BlockQ8K* x_q8, float* y, int n_rows, int k, cudaStream_t stream) {
+  b200_detail::note(sgr_gemv_q6_k_q8_smx(w_q6, x_q8, y, n_rows, k, stream));
+}
+void topk_select_f32_2p(const float* logits, float* seg_v, int* seg_i, int seg_slots, float* out_v, int* out_i, int n, int k, cudaStream_t stream) {
+  b200_detail::note(sgr_topk_select_f32_2p(logits, seg_v, seg_i, seg_slots, out_v, out_i, n, k, stream));
 }
 void rmsnorm_quant_f16(uint16_t* out, const uint16_t* x, const uint16_t* w, q4k::BlockQ8K* xq, int n, float eps, int n_rows, cudaStream_t stream) {
   b200_detail::note(sgr_rmsnorm_quant_f16(out, x, w, xq, n, eps, n_rows, stream));

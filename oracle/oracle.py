@@ -324,6 +324,88 @@ def rmsnorm_quant_f16(oracle, x16: np.ndarray, w16: np.ndarray, eps: float):
     return out, oracle.quantize_q8k_f16(out)
 
 
+Q6K_BYTES = 210
+
+
+def make_q6k(rng: np.random.Generator, rows: int, k: int, d_scale: float = 1e-3) -> np.ndarray:
+    """Seeded raw Q6_K rows [rows][k/256*210]: random 6-bit codes and int8 sub-group scales, fp16 block
+    scale around d_scale. Any byte pattern is a valid block; both sides consume the same bytes."""
+    nb = k // QK_K
+    blk = np.zeros((rows, nb, Q6K_BYTES), dtype=np.uint8)
+    blk[:, :, :192] = rng.integers(0, 256, size=(rows, nb, 192), dtype=np.uint8)
+    blk[:, :, 192:208] = rng.integers(-64, 64, size=(rows, nb, 16)).astype(np.int8).view(np.uint8)
+    d = (d_scale * (0.5 + rng.random((rows, nb)))).astype(np.float16)
+    blk[:, :, 208:210] = d.view(np.uint8).reshape(rows, nb, 2)
+    return blk.reshape(rows, nb * Q6K_BYTES)
+
+
+def dequant_q6k(w6: np.ndarray, k: int) -> np.ndarray:
+    """Raw Q6_K rows -> fp32 [rows][k], the host dequantiser of the reference restated
+    (src/core/weights.cpp:168-209): ql[128] | qh[64] | sc int8[16] | d fp16 per 256 weights; in each
+    128-weight half, weight l + 32*j (l < 32, j < 4) is ((ql[l + 32*(j&1)] >> 4*(j>>1)) & 15) |
+    (((qh[l] >> 2*j) & 3) << 4), minus 32, times d * sc[8*half + l/16 + 2*j]."""
+    rows = w6.shape[0]
+    nb = k // QK_K
+    b = w6.reshape(rows, nb, Q6K_BYTES)
+    ql = b[:, :, :128].reshape(rows, nb, 2, 64).astype(np.int32)
+    qh = b[:, :, 128:192].reshape(rows, nb, 2, 32).astype(np.int32)
+    sc = b[:, :, 192:208].view(np.int8).reshape(rows, nb, 2, 8).astype(np.float32)
+    d = b[:, :, 208:210].copy().view(np.float16).reshape(rows, nb).astype(np.float32)
+    out = np.zeros((rows, nb, 2, 128), dtype=np.float32)
+    for j in range(4):
+        lo = (ql[:, :, :, 32 * (j & 1):32 * (j & 1) + 32] >> (4 * (j >> 1))) & 15
+        hi = (qh >> (2 * j)) & 3
+        q = (lo | (hi << 4)) - 32                                   # [rows][nb][2][32]
+        scale = np.repeat(sc[:, :, :, 2 * j:2 * j + 2], 16, axis=3)  # l/16 picks one of two scales
+        out[:, :, :, 32 * j:32 * j + 32] = d[:, :, None, None] * scale * q
+    return out.reshape(rows, k)
+
+
+def gemv_q6k_q8k(w6: np.ndarray, xq: np.ndarray, k: int) -> np.ndarray:
+    """y[row] = W6[row] . x on Q8_K activations, the arithmetic of the reference's head kernel
+    (src/kernels/cuda/q4_k.cu:1578-1658): per 16-weight sub-group t of a block the exact integer
+    sums isum = sum q*x and xsum = sum x, term = xd * d * sc[t] * (isum - 32 * xsum), terms added in
+    fp32 (here in float64, compared to fp32 rounding)."""
+    rows = w6.shape[0]
+    nb = k // QK_K
+    b = w6.reshape(rows, nb, Q6K_BYTES)
+    ql = b[:, :, :128].reshape(rows, nb, 2, 64).astype(np.int64)
+    qh = b[:, :, 128:192].reshape(rows, nb, 2, 32).astype(np.int64)
+    sc = b[:, :, 192:208].view(np.int8).reshape(rows, nb, 16).astype(np.float64)
+    d = b[:, :, 208:210].copy().view(np.float16).reshape(rows, nb).astype(np.float64)
+    xb = np.ascontiguousarray(xq).view(np.uint8).reshape(nb, Q8K_BYTES)
+    xd = xb[:, :4].copy().view(np.float32).reshape(nb).astype(np.float64)
+    xc = xb[:, 4:260].copy().view(np.int8).reshape(nb, 2, 4, 2, 16).astype(np.int64)   # [blk][half][qslot][is][j]
+    y = np.zeros(rows, dtype=np.float64)
+    for t in range(16):
+        n_half, qslot, is_ = t >> 3, (t & 7) >> 1, t & 1
+        lo = (ql[:, :, n_half, (qslot & 1) * 32 + is_ * 16:(qslot & 1) * 32 + is_ * 16 + 16] >> (4 if qslot & 2 else 0)) & 15
+        hi = (qh[:, :, n_half, is_ * 16:is_ * 16 + 16] >> (2 * qslot)) & 3
+        q = lo | (hi << 4)                                           # [rows][nb][16], 0..63
+        x = xc[:, n_half, qslot, is_, :]                              # [nb][16]
+        isum = (q * x[None]).sum(axis=2)
+        xsum = x.sum(axis=1)
+        y += (xd[None] * d * sc[:, :, t] * (isum - 32 * xsum[None])).sum(axis=1)
+    return y
+
+
+def topk_select(logits: np.ndarray, k: int):
+    """The selection rule of the reference's top-k kernels (src/kernels/cuda/sampling.cu:109-153,
+    173-289): k <= 64 largest values in descending order, equal values by ascending index; values
+    that are not greater than -3.4e38 (and NaN) never qualify, missing entries are (-3.4e38, -1)."""
+    k = min(k, 64)
+    none = np.float32(-3.4e38)
+    v = np.asarray(logits, dtype=np.float32)
+    ok = v > none                                  # False for NaN, -inf and the sentinel
+    idx = np.nonzero(ok)[0]
+    order = idx[np.lexsort((idx, -v[idx].astype(np.float64)))][:k]
+    out_v = np.full(k, none, dtype=np.float32)
+    out_i = np.full(k, -1, dtype=np.int32)
+    out_v[:order.size] = v[order]
+    out_i[:order.size] = order
+    return out_v, out_i
+
+
 class Reference(_Common, _Lib):
     p = "ref_"
 

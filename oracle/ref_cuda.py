@@ -1,6 +1,6 @@
 """TEST INFRASTRUCTURE, not part of the product: the reference's own CUDA launchers
 (oracle/_ref/libsager_ref_cuda.so, built by oracle/Makefile from the reference's
-src/kernels/cuda/{q4_k,mmq,moe,norm_rotary}.cu for sm_100a) on torch tensors, and the
+src/kernels/cuda/{q4_k,mmq,moe,norm_rotary,sampling}.cu for sm_100a) on torch tensors, and the
 launch sequence of the reference's device MoE path written over a launcher set, so
 that the same sequence runs on the reference's kernels and on this library's.
 

@@ -5,7 +5,7 @@
 // include/sager_b200.h, so that a test or the benchmark can load the reference's
 // kernels and this library's side by side with one set of prototypes and run the
 // same launch sequence on either. Built by oracle/Makefile (target refcuda) together
-// with the reference's src/kernels/cuda/{q4_k,mmq,moe,norm_rotary}.cu, compiled
+// with the reference's src/kernels/cuda/{q4_k,mmq,moe,norm_rotary,sampling}.cu, compiled
 // where they lie for sm_100a, into oracle/_ref/libsager_ref_cuda.so. The cuBLAS
 // family (tc_*) is left out. Every forward returns 0: the reference's launchers
 // are void.
@@ -196,6 +196,21 @@ SGR_REF_API int sgr_moe_combine_batched_f16(uint16_t* out, const uint16_t* exper
 
 SGR_REF_API int sgr_moe_combine_add_slots_f16(uint16_t* out, const uint16_t* expert_y, const float* weight, const int* rk, int n_used, int hidden, int n_list, void* stream) {
   sager::cuda::moe_combine_add_slots_f16((uint16_t*)out, (const uint16_t*)expert_y, (const float*)weight, (const int*)rk, (int)n_used, (int)hidden, (int)n_list, (cudaStream_t)stream);
+  return 0;
+}
+
+SGR_REF_API int sgr_gemv_q6_k_q8(const void* w_q6, const void* x_q8, float* y, int n_rows, int k, void* stream) {
+  sager::cuda::gemv_q6_k_q8((const void*)w_q6, (const q4k::BlockQ8K*)x_q8, (float*)y, (int)n_rows, (int)k, (cudaStream_t)stream);
+  return 0;
+}
+
+SGR_REF_API int sgr_gemv_q6_k_q8_smx(const void* w_q6, const void* x_q8, float* y, int n_rows, int k, void* stream) {
+  sager::cuda::gemv_q6_k_q8_smx((const void*)w_q6, (const q4k::BlockQ8K*)x_q8, (float*)y, (int)n_rows, (int)k, (cudaStream_t)stream);
+  return 0;
+}
+
+SGR_REF_API int sgr_topk_select_f32_2p(const float* logits, float* seg_v, int* seg_i, int seg_slots, float* out_v, int* out_i, int n, int k, void* stream) {
+  sager::cuda::topk_select_f32_2p((const float*)logits, (float*)seg_v, (int*)seg_i, (int)seg_slots, (float*)out_v, (int*)out_i, (int)n, (int)k, (cudaStream_t)stream);
   return 0;
 }
 

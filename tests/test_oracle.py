@@ -249,3 +249,25 @@ def test_rmsnorm_quant_restatement(oracle):
     assert np.abs(out.astype(np.float64) - want).max() <= 2.0 ** -10 * np.abs(want).max() * 1.01
     assert np.array_equal(xq, oracle.quantize_q8k_f16(out))
     assert xq.shape == (3, 8 * 276)
+
+
+def test_q6k_restatements_agree_with_each_other():
+    """The integer-dot restatement of the Q6_K head GEMV against the dequantise-then-dot form
+    (src/core/weights.cpp:168-209 of the reference), and the top-k rule on hand-made cases."""
+    from oracle.oracle import dequant_q6k, gemv_q6k_q8k, make_q6k, topk_select
+    from oracle.oracle import Oracle
+    o = Oracle()
+    rng = np.random.default_rng(2)
+    k = 512
+    w6 = make_q6k(rng, 9, k)
+    x = rng.standard_normal(k).astype(np.float32)
+    xq = o.quantize_q8k(x[None])[0]
+    xb = xq.reshape(-1, 276)
+    xdq = (xb[:, :4].copy().view(np.float32) * xb[:, 4:260].copy().view(np.int8).astype(np.float32)).reshape(-1)
+    a = gemv_q6k_q8k(w6, xq, k)
+    b = dequant_q6k(w6, k).astype(np.float64) @ xdq.astype(np.float64)
+    assert np.abs(a - b).max() <= 1e-5 * np.abs(b).max()
+    v, i = topk_select(np.float32([1, 5, 5, np.nan, -np.inf, 2, 5]), 5)
+    assert i.tolist() == [1, 2, 6, 5, 0] and v.tolist() == [5, 5, 5, 2, 1]
+    v, i = topk_select(np.float32([np.nan, -3.4e38]), 3)
+    assert i.tolist() == [-1, -1, -1]
