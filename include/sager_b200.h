@@ -401,6 +401,40 @@ int sgr_ep_set_wait_limit(int polls);
 /* *step += 1 (one thread), in stream order: the end of a step. */
 int sgr_ep_step_advance(unsigned* step, void* stream);
 
+/* ---- host side: model container and expert pool (no GPU involved) ---------------------------
+ * A GGUF v3 reader over a read-only mapping (include/sager/core/gguf.hpp, src/core/gguf.cpp of the
+ * reference: header, typed key/value metadata, tensor directory, data section at the file's
+ * alignment) and the builder of the expert pool that the pointer tables point into
+ * (Weights::load_expert_pool, src/core/weights.cpp:730-862): expert (layer, e) at
+ * (layer * n_expert + e) * sgr_expert_bytes(), its gate, up and down Q4_K matrices back to back,
+ * cut from blk.<L>.ffn_{gate,up,down}_exps; a Q6_K down tensor is dequantised and requantised to
+ * Q4_K row by row with the reference's quantiser (src/kernels/q4_k.cpp:68-174), byte for byte. */
+typedef struct sgr_gguf_tensor_info {
+  int type;                 /* ggml type id: 0 F32, 1 F16, 8 Q8_0, 12 Q4_K, 14 Q6_K, 30 BF16 */
+  int n_dims;
+  long long dims[4];        /* dims[0] is the fastest-varying */
+  long long offset;         /* from the start of the data section */
+  long long nbytes;         /* 0 for a type whose size the reader does not know */
+  long long row_bytes;      /* bytes of one row of dims[0] elements */
+  const void* data;         /* inside the mapping: valid until sgr_gguf_close */
+} sgr_gguf_tensor_info;
+int sgr_gguf_open(const char* path, void** handle);   /* SGR_EARG: not a GGUF file / truncated; SGR_EUNSUPPORTED: not v3 */
+void sgr_gguf_close(void* handle);
+long long sgr_gguf_count(const void* handle, int what);   /* 0 tensors, 1 key/value pairs, 2 alignment, 3 data offset */
+int sgr_gguf_kv_type(const void* handle, const char* key);   /* GGUF value type id, -1 = no such key */
+long long sgr_gguf_kv_int(const void* handle, const char* key, long long dflt);
+double sgr_gguf_kv_double(const void* handle, const char* key, double dflt);
+long long sgr_gguf_kv_str(const void* handle, const char* key, char* buf, long long cap);   /* length, -1 = absent */
+long long sgr_gguf_kv_array(const void* handle, const char* key, int* elem_type, const void** data);   /* count, -1 */
+int sgr_gguf_tensor(const void* handle, const char* name, sgr_gguf_tensor_info* out);
+long long sgr_gguf_tensor_name(const void* handle, long long index, char* buf, long long cap);
+/* q4k::quantize_row (src/kernels/q4_k.cpp:68-174) and dequant_row_q6 (src/core/weights.cpp:171-209) on the host */
+int sgr_quantize_row_q4_k(const float* x, int n, void* out_blocks);
+int sgr_dequant_row_q6_k(const void* src, float* out, int cols);
+size_t sgr_expert_bytes(int hidden, int n_ff);
+int sgr_expert_pool_fill(const void* handle, void* pool, size_t pool_bytes, int first_block, int n_layer,
+                         int n_expert, int hidden, int n_ff, int n_threads);
+
 /* No counterpart in the reference. sgr_moe_layer_decode for callers that cannot
  * allocate device memory - an engine whose whole VRAM budget was handed out at
  * start-up (KV cache, expert slab) and that treats any later cudaMalloc as a bug,

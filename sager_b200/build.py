@@ -35,7 +35,8 @@ def nvcc_path() -> str:
 
 
 def sources():
-    return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+    """CUDA sources and the host-only C++ sources (compiled by the same nvcc as host code)."""
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cpp")))
 
 
 def headers():
@@ -44,7 +45,7 @@ def headers():
 
 
 def _obj(src):
-    return os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
+    return os.path.join(OBJ, os.path.splitext(os.path.basename(src))[0] + ".o")
 
 
 def needs_build() -> bool:
@@ -67,7 +68,12 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         if not force and not ptxas_info and os.path.exists(obj) and \
                 os.path.getmtime(obj) > max(hdr_t, os.path.getmtime(src)):
             return src, 0, ""
-        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + inc + ["-c", "-o", obj, src]
+        flags = list(NVCC_FLAGS)
+        if src.endswith(".cpp"):
+            # host arithmetic that must reproduce the reference's bytes: hardware FMA for the fused
+            # operations the source spells out, and no other contraction
+            flags[flags.index("-fPIC,-fvisibility=hidden")] = "-fPIC,-fvisibility=hidden,-mfma,-ffp-contract=off"
+        cmd = [nvcc] + flags + (["-Xptxas", "-v"] if ptxas_info else []) + inc + ["-c", "-o", obj, src]
         if verbose:
             print(" ".join(cmd))
         res = subprocess.run(cmd, capture_output=True, text=True)

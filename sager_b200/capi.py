@@ -20,7 +20,7 @@ LIB_PATH = os.path.join(HERE, "libsager_b200.so")
 ERRORS = {1: "SGR_EARG", 2: "SGR_EALIGN", 3: "SGR_EUNSUPPORTED", 4: "SGR_ELAUNCH", 5: "SGR_EGEOMETRY",
           6: "SGR_ESTATICLIMIT"}
 
-_SCALARS = {"int": C.c_int, "float": C.c_float, "long long": C.c_longlong, "size_t": C.c_size_t,
+_SCALARS = {"int": C.c_int, "float": C.c_float, "double": C.c_double, "long long": C.c_longlong, "size_t": C.c_size_t,
             "unsigned long long": C.c_ulonglong}
 
 
@@ -35,7 +35,7 @@ def parse_header(path: str = HEADER):
     text = open(path).read()
     text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
     protos = {}
-    for m in re.finditer(r"\b(int|long long|void\s*\*|void|size_t)\s*(sgr_\w+)\s*\(([^)]*)\)\s*;", text):
+    for m in re.finditer(r"\b(int|long long|double|void\s*\*|void|size_t)\s*(sgr_\w+)\s*\(([^)]*)\)\s*;", text):
         ret, name, args = "".join(m.group(1).split()), m.group(2), m.group(3).strip()
         argtypes = []
         if args and args != "void":
@@ -46,7 +46,8 @@ def parse_header(path: str = HEADER):
                 else:
                     base = a.rsplit(" ", 1)[0].replace("const ", "").strip()
                     argtypes.append(_SCALARS[base])
-        protos[name] = ({"int": C.c_int, "longlong": C.c_longlong, "size_t": C.c_size_t, "void": None, "void*": C.c_void_p}[ret], argtypes)
+        protos[name] = ({"int": C.c_int, "longlong": C.c_longlong, "double": C.c_double, "size_t": C.c_size_t, "void": None,
+                        "void*": C.c_void_p}[ret], argtypes)
     return protos
 
 
