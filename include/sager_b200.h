@@ -435,6 +435,31 @@ size_t sgr_expert_bytes(int hidden, int n_ff);
 int sgr_expert_pool_fill(const void* handle, void* pool, size_t pool_bytes, int first_block, int n_layer,
                          int n_expert, int hidden, int n_ff, int n_threads);
 
+/* ---- residency: where the experts live on the device, and the tables the kernels read --------
+ * HotTier::rebuild (src/core/layer.cpp:21-109), the arena half of ExpertPump
+ * (src/core/expert_pump.cpp:130-216) and Session::build_decode_table
+ * (src/core/session.cpp:3569-3627) behind one handle. All memory is the caller's: the host pool
+ * (expert (l, e) at (l * E + e) * sgr_expert_bytes), a device slab of slab_experts experts, a device
+ * arena of arena_slots experts, the device table of 3 * L * E pointers laid out [3][L][E] - the
+ * table sgr_moe_layer / sgr_moe_prefill take with tab_stride = L * E. With host_only != 0 the
+ * "device" pointers are host memory and no CUDA call is made (the policy can be tested without a GPU).
+ * Single producer: one thread drives a handle, as the session thread does in the reference. */
+int sgr_residency_create(int n_layers, int n_experts, int hidden, int n_ff, long long slab_experts,
+                         int arena_slots, void** out);
+void sgr_residency_destroy(void* handle);
+int sgr_residency_bind(void* handle, const void* host_pool, void* dev_slab, void* dev_arena, void* dev_table,
+                       void* copy_stream, int host_only);
+int sgr_residency_set_resident(void* handle, int layer, int expert, int on);
+int sgr_residency_rebuild(void* handle, void* stream, int* resident);
+/* arena slot (>= 0), -1 = no slot can be had right now: fall back for this expert, -2 = in the slab */
+int sgr_residency_submit(void* handle, int layer, int expert, unsigned long long step);
+int sgr_residency_wait(void* handle, int slot, void* stream);
+int sgr_residency_clear_arena(void* handle);
+int sgr_residency_build_decode_table(void* handle, void* stream, int* total_absent);
+long long sgr_residency_stat(const void* handle, int what);
+int sgr_residency_where(const void* handle, int layer, int expert);
+const void* const* sgr_residency_host_table(const void* handle, int which);
+
 /* No counterpart in the reference. sgr_moe_layer_decode for callers that cannot
  * allocate device memory - an engine whose whole VRAM budget was handed out at
  * start-up (KV cache, expert slab) and that treats any later cudaMalloc as a bug,

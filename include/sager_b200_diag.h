@@ -22,6 +22,11 @@ int sgr_tc_set_operand_layout(int layout);
 long long sgr_moe_layer_workspace_offset(int n_max, int hidden, int n_ff, int n_expert, int n_used,
                                          int which);
 
+/* Residency handle in host-only mode: mark an arena slot as "its copy is still in flight" (what an
+ * unfinished event says on the device), so that the rule "an in-flight slot is never evicted" can be
+ * exercised without a GPU. */
+int sgr_residency_test_set_inflight(void* handle, int slot, int on);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,7 +35,7 @@ def parse_header(path: str = HEADER):
     text = open(path).read()
     text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
     protos = {}
-    for m in re.finditer(r"\b(int|long long|double|void\s*\*|void|size_t)\s*(sgr_\w+)\s*\(([^)]*)\)\s*;", text):
+    for m in re.finditer(r"\b(const void\* const\*|int|long long|double|void\s*\*|void|size_t)\s*(sgr_\w+)\s*\(([^)]*)\)\s*;", text):
         ret, name, args = "".join(m.group(1).split()), m.group(2), m.group(3).strip()
         argtypes = []
         if args and args != "void":
@@ -47,7 +47,7 @@ def parse_header(path: str = HEADER):
                     base = a.rsplit(" ", 1)[0].replace("const ", "").strip()
                     argtypes.append(_SCALARS[base])
         protos[name] = ({"int": C.c_int, "longlong": C.c_longlong, "double": C.c_double, "size_t": C.c_size_t, "void": None,
-                        "void*": C.c_void_p}[ret], argtypes)
+                        "void*": C.c_void_p, "constvoid*const*": C.c_void_p}[ret], argtypes)
     return protos
 
 
