@@ -273,6 +273,21 @@ typedef struct sgr_moe_layer {
    * The reference's decode table is [3][Lm][E] (src/core/session.cpp:3596-3598): pass
    * w_tab = table + layer * E and tab_stride = Lm * E to use it in place. */
   long long tab_stride;
+  /* Expert parallelism with both exchanges done by the layer's own kernels over peer memory (all
+   * NULL / 0: off). ep_flags[p] is this rank's address of an arrival word of rank p, set to
+   * *ep_step * ep_mul + ep_add (st.release.sys, after a system-scope fence) once the data are there.
+   *   home side (stages 1 | 8 with xq_out = the record block of ep_rec_bytes per row): after the
+   *     selection the records are stored into ep_dst[p] (this rank's slot in rank p's receive
+   *     buffer) for every p < ep_world, then the owners' words are set;
+   *   owner side (routing_given): row t of the result is stored to
+   *     ep_out[t / ep_home_rows] + (t % ep_home_rows) * hidden (this rank's slot in the home rank's
+   *     return buffer) instead of out_f32, then the home ranks' words are set.
+   * Plain stores to peer memory only: no multicast, no library kernel touches a peer's memory. */
+  void* const* ep_dst;
+  unsigned* const* ep_flags;
+  float* const* ep_out;
+  const unsigned* ep_step;
+  int ep_world, ep_rec_bytes, ep_home_rows, ep_mul, ep_add;
 } sgr_moe_layer;
 
 size_t sgr_moe_layer_workspace_bytes(int n_max, int hidden, int n_ff, int n_expert, int n_used);

@@ -104,6 +104,9 @@ class MoeLayerArgs(C.Structure):
         ("wait_count", C.c_int), ("wait_mul", C.c_int), ("wait_add", C.c_int),
         ("xq_padded", C.c_int),
         ("tab_stride", C.c_longlong),
+        ("ep_dst", C.c_void_p), ("ep_flags", C.c_void_p), ("ep_out", C.c_void_p), ("ep_step", C.c_void_p),
+        ("ep_world", C.c_int), ("ep_rec_bytes", C.c_int), ("ep_home_rows", C.c_int), ("ep_mul", C.c_int),
+        ("ep_add", C.c_int),
     ]
 
 

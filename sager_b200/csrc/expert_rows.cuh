@@ -670,6 +670,22 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     combine_rows(L, c * kCombineRows, min(kCombineRows, L.H - c * kCombineRows), tg * 16, min(L.n, tg * 16 + 16),
                  tid, kConsumers);
   }
+  if (L.ep_out != nullptr) {
+    // Owner side of an expert-parallel layer: the rows went straight into the home ranks' buffers;
+    // the last CTA to finish tells the home ranks.
+    __threadfence_system();
+    rs_consumers_sync();
+    if (tid == 0) flag[1] = atom_add_acq_rel(&L.cnt[11], 1u) == gridDim.x - 1 ? 1 : 0;
+    rs_consumers_sync();
+    if (flag[1]) {
+      if (tid == 0) L.cnt[11] = 0u;
+      __threadfence_system();
+      if (tid < L.ep_world) {
+        const unsigned v = *L.ep_step * L.ep_mul + L.ep_add;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(L.ep_flags[tid]), "r"(v) : "memory");
+      }
+    }
+  }
 }
 
 }  // namespace rs

@@ -110,6 +110,17 @@ struct LayerDev {
   const unsigned* wait_step;
   int wait_count, wait_mul, wait_add;
   unsigned wait_limit;          // polls before a wait for arrival words gives up
+  // expert parallelism, exchanges done by the layer's own kernels over peer memory:
+  //   home side (route without plan): the records just written (rows of ep_rec bytes at ep_src) go to
+  //   slot ep_dst[p] of every peer p < ep_world, then the peers' arrival words ep_flags[p] are set;
+  //   owner side: row t of the result goes to ep_out[t / ep_home] + (t % ep_home) * H (the home rank's
+  //   buffer) instead of out_f32, then the home ranks' arrival words ep_flags[p] are set.
+  void* const* ep_dst;
+  unsigned* const* ep_flags;
+  float* const* ep_out;
+  const unsigned char* ep_src;
+  const unsigned* ep_step;
+  int ep_world, ep_rec, ep_home, ep_mul, ep_add;
   unsigned char* tmaps;   // [grid][kTmapSlots][3][128] row-streaming kernel: patched TMA descriptors
   // TMA descriptors (placeholder address) of a gate / up matrix and of a down matrix. Only ever
   // read with constant indices: a dynamic index would make every thread keep a local-memory
@@ -431,7 +442,34 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
                        L.w + static_cast<size_t>(tok0 + t) * L.rstride, L.shared_w, true, lane);
     __syncwarp();
   }
-  if (L.skip_plan) return;
+  if (L.skip_plan) {
+    if (L.ep_dst == nullptr) return;
+    // Home side of an expert-parallel layer: this tile's records (quantised rows written by every
+    // CTA of the tile, ids and weights written above) go straight into every owner's receive slot
+    // with 16-byte peer stores; the last tile to finish sets the owners' arrival words.
+    __syncthreads();
+    {
+      const size_t tile_off = static_cast<size_t>(tok0) * L.ep_rec;
+      const int n16 = nt * L.ep_rec / 16;
+      const uint4* src = reinterpret_cast<const uint4*>(L.ep_src + tile_off);
+      for (int p = 0; p < L.ep_world; ++p) {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned char*>(L.ep_dst[p]) + tile_off);
+        for (int i = tid; i < n16; i += blockDim.x) dst[i] = __ldcg(src + i);
+      }
+    }
+    __threadfence_system();                   // this thread's peer stores before the count below, at every GPU
+    __syncthreads();
+    if (tid == 0) last_sh = atom_add_acq_rel(&L.cnt[8], 1u) == gridDim.y - 1 ? 1 : 0;
+    __syncthreads();
+    if (!last_sh) return;
+    if (tid == 0) L.cnt[8] = 0u;
+    __threadfence_system();
+    if (tid < L.ep_world) {
+      const unsigned v = *L.ep_step * L.ep_mul + L.ep_add;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(L.ep_flags[tid]), "r"(v) : "memory");
+    }
+    return;
+  }
   // last token tile plans
   __syncthreads();
   if (tid == 0) last_sh = atom_add_acq_rel(&L.cnt[8], 1u) == gridDim.y - 1 ? 1 : 0;
@@ -681,7 +719,8 @@ __device__ __forceinline__ void combine_rows(const LayerDev& L, int row0, int nr
     }
     if (has_shared && tk >= L.sh_lo && tk < L.sh_hi)
       acc += __ldcg(wr + L.K) * __ldcg(L.ybuf + static_cast<size_t>(L.n_max * L.K + tk) * L.H + r);
-    if (L.out_f32 != nullptr) L.out_f32[o] = acc;
+    if (L.ep_out != nullptr) L.ep_out[tk / L.ep_home][static_cast<size_t>(tk % L.ep_home) * L.H + r] = acc;
+    else if (L.out_f32 != nullptr) L.out_f32[o] = acc;
     if (L.x_f16 != nullptr && L.add_residual) L.x_f16[o] = f2h(acc);
   }
 }
@@ -1139,7 +1178,7 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
       a->n_used <= 0 || a->n_used > a->n_expert || a->n_max < a->n || a->n_max > kMaxRows)
     return kErrGeometry;
   if (a->n_expert > 1024 || a->hidden > 8192 || a->n_ff > 8192) return kErrUnsupported;
-  if (!a->w_tab || !a->route_idx || !a->route_w || !a->workspace || (!a->x_f16 && !a->out_f32))
+  if (!a->w_tab || !a->route_idx || !a->route_w || !a->workspace || (!a->x_f16 && !a->out_f32 && !a->ep_out))
     return kErrArg;
   if (!a->routing_given && (!a->xn || !a->router_w)) return kErrArg;
   if (a->routing_given && !a->xq_in && !a->xn) return kErrArg;
@@ -1210,6 +1249,26 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   L.wait_count = a->wait_count; L.wait_mul = a->wait_mul; L.wait_add = a->wait_add;
   L.wait_limit = g_wait_limit.load(std::memory_order_relaxed);
   if (L.wait_flags != nullptr && (!a->routing_given || !L.wait_step || L.wait_count < 0 || L.wait_count > 128)) return kErrArg;
+  if (a->ep_dst != nullptr || a->ep_out != nullptr) {
+    if (!a->ep_flags || !a->ep_step || a->ep_world <= 0 || a->ep_world > 64) return kErrArg;
+    if (a->ep_dst != nullptr) {              // home side: route without plan, records at xq_out
+      if ((stages & 15) != 9 || a->xq_out == nullptr || a->ep_rec_bytes <= 0 || (a->ep_rec_bytes & 15) ||
+          (reinterpret_cast<uintptr_t>(a->xq_out) & 15u))
+        return kErrArg;
+      L.ep_dst = a->ep_dst;
+      L.ep_src = static_cast<const unsigned char*>(a->xq_out);
+      L.ep_rec = a->ep_rec_bytes;
+    } else {                                 // owner side
+      if (!a->routing_given || a->ep_home_rows <= 0 || !a->no_residual) return kErrArg;
+      L.ep_out = a->ep_out;
+      L.ep_home = a->ep_home_rows;
+    }
+    L.ep_flags = a->ep_flags;
+    L.ep_step = a->ep_step;
+    L.ep_world = a->ep_world;
+    L.ep_mul = a->ep_mul;
+    L.ep_add = a->ep_add;
+  }
   // Which expert kernel: the row-streaming one pays once a layer has enough tiles to
   // give every SM whole groups (bit 4 of `stages` forces it, bit 5 forces the item
   // kernel; both stages of a split call must be given the same bits).
@@ -1217,6 +1276,7 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   const bool use_rows = (stages & 32) ? false
                         : ((stages & 16) ? true
                                          : a->n >= kRowsKernelMinRows && a->workspace_bytes >= lay.total);
+  if (a->ep_out != nullptr && !use_rows) return kErrUnsupported;   // the peer stores live in the row-streaming kernel's tail
   L.tok_tile = use_rows ? rs::kTok : kTokTile;
   if (a->workspace_bytes < (use_rows ? lay.total : lay.items_total)) return kErrArg;
   if (L.xq_padded) {
@@ -1252,6 +1312,7 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   // persistent launch (token_layer.cuh). Bit 6 of `stages` keeps the two-launch path.
   if ((stages & 7) == 7 && !(stages & (8 | 16 | 32 | 64)) && a->n <= kTokenKernelMaxRows && a->n * a->n_used <= 32 &&
       !a->routing_given && a->xq_in == nullptr && a->xq_out == nullptr && a->wait_flags == nullptr &&
+      a->ep_dst == nullptr && a->ep_out == nullptr &&
       L.e_lo == 0 && L.e_hi == L.E && L.sh_lo == 0 && L.sh_hi == L.n && L.nbh <= 16 && L.nbf <= 16 &&
       a->workspace_bytes >= lay.items_total) {
     const tk::Geom g = tk::geom(tk::kMaxTok, L.H, L.FF, L.E, L.grid);

@@ -167,9 +167,13 @@ class EpStack:
         # records carry the Q8 rows in 288-byte blocks when the owner runs the row-streaming kernel,
         # which then reads them in place
         self.padded = device != "cpu" and tokens >= 16
-        # peer-memory exchange when the ranks can map each other's memory, NCCL all-to-alls otherwise
+        # peer-memory exchange when the ranks can map each other's memory, NCCL all-to-alls otherwise.
+        # SGR_EP_EXCHANGE: "fused" (default: the layer's kernels store into peer memory themselves),
+        # "push" (separate copy kernels between the layer's launches), "nccl" (two all-to-alls per layer)
+        mode = os.environ.get("SGR_EP_EXCHANGE", "fused")
+        self.fused = mode == "fused"
         if peer is None:
-            peer = world > 1 and device != "cpu" and os.environ.get("SGR_EP_EXCHANGE", "peer") == "peer"
+            peer = world > 1 and device != "cpu" and mode in ("fused", "push", "peer")
         self.peer = None
         if peer:
             try:
@@ -197,7 +201,8 @@ class EpStack:
         self.x0 = x0[h0:h0 + self.n_home].contiguous()
         self.x = self.x0.clone()
         self.graph = None
-        self.launches_per_step = (6 if self.peer is not None else 4) * len(layers)   # route, (push,) plan, experts, (push,) reduce
+        # route, (push,) plan, experts, (push,) reduce
+        self.launches_per_step = ((4 if self.fused else 6) if self.peer is not None else 4) * len(layers)
         self.n_layers = len(layers)
 
     def _ptr(self, t, off=0):
@@ -239,9 +244,48 @@ class EpStack:
         L.call("sgr_ep_reduce_add_f16_wait", self._ptr(self.x), self._ptr(px.back), self.world, n, n,
                self._ptr(px.flag_r), self._ptr(px.step), mul, add, sp)
 
+    def issue_layer_fused(self, li):
+        """One layer with both exchanges done by the layer's own kernels: the route kernel stores the
+        records into the owners' receive slots, the expert kernel stores its rows into the home
+        ranks' return slots. Four launches: route, plan (waits for the records), experts, home
+        reduction (waits for the rows)."""
+        from .capi import lib
+        from .ops import stream_ptr
+        w, px = self.layers[li], self.peer
+        L, sp = lib(), stream_ptr()
+        mul, add = self.n_layers, li + 1               # arrival value of this layer in this step
+        a = self.home.args(self.n_home, self.inputs[li], w.router, self.tables[li], None, x_f16=self.x,
+                           bias=None if self.biases is None else self.biases[li])
+        a.xq_out = self._ptr(px.send)
+        a.xq_stride = px.rec
+        a.route_idx = self._ptr(px.send, px.idx_off)
+        a.route_w = self._ptr(px.send, px.w_off)
+        a.route_stride = px.rec // 4
+        a.xq_padded = int(self.padded)
+        a.ep_dst, a.ep_flags, a.ep_step = self._ptr(px.dst_recv), self._ptr(px.dst_flag_d), self._ptr(px.step)
+        a.ep_world, a.ep_rec_bytes, a.ep_mul, a.ep_add = self.world, px.rec, mul, add
+        L.call("sgr_moe_layer_decode_stages", C.byref(a), 1 | 8, sp)
+        h0 = self.rank * self.n_home
+        b = self.owner.args(self.tokens, None, None, self.tables[li], w.shared_ptrs(), out_f32=None,
+                            xq_in=px.recv, routing_given=True, no_residual=True, shared_lo=h0,
+                            shared_hi=h0 + self.n_home)
+        b.xq_stride = px.rec
+        b.route_idx = self._ptr(px.recv, px.idx_off)
+        b.route_w = self._ptr(px.recv, px.w_off)
+        b.route_stride = px.rec // 4
+        b.wait_flags, b.wait_step = self._ptr(px.flag_d), self._ptr(px.step)
+        b.wait_count, b.wait_mul, b.wait_add = self.world, mul, add
+        b.xq_padded = int(self.padded)
+        b.ep_out, b.ep_flags, b.ep_step = self._ptr(px.dst_back), self._ptr(px.dst_flag_r), self._ptr(px.step)
+        b.ep_world, b.ep_home_rows, b.ep_mul, b.ep_add = self.world, self.n_home, mul, add
+        L.call("sgr_moe_layer_decode_stages", C.byref(b), 7, sp)
+        n = self.n_home * w.hidden
+        L.call("sgr_ep_reduce_add_f16_wait", self._ptr(self.x), self._ptr(px.back), self.world, n, n,
+               self._ptr(px.flag_r), self._ptr(px.step), mul, add, sp)
+
     def issue_layer(self, li):
         if self.peer is not None:
-            return self.issue_layer_peer(li)
+            return self.issue_layer_fused(li) if self.fused else self.issue_layer_peer(li)
         from .capi import lib
         from .ops import stream_ptr
         w, ex = self.layers[li], self.ex
@@ -393,8 +437,10 @@ def run_ep_bench(args, rank, world, device):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8 dots, fp32 accumulate", "data": "synthetic",
         "config": dict(bench.workload_config(world), layers=layers_n, tokens=tokens, zipf_alpha=alpha,
-                       exchange=("records and partial sums stored into peer memory over NVLink by the library's "
-                                 "own kernels, arrival words, captured in the step graph") if st.peer is not None
+                       exchange=(("records and partial sums stored into peer memory over NVLink by the layer's own "
+                                  "kernels (route and expert kernel), arrival words, 4 launches per layer") if st.fused else
+                                 ("records and partial sums stored into peer memory over NVLink by copy kernels "
+                                  "between the layer's launches, arrival words, 6 launches per layer")) if st.peer is not None
                        else "2 NCCL all-to-alls per layer, fixed capacity, captured in the step graph"),
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": int(h_in.numel() * 2) * world,

@@ -476,3 +476,50 @@ def test_token_kernel_agrees_with_the_two_launch_path(full_w):
             assert torch.equal(res[0][3][:n], res[1][3][:n])
             assert rel(res[0][0].cpu().numpy(), res[1][0].cpu().numpy()) < 1e-5
     assert lib().raw("sgr_status")(0) == 0
+
+
+@pytest.mark.parametrize("tokens", [8, 64])
+def test_fused_exchange_entry_points_with_one_rank(full_w, tokens):
+    """The expert-parallel layer with the exchanges done by its own kernels, this device being its
+    own only peer: the route kernel stores the records into the 'owner's' receive slot and sets the
+    arrival word, the owner call waits for it and stores its rows into the 'home rank's' return
+    slot, the home reduction waits for that word. Must reproduce the single call."""
+    import ctypes as C
+    from sager_b200.ep import record_layout
+    from sager_b200.ops import stream_ptr
+    w, k, H = full_w, 8, full_w.hidden
+    x16 = synth.normal_fp16((tokens, H), 191, DEV)
+    _, x_full, _ = run_layer(w, tokens, k, x16, n_max=64)
+    rec, idx_off, w_off = record_layout(H, k, True)
+    send = torch.zeros(tokens, rec, dtype=torch.uint8, device=DEV)
+    recv = torch.zeros(tokens, rec, dtype=torch.uint8, device=DEV)
+    back = torch.zeros(1, tokens, H, dtype=torch.float32, device=DEV)
+    flags = torch.zeros(2, dtype=torch.int32, device=DEV)
+    step = torch.full((1,), 5, dtype=torch.int32, device=DEV)
+    p64 = lambda *addr: torch.tensor(list(addr), dtype=torch.int64, device=DEV)
+    dst_recv, dst_back = p64(recv.data_ptr()), p64(back.data_ptr())
+    fl_d, fl_r = p64(flags.data_ptr()), p64(flags.data_ptr() + 4)
+    ptr = lambda t, off=0: C.c_void_p(t.data_ptr() + off)
+    L, sp = lib(), stream_ptr()
+    home = MoeLayerRunner(tokens, H, w.n_ff, w.n_expert, k, DEV)
+    x = x16.clone()
+    a = home.args(tokens, x16, w.router, w.table(), None, x_f16=x)
+    a.xq_out, a.xq_stride, a.xq_padded = ptr(send), rec, 1
+    a.route_idx, a.route_w, a.route_stride = ptr(send, idx_off), ptr(send, w_off), rec // 4
+    a.ep_dst, a.ep_flags, a.ep_step = ptr(dst_recv), ptr(fl_d), ptr(step)
+    a.ep_world, a.ep_rec_bytes, a.ep_mul, a.ep_add = 1, rec, 3, 2
+    L.call("sgr_moe_layer_decode_stages", C.byref(a), 1 | 8, sp)
+    owner = MoeLayerRunner(64, H, w.n_ff, w.n_expert, k, DEV)
+    b = owner.args(tokens, None, None, w.table(), w.shared_ptrs(), xq_in=recv, routing_given=True, no_residual=True)
+    b.xq_stride, b.route_stride, b.xq_padded = rec, rec // 4, 1
+    b.route_idx, b.route_w = ptr(recv, idx_off), ptr(recv, w_off)
+    b.wait_flags, b.wait_step, b.wait_count, b.wait_mul, b.wait_add = ptr(flags), ptr(step), 1, 3, 2
+    b.ep_out, b.ep_flags, b.ep_step = ptr(dst_back), ptr(fl_r), ptr(step)
+    b.ep_world, b.ep_home_rows, b.ep_mul, b.ep_add = 1, tokens, 3, 2
+    L.call("sgr_moe_layer_decode_stages", C.byref(b), 7 | 16, sp)
+    L.call("sgr_ep_reduce_add_f16_wait", ptr(x), ptr(back), 1, tokens * H, tokens * H, ptr(flags, 4), ptr(step), 3, 2, sp)
+    torch.cuda.synchronize()
+    assert flags.tolist() == [17, 17]
+    assert torch.equal(recv, send)
+    assert rel(x.float().cpu().numpy(), x_full.float().cpu().numpy()) <= 2.0 ** -10      # fp16 store after another add order
+    assert lib().raw("sgr_status")(0) == 0
