@@ -457,16 +457,18 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
         for (int i = tid; i < n16; i += blockDim.x) dst[i] = __ldcg(src + i);
       }
     }
-    __threadfence_system();                   // this thread's peer stores before the count below, at every GPU
+    // Ordering: the CTA barrier makes every thread's peer stores observed by thread 0; its
+    // acquire-release count chains the tiles' CTAs; the release stores of the arrival words (system
+    // scope, by the last CTA) are cumulative over all of that. No separate system fence: each one
+    // waits for the outstanding NVLink stores to be acknowledged (about 5 us measured).
     __syncthreads();
-    if (tid == 0) last_sh = atom_add_acq_rel(&L.cnt[8], 1u) == gridDim.y - 1 ? 1 : 0;
-    __syncthreads();
-    if (!last_sh) return;
-    if (tid == 0) L.cnt[8] = 0u;
-    __threadfence_system();
-    if (tid < L.ep_world) {
-      const unsigned v = *L.ep_step * L.ep_mul + L.ep_add;
-      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(L.ep_flags[tid]), "r"(v) : "memory");
+    if (tid == 0) {
+      if (atom_add_acq_rel(&L.cnt[8], 1u) == gridDim.y - 1) {     // every tile's records are on their way
+        L.cnt[8] = 0u;
+        const unsigned v = *L.ep_step * L.ep_mul + L.ep_add;
+        for (int p = 0; p < L.ep_world; ++p)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(L.ep_flags[p]), "r"(v) : "memory");
+      }
     }
     return;
   }
@@ -1045,18 +1047,15 @@ __global__ void ep_push_kernel(const unsigned char* __restrict__ src, size_t src
   const size_t per = (n16 + gridDim.x - 1) / gridDim.x;
   const size_t lo = per * blockIdx.x, hi = lo + per < n16 ? lo + per : n16;
   for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) d[i] = s[i];
-  __threadfence_system();                       // this thread's stores before the count below, at every GPU
+  // the CTA barrier makes the stores observed by thread 0, its acquire-release count chains the CTAs,
+  // and the last CTA's release stores of the arrival words (system scope) are cumulative over all of it
   __syncthreads();
-  __shared__ int last;
-  if (threadIdx.x == 0) last = atomicAdd(scratch, 1u) == gridDim.x * gridDim.y - 1 ? 1 : 0;
-  __syncthreads();
-  if (!last) return;
-  __threadfence_system();
-  if (threadIdx.x == 0) *scratch = 0u;
-  if (static_cast<int>(threadIdx.x) < world) {
-    const unsigned v = *step * mul + add;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags[threadIdx.x]), "r"(v) : "memory");
-  }
+  if (threadIdx.x != 0) return;
+  if (atom_add_acq_rel(scratch, 1u) != gridDim.x * gridDim.y - 1) return;
+  *scratch = 0u;
+  const unsigned v = *step * mul + add;
+  for (int p2 = 0; p2 < world; ++p2)
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags[p2]), "r"(v) : "memory");
 }
 
 __global__ void ep_step_kernel(unsigned* step) {
