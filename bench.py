@@ -538,6 +538,7 @@ def gemv_measure(args, device, shapes=None, sampler=None):
                 row["reference_cuda_us"] = ref_us
                 row["reference_cuda_gbs"] = wbytes / ref_us / 1e3
             rows_out.append(row)
+    q6 = None if args.shape else q6_head_measure(args, device, ops, ref, peak)
     clocks = sampler.stop() if own_sampler else None
     head = max((r for r in rows_out if r["batch"] == 1), key=lambda r: r["rows"] * r["k"])
     line = {
@@ -552,9 +553,66 @@ def gemv_measure(args, device, shapes=None, sampler=None):
                      "traffic": None},
         "sweep": rows_out,
     }
+    if q6 is not None:
+        line["q6k_head"] = q6
     if lib().raw("sgr_status")(0) != 0:
         line["device_status"] = "a bounded device-side wait gave up"
     return line
+
+
+def q6_head_measure(args, device, ops, ref, peak):
+    """The LM head as the checkpoint stores it (Q6_K, 210-byte blocks) and the two-phase top-k over
+    its logits: 151936 x 2048 = 255 MB per launch, twice the L2, two weight copies alternating.
+    Random 6-bit codes and sub-block scales with a small block scale; time does not depend on
+    the values."""
+    import torch
+    rows, k, topk = 151936, 2048, 40
+    nblk = rows * (k // 256)
+    g = torch.Generator(device=device).manual_seed(SEED + 6)
+    w = torch.randint(0, 256, (2, nblk, 210), dtype=torch.uint8, device=device, generator=g)
+    w[:, :, 208:210] = torch.tensor([0.01], dtype=torch.float16).view(torch.uint8).to(device)
+    from sager_b200 import synth
+    x = synth.normal_fp16((1, k), SEED + 66, device)
+    xq = torch.empty(1, k // 256 * 276, dtype=torch.uint8, device=device)
+    ops.quantize_q8_k(x, xq, k)
+    y = torch.zeros(rows, dtype=torch.float32, device=device)
+    slots = (rows + 2047) // 2048 * topk
+    seg_v = torch.zeros(slots, dtype=torch.float32, device=device)
+    seg_i = torch.zeros(slots, dtype=torch.int32, device=device)
+    out_v = torch.zeros(64, dtype=torch.float32, device=device)
+    out_i = torch.zeros(64, dtype=torch.int32, device=device)
+
+    def timed(fn, per_replay):
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (args.steps * per_replay)
+
+    def head(o):
+        return lambda: [o.gemv_q6_k_q8(w[c], xq, y, rows, k) for c in range(2)]
+
+    def select(o):
+        return lambda: [o.topk_select_f32_2p(y, seg_v, seg_i, slots, out_v, out_i, rows, topk) for _ in range(8)]
+
+    wbytes = nblk * 210
+    us = timed(head(ops), 2)
+    out = {"rows": rows, "k": k, "us": us, "gbs": wbytes / us / 1e3, "frac": wbytes / us / 1e3 / peak,
+           "topk": topk, "topk_us": timed(select(ops), 8)}
+    if ref is not None:
+        out["reference_cuda_us"] = timed(head(ref), 2)
+        out["reference_cuda_topk_us"] = timed(select(ref), 8)
+    return out
 
 
 def run_gemv_bench(args, device):
@@ -567,7 +625,8 @@ def gemv_config_leg(args, device):
     line = gemv_measure(args, device, sampler=False)
     keys = ("rows", "k", "batch", "us", "gbs", "frac", "reference_cuda_us")
     return {"workload": line["config"]["workload"], "lm_head_gbs": line["value"], "lm_head_frac": line["roofline"]["frac"],
-            "sweep": [{k: r[k] for k in keys if k in r} for r in line["sweep"]]}
+            "sweep": [{k: r[k] for k in keys if k in r} for r in line["sweep"]],
+            "q6k_head": line.get("q6k_head")}
 
 
 def run_tc_bench(args, device):
@@ -657,6 +716,9 @@ def main():
     ap.add_argument("--kernel", default=None, choices=["rows", "items", "two_launch"],
                     help="decode: force the row-streaming or the item expert kernel (default: the library's choice)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--chain", action="store_true",
+                    help="decode: every layer's input rows are rmsnorm_quant_f16 of the residual its predecessor "
+                         "wrote (one more launch per layer) instead of pre-drawn matrices")
     ap.add_argument("--shape", default=None, help="gemv workload: only this ROWS,K shape; tc workload: ROWS,K,TOKENS (profiling captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -709,7 +771,7 @@ def main():
     n = TOKENS
     sampler = ClockSampler(local_rank)
     sampler.start()                      # runs across every timed region of this process
-    main_leg = decode_leg(ws, inputs, x0, biases, n, args, device, e2e=True)
+    main_leg = decode_leg(ws, inputs, x0, biases, n, args, device, e2e=True, chain=args.chain)
     ms_step, value, e2e, roofline = main_leg["ms_step"], main_leg["value"], main_leg["e2e"], main_leg["roofline"]
 
     line = {
@@ -739,6 +801,17 @@ def main():
                     "stage_ms_per_step": leg["roofline"]["stage_ms_per_step"]}
             except Exception as exc:
                 cfgs[name] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+        try:
+            # the same step with a true dependency between layers (input rows = RMSNorm of the residual)
+            leg = decode_leg(ws, inputs, x0, biases, n, args, device, e2e=False, chain=True)
+            cfgs["chained"] = {
+                "workload": "the headline step with every layer's input computed from its predecessor's residual "
+                            "by rmsnorm_quant_f16 (3 launches per layer)",
+                "tokens_per_s": leg["value"], "ms_per_step": leg["ms_step"],
+                "distinct_experts_per_layer": leg["uniq_mean"]}
+            del leg
+        except Exception as exc:
+            cfgs["chained"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
         for name, fn in (("gemv", gemv_config_leg), ("prefill", prefill_config_leg)):
             try:
                 cfgs[name] = fn(args, device)
@@ -765,7 +838,7 @@ def main():
     print(json.dumps(line))
 
 
-def decode_leg(ws, inputs, x0, biases, n, args, device, e2e):
+def decode_leg(ws, inputs, x0, biases, n, args, device, e2e, chain=False):
     """One decode measurement over the layer stack with n token rows: graph-replayed steps with
     the inputs resident (value), optionally the same through host buffers (e2e), and each stage of
     all layers back to back (the roofline of the expert kernel)."""
@@ -773,7 +846,8 @@ def decode_leg(ws, inputs, x0, biases, n, args, device, e2e):
     from sager_b200 import synth
     from sager_b200.layer import MoeStack
     layers = len(ws)
-    stack = MoeStack(ws, n, K, device, biases=biases, inputs=inputs, per_layer_ws=True, kernel=args.kernel)
+    stack = MoeStack(ws, n, K, device, biases=biases, inputs=inputs, per_layer_ws=True, kernel=args.kernel,
+                     chain=chain)
     stack.x.copy_(x0[:n])
     stack.capture(n)
 

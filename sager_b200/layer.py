@@ -83,7 +83,7 @@ class MoeStack:
     activations are still there and single stages can be re-launched (timing)."""
 
     def __init__(self, layers, n_max, n_used, device, biases=None, inputs=None,
-                 per_layer_ws=False, kernel=None):
+                 per_layer_ws=False, kernel=None, chain=False):
         self.layers = layers
         self.kernel_bits = KERNEL_BITS[kernel]
         w0 = layers[0]
@@ -103,11 +103,21 @@ class MoeStack:
         self.w = torch.zeros(len(layers), n_max, n_used + 1, dtype=torch.float32, device=device)
         # one persistent launch per layer for up to three rows, else route + experts
         self.launches_per_step = (1 if (kernel is None and n_max <= 3) else 2) * len(layers)
+        # chain: layer l's input rows are RMSNorm(x) computed on the device by rmsnorm_quant_f16 (the
+        # producer of the MoE half's rows in the reference's decode layer, src/core/session.cpp:1020-1032),
+        # so every layer depends on the residual its predecessor wrote
+        self.chain = chain
+        if chain:
+            g = torch.Generator().manual_seed(77)
+            self.norm_w = (1.0 + 0.1 * torch.randn(len(layers), w0.hidden, generator=g)).half().to(device)
+            self.xn = torch.zeros(n_max, w0.hidden, dtype=torch.float16, device=device)
+            self.xq = torch.zeros(n_max, w0.hidden // 256 * 276, dtype=torch.uint8, device=device)
+            self.launches_per_step += len(layers)
 
     def layer_args(self, li, n):
         w = self.layers[li]
         r = self.runners[li % len(self.runners)]
-        xn = self.x if self.inputs is None else self.inputs[li]
+        xn = self.xn if self.chain else self.x if self.inputs is None else self.inputs[li]
         return r, r.args(n, xn, w.router, self.tables[li], w.shared_ptrs(), x_f16=self.x,
                          bias=None if self.biases is None else self.biases[li],
                          route_idx=self.idx[li], route_w=self.w[li])
@@ -115,6 +125,9 @@ class MoeStack:
     def _issue(self, n, stages=7):
         for li in range(len(self.layers)):
             r, a = self.layer_args(li, n)
+            if self.chain and (stages & 1):
+                lib().call("sgr_rmsnorm_quant_f16", _p(self.xn), _p(self.x), _p(self.norm_w[li]), _p(self.xq),
+                           self.layers[0].hidden, 1e-6, n, stream_ptr())
             lib().call("sgr_moe_layer_decode_stages", C.byref(a), stages | self.kernel_bits, stream_ptr())
 
     def step_eager(self, n):
