@@ -16,8 +16,8 @@
 //
 // The weight part of a stage arrives by TMA: two tiled copies per stage (boxes of
 // 144 bytes x 128 rows) through 2-D tensor maps over [rows][row bytes]. The maps
-// are made on the host for a placeholder address; when the weight warp enters a
-// tile it patches the expert's base addresses into shared-memory copies
+// are made on the host for a placeholder address; the weight warp patches a group's
+// descriptors while the group before it streams: the expert's base addresses go into shared-memory copies
 // (tensormap.replace), publishes them to a per-CTA ring of descriptors in global
 // memory (tensormap.cp_fenceproxy) and acquires them before use. (16-byte cp.async
 // copies reach the same HBM rate on their own, but every one of them passes through
@@ -55,12 +55,12 @@ constexpr int kXCodes = kTok * kXqStride;
 constexpr int kXBytes = kXCodes + kTok * 16 + kTok * 16;
 constexpr int kStageBytes = (kWBytes + kXBytes + 127) & ~127;
 constexpr int kHq = 288;                        // padded Q8_K block of h: d | 12 bytes | 256 codes | 8 sums
-constexpr int kHdr = 2048;
+constexpr int kHdr = 4096;
 constexpr size_t kSmem = kHdr + static_cast<size_t>(kStageCount) * kStageBytes;
 constexpr int kGateUpPairs = 128;               // pairs per gate/up group
 constexpr int kDownRows = 256;                  // rows per down group
 constexpr int kCombineRows = 64;
-constexpr int kFullArrivals = 32 + kXThreads;     // weight warp: one arrival per lane; activation warps: copies landed
+constexpr int kFullArrivals = 1 + kXThreads;      // weight warp: one arrival; activation warps: a thread's copies landed
 constexpr int kMapRing = kStageCount + 1;        // descriptor slots per CTA: a slot is patched again only after every
                                                  // stage that could still reference it has been refilled (a tile has at
                                                  // least one stage, and at most kStageCount stages are in flight)
@@ -159,6 +159,17 @@ struct Sched {
 };
 constexpr int kListSlots = 16;
 
+// One entry of a CTA's group list, published by the weight warp one group ahead of its copies,
+// with everything the other roles would otherwise fetch from global memory again.
+struct GEntry {
+  int id;          // global group number, -1 = end of this CTA's list
+  int absent;      // bit 0: the expert's pointers are null; bit 1 (down groups): the tile's h was already published
+                   // when the weight warp looked
+  int4 rc;         // the tile's record: expert, token rows, first h / y row, first entry of grows
+  int rows[kTok];  // gate/up groups: source row of the tile's token slot t in the quantised inputs
+};
+static_assert(sizeof(GEntry) * kListSlots + 2048 <= kHdr, "group list exceeds the header");
+
 // One warp: Q8_K-quantise block `hb` of the fp32 h rows [hrow0, hrow0 + ntok) into the
 // padded rows of L.hq (arithmetic of src/kernels/cpu/q4_avx2.cpp:77-94 in the reference,
 // the same as stage_quantized_f32). Two rows per pass keep two sets of loads in flight.
@@ -240,40 +251,132 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
   sc.n_gu = L.meta[1] * sc.gpt_gu;
   sc.total = sc.n_gu + L.meta[1] * sc.gpt_dn;
   const int rb_h = L.nbh * kW4, rb_f = L.nbf * kW4;
-  volatile int* glist = reinterpret_cast<volatile int*>(smem + 768);           // [kListSlots] this CTA's groups, -1 = end
+  GEntry* glist = reinterpret_cast<GEntry*>(smem + 2048);                       // [kListSlots] this CTA's groups
   volatile unsigned* g_pub = reinterpret_cast<volatile unsigned*>(smem + 144);  // entries of glist published
-  // a follower role's k-th group (bounded wait for the weight warp to publish it)
-  auto follow = [&](int k, bool& ok) {
+  // a follower role's k-th group (bounded wait for the weight warp to publish it); an entry stays
+  // valid for kListSlots further groups, far longer than any role can lag behind the ring
+  auto follow = [&](int k, bool& ok) -> const GEntry* {
     unsigned it = 0;
     if (lane == 0)
       while (*g_pub <= static_cast<unsigned>(k) && ++it < kSpinLimit) __nanosleep(40);
     it = __shfl_sync(0xFFFFFFFFu, it, 0);
     ok = it < kSpinLimit;
     __threadfence_block();
-    return ok ? static_cast<int>(glist[k % kListSlots]) : -1;
+    return glist + k % kListSlots;
   };
 
   if (warp == kConsumerWarps) {
     // ---------------- weight warp ----------------
+    // Streams group k while it prepares group k + 1: the group number was drawn a group earlier, the
+    // tile's record is requested after the first stage of group k has been issued, the expert's
+    // pointers (and the token slots' source rows) after the last one, and the descriptors are
+    // patched once the group's copies are all issued - so none of these global round trips, nor the
+    // descriptor update, sits between two copies of the stream.
     unsigned char* smaps = smem + 1024;                                 // three 128-byte descriptors being patched
+    uint32_t* tmpl = reinterpret_cast<uint32_t*>(smem + 1408);          // the two host-made descriptors
     unsigned char* gmaps = L.tmaps + static_cast<size_t>(blockIdx.x) * kMapRing * 3 * 128;
-    int cur_tile = -1, tile_seq = 0;
-    int4 rc = make_int4(0, 0, 0, 0);
-    const unsigned char *w0 = nullptr, *w1 = nullptr, *w2 = nullptr;
-    const unsigned char* maps = nullptr;                                // this tile's descriptors: gate, up, down
-    bool absent = false, aligned = true;
-    int drawn = blockIdx.x;                     // the first group is this CTA's own number
-    int q = 0;
-    for (int k = 0;; ++k) {
-      // publish group k of this CTA (or the end of the list) and draw the one after it;
-      // the drawn number is only looked at when this group has been issued
-      const int cur = __shfl_sync(0xFFFFFFFFu, drawn, 0);
-      const Group wk = sc.decode(cur);
+    if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {             // constant indices only (see LayerDev)
+        tmpl[i] = L.tmap_gu[i];
+        tmpl[32 + i] = L.tmap_dn[i];
+      }
+    }
+    __syncwarp();
+    struct Prep {
+      Group g;
+      int id;
+      int4 rc;
+      const unsigned char *w0, *w1, *w2;
+      const unsigned char* maps;
+      int row;            // this lane's entry of GEntry::rows
+      bool absent, aligned;
+      unsigned ready;     // down groups: quantised blocks of the tile's h published so far
+    };
+    int map_seq = 0;
+    auto load_ptrs = [&](Prep& p) {
+      const bool shared = p.rc.x == L.E;
+      p.w0 = shared ? L.sh[0] : L.tab[p.rc.x];
+      p.w1 = shared ? L.sh[1] : L.tab[L.tab_stride + p.rc.x];
+      p.w2 = shared ? L.sh[2] : L.tab[2 * L.tab_stride + p.rc.x];
+      p.row = 0;
+      if (p.g.kind == 0 && lane < p.rc.y) p.row = shared ? p.rc.w + lane : __ldcg(L.grows + p.rc.w + lane);
+      // a down group's activation rows are the tile's quantised h: seen complete here (acquire), the
+      // activation warps need not look again (they run after this warp's publication of the entry)
+      p.ready = p.g.kind == 1 ? ld_acquire(L.ready + p.g.tile) : 0u;
+    };
+    // descriptors of the matrices this group reads (gate and up, or down), in the next slot of the
+    // CTA's ring: the ring keeps the descriptors of earlier groups intact while their copies fly
+    auto patch = [&](Prep& p) {
+      p.absent = p.w0 == nullptr || p.w1 == nullptr || p.w2 == nullptr;
+      p.aligned = ((reinterpret_cast<uintptr_t>(p.w0) | reinterpret_cast<uintptr_t>(p.w1) |
+                    reinterpret_cast<uintptr_t>(p.w2)) & 15u) == 0;
+      p.maps = nullptr;
+      if (p.absent || !p.aligned) return;
+      unsigned char* slot = gmaps + static_cast<size_t>(map_seq % kMapRing) * 3 * 128;
+      ++map_seq;
+      uint32_t* m = reinterpret_cast<uint32_t*>(smaps);
+      if (p.g.kind == 0) {
+        m[lane] = tmpl[lane];
+        m[32 + lane] = tmpl[lane];
+        __syncwarp();
+        if (lane == 0) {
+          tmap_replace_addr(smaps, p.w0);
+          tmap_replace_addr(smaps + 128, p.w1);
+        }
+        __syncwarp();
+        tmap_publish(slot, smaps);
+        tmap_publish(slot + 128, smaps + 128);
+        if (lane == 0) {
+          tmap_acquire(slot);
+          tmap_acquire(slot + 128);
+        }
+      } else {
+        m[64 + lane] = tmpl[32 + lane];
+        __syncwarp();
+        if (lane == 0) tmap_replace_addr(smaps + 256, p.w2);
+        __syncwarp();
+        tmap_publish(slot + 256, smaps + 256);
+        if (lane == 0) tmap_acquire(slot + 256);
+      }
+      __syncwarp();
+      p.maps = slot;
+    };
+    auto publish = [&](int k, const Prep& p) {
+      GEntry* e = glist + k % kListSlots;
+      if (lane < kTok) e->rows[lane] = p.row;
       if (lane == 0) {
-        glist[k % kListSlots] = wk.valid ? cur : -1;
+        e->id = p.g.valid ? p.id : -1;
+        e->absent = (p.absent ? 1 : 0) | (p.ready >= static_cast<unsigned>(L.nbf) ? 2 : 0);
+        e->rc = p.rc;
+      }
+      __syncwarp();
+      if (lane == 0) {
         __threadfence_block();
         *g_pub = static_cast<unsigned>(k) + 1u;
       }
+    };
+    Prep cur;
+    cur.id = blockIdx.x;                        // the first group is this CTA's own number
+    cur.g = sc.decode(cur.id);
+    cur.rc = make_int4(0, 0, 0, 0);
+    cur.w0 = cur.w1 = cur.w2 = nullptr;
+    cur.maps = nullptr;
+    cur.row = 0;
+    cur.absent = false;
+    cur.aligned = true;
+    cur.ready = 0u;
+    int drawn = 0;                               // lane 0: the number of the group after the next one
+    if (lane == 0) drawn = static_cast<int>(atomicAdd(&L.cnt[10], 1u));
+    if (cur.g.valid) {
+      cur.rc = __ldcg(L.rec + cur.g.tile);
+      load_ptrs(cur);
+      patch(cur);
+    }
+    publish(0, cur);
+    int q = 0;
+    for (int k = 0;; ++k) {
+      const Group wk = cur.g;
       if (!wk.valid) {                           // end of the list: one last stage that only says so
         const int s = q % kStageCount;
         const unsigned ph = (q / kStageCount) & 1;
@@ -285,51 +388,24 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
           Desc d;
           d.flags = 1 << 17; d.tile = 0; d.hrow0 = 0; d.row0 = 0;
           desc[s] = d;
+          mbar_arrive(&full[s]);
         }
-        mbar_arrive(&full[s]);
         return;
       }
+      Prep nx;
+      nx.id = __shfl_sync(0xFFFFFFFFu, drawn, 0);      // drawn while the previous group streamed
+      nx.g = sc.decode(nx.id);
+      nx.rc = make_int4(0, 0, 0, 0);
+      nx.w0 = nx.w1 = nx.w2 = nullptr;
+      nx.maps = nullptr;
+      nx.row = 0;
+      nx.absent = false;
+      nx.aligned = true;
+      nx.ready = 0u;
       if (lane == 0) drawn = static_cast<int>(atomicAdd(&L.cnt[10], 1u));
-      if (wk.tile != cur_tile) {
-        cur_tile = wk.tile;
-        rc = __ldcg(L.rec + wk.tile);
-        const bool shared = rc.x == L.E;
-        w0 = shared ? L.sh[0] : L.tab[rc.x];
-        w1 = shared ? L.sh[1] : L.tab[L.tab_stride + rc.x];
-        w2 = shared ? L.sh[2] : L.tab[2 * L.tab_stride + rc.x];
-        absent = w0 == nullptr || w1 == nullptr || w2 == nullptr;
-        aligned = ((reinterpret_cast<uintptr_t>(w0) | reinterpret_cast<uintptr_t>(w1) |
-                    reinterpret_cast<uintptr_t>(w2)) & 15u) == 0;
-        if (!absent && aligned) {
-          // descriptors of this expert's three matrices (the ring keeps the previous
-          // tiles' descriptors intact while their copies are in flight)
-          unsigned char* slot = gmaps + static_cast<size_t>(tile_seq % kMapRing) * 3 * 128;
-          ++tile_seq;
-          if (lane == 0) {
-            uint32_t* m = reinterpret_cast<uint32_t*>(smaps);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {       // constant indices only (see LayerDev)
-              m[i] = L.tmap_gu[i];
-              m[32 + i] = L.tmap_gu[i];
-              m[64 + i] = L.tmap_dn[i];
-            }
-            tmap_replace_addr(smaps, w0);
-            tmap_replace_addr(smaps + 128, w1);
-            tmap_replace_addr(smaps + 256, w2);
-          }
-          __syncwarp();
-          tmap_publish(slot, smaps);
-          tmap_publish(slot + 128, smaps + 128);
-          tmap_publish(slot + 256, smaps + 256);
-          if (lane == 0) {
-            tmap_acquire(slot);
-            tmap_acquire(slot + 128);
-            tmap_acquire(slot + 256);
-          }
-          __syncwarp();
-          maps = slot;
-        }
-      }
+      const int4 rc = cur.rc;
+      const bool absent = cur.absent, aligned = cur.aligned;
+      const unsigned char* maps = cur.maps;
       for (int blk = 0; blk < wk.nb; ++blk, ++q) {
       const int s = q % kStageCount;
       const unsigned ph = (q / kStageCount) & 1;
@@ -356,8 +432,6 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
             tma_load_box(st, maps + 256, blk * kW4, wk.gi * kDownRows, &full[s]);
             tma_load_box(st + kHalfBytes, maps + 256, blk * kW4, wk.gi * kDownRows + kHalfRows, &full[s]);
           }
-        } else {
-          mbar_arrive(&full[s]);
         }
       } else {
         if (!absent) {                           // sources without 16-byte alignment: plain loads
@@ -365,11 +439,11 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
           int rb;
           if (wk.kind == 0) {
             rb = rb_h;
-            b0 = w0 + static_cast<size_t>(wk.gi) * kGateUpPairs * rb_h + blk * kW4;
-            b1 = w1 + static_cast<size_t>(wk.gi) * kGateUpPairs * rb_h + blk * kW4;
+            b0 = cur.w0 + static_cast<size_t>(wk.gi) * kGateUpPairs * rb_h + blk * kW4;
+            b1 = cur.w1 + static_cast<size_t>(wk.gi) * kGateUpPairs * rb_h + blk * kW4;
           } else {
             rb = rb_f;
-            b0 = w2 + static_cast<size_t>(wk.gi) * kDownRows * rb_f + blk * kW4;
+            b0 = cur.w2 + static_cast<size_t>(wk.gi) * kDownRows * rb_f + blk * kW4;
             b1 = b0 + static_cast<size_t>(kHalfRows) * rb_f;
           }
           for (int p = lane; p < kHalfBytes / 16; p += 32) {
@@ -379,27 +453,34 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
           }
           fence_proxy_async();                   // the next fill of this stage may come from the TMA unit
         }
-        mbar_arrive(&full[s]);
+        __syncwarp();                            // every lane's part of the stage (and of its descriptor) is written
+        if (lane == 0) mbar_arrive(&full[s]);
       }
+      // the next group's global reads, requested between this group's copies
+      if (blk == 0 && nx.g.valid) nx.rc = __ldcg(L.rec + nx.g.tile);
+      if (blk == wk.nb - 1 && nx.g.valid) load_ptrs(nx);
       }   // block columns of the group
+      if (nx.g.valid) patch(nx);
+      publish(k + 1, nx);
+      cur = nx;
     }
   }
 
   if (warp > kConsumerWarps && warp <= kConsumerWarps + kXWarps) {
     // ---------------- activation warps ----------------
     const int xtid = tid - kConsumers - 32;
-    int cur_tile = -1, cur_kind = -1;
-    int4 rc = make_int4(0, 0, 0, 0);
-    bool absent = false;
     int myoff = 0;                              // lane t < 16: byte offset of token slot t's row
     int q = 0;
     for (int k = 0;; ++k) {
       bool got;
-      const Group wk = sc.decode(follow(k, got));
+      const GEntry* ge = follow(k, got);
       if (!got) {
         if (lane == 0) atomicExch(L.status, 7);
         return;
       }
+      const Group wk = sc.decode(ge->id);
+      const int4 rc = ge->rc;
+      const bool absent = (ge->absent & 1) != 0;
       if (!wk.valid) {                           // end of the list: count in at the last stage and leave
         const int s = q % kStageCount;
         const unsigned ph = (q / kStageCount) & 1;
@@ -410,34 +491,19 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
         cp_async_arrive(&full[s]);
         return;
       }
-      if (wk.tile != cur_tile || wk.kind != cur_kind) {
-        if (wk.tile != cur_tile) {
-          rc = __ldcg(L.rec + wk.tile);
-          const bool shared = rc.x == L.E;
-          const unsigned char* a0 = shared ? L.sh[0] : L.tab[rc.x];
-          const unsigned char* a1 = shared ? L.sh[1] : L.tab[L.tab_stride + rc.x];
-          const unsigned char* a2 = shared ? L.sh[2] : L.tab[2 * L.tab_stride + rc.x];
-          absent = a0 == nullptr || a1 == nullptr || a2 == nullptr;
-        }
-        cur_tile = wk.tile;
-        cur_kind = wk.kind;
-        myoff = 0;
-        if (wk.kind == 0) {
-          if (lane < rc.y) {
-            const int r = rc.x == L.E ? rc.w + lane : __ldcg(L.grows + rc.w + lane);
-            myoff = r * L.xq16_stride;
-          }
-        } else {
-          if (lane < rc.y) myoff = (rc.z + lane) * L.nbf * kHq;
-          if (!absent) {                        // the tile's h must be quantised and published
-            unsigned it = 0;
-            if (lane == 0)
-              while (ld_acquire(L.ready + wk.tile) < static_cast<unsigned>(L.nbf) && ++it < kSpinLimit) __nanosleep(64);
-            it = __shfl_sync(0xFFFFFFFFu, it, 0);
-            if (it >= kSpinLimit) {
-              if (lane == 0) atomicExch(L.status, 4);
-              return;
-            }
+      myoff = 0;
+      if (wk.kind == 0) {
+        if (lane < rc.y) myoff = ge->rows[lane] * L.xq16_stride;
+      } else {
+        if (lane < rc.y) myoff = (rc.z + lane) * L.nbf * kHq;
+        if (!absent && !(ge->absent & 2)) {     // the tile's h must be quantised and published
+          unsigned it = 0;
+          if (lane == 0)
+            while (ld_acquire(L.ready + wk.tile) < static_cast<unsigned>(L.nbf) && ++it < kSpinLimit) __nanosleep(64);
+          it = __shfl_sync(0xFFFFFFFFu, it, 0);
+          if (it >= kSpinLimit) {
+            if (lane == 0) atomicExch(L.status, 4);
+            return;
           }
         }
       }
@@ -480,11 +546,12 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     // rows and publishes it. The consumers never wait for any of this.
     for (int g = 0;; ++g) {
       bool got;
-      const Group wk = sc.decode(follow(g, got));
+      const GEntry* ge = follow(g, got);
       if (!got) {
         if (lane == 0) atomicExch(L.status, 7);
         return;
       }
+      const Group wk = sc.decode(ge->id);
       if (!wk.valid || wk.kind == 1) return;     // a CTA's gate/up groups all come before its down groups
       unsigned it = 0;
       if (lane == 0)

@@ -9,8 +9,10 @@
 // activations, exact integer dots, fp32 scaling - so it is checked against that
 // path, not against the fp16 one.
 //
-// A CTA owns 128 weight rows of one expert and walks that expert's token rows in
-// chunks of up to 64, two chunks per pass. The work of a pass is a list of jobs
+// The kernel is persistent: one CTA per SM takes work items (expert, tile of 128 weight rows)
+// round-robin, so tensor memory, the barriers and the pipeline are set up once per SM and the
+// roles run on into the next item without draining. Inside an item the CTA walks that expert's
+// token rows in chunks of up to 64, two chunks per pass. The work of a pass is a list of jobs
 // (super-block, chunk); job j uses accumulator set j & 1 in tensor memory and is
 // finished by epilogue group j & 1, so with one chunk the two groups take alternate
 // super-blocks and with two chunks each group owns a chunk. Four roles run as a
@@ -38,9 +40,6 @@
 
 namespace sgr {
 namespace {
-
-#define GP_T0() do {} while (0)
-#define GP_ADD(i) do {} while (0)
 
 constexpr int kGemmRows = 128;     // weight rows per CTA = MMA M
 constexpr int kGemmTok = 64;       // token rows per chunk = max MMA N
@@ -149,26 +148,36 @@ struct JobWalk {
   }
 };
 
-// grid (ceil(n_rows / 128), n_expert)
+// One work item: 128 weight rows of one expert against that expert's token rows.
+struct Item {
+  int e, row0, row_off, m_e;
+  const unsigned char* w;
+};
+
+// grid: one CTA per SM (or per item when there are fewer); item i = expert i / tiles, row tile i % tiles
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int* __restrict__ off,
                        const unsigned char* __restrict__ xq, uint16_t* __restrict__ y, int n_rows,
-                       int nb, int* status) {
+                       int nb, int tiles, int n_items, int* status) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  const int e = blockIdx.y;
-  const int row_off = off[e];
-  const int m_e = off[e + 1] - row_off;
-  if (m_e <= 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row0 = blockIdx.x * kGemmRows;
-  const unsigned char* w = w_tab[e];
-  if (w == nullptr) {                                      // absent expert: zero rows
-    for (int i = tid; i < m_e * kGemmRows; i += kGemmThreads) {
-      const int t = i / kGemmRows, r = row0 + (i % kGemmRows);
-      if (r < n_rows) y[static_cast<size_t>(row_off + t) * n_rows + r] = 0;
+  auto item_at = [&](int it) {
+    Item r;
+    r.e = it / tiles;
+    r.row0 = (it - r.e * tiles) * kGemmRows;
+    r.row_off = __ldg(off + r.e);
+    r.m_e = __ldg(off + r.e + 1) - r.row_off;
+    r.w = w_tab[r.e];
+    return r;
+  };
+  // first item at or after `it` (in this CTA's stride) that has token rows; with `need_w` also weights
+  auto next_item = [&](int it, bool need_w) {
+    for (; it < n_items; it += gridDim.x) {
+      const Item r = item_at(it);
+      if (r.m_e > 0 && (!need_w || r.w != nullptr)) break;
     }
-    return;
-  }
+    return it;
+  };
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem + kOffBar);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + 128);
   int* fail = reinterpret_cast<int*>(smem + kOffBar + 136);
@@ -199,7 +208,7 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
   const uint32_t tmem = *tmem_slot;
   const size_t xrow_bytes = static_cast<size_t>(nb) * kX8;
   JobWalk jw;
-  jw.start(m_e, nb);
+  auto failed = [&]() { return *reinterpret_cast<volatile int*>(fail) != 0; };
   // a wait that gives up: flag the CTA, every role leaves its loop at its next wait
   auto wait = [&](int b, unsigned parity) {
     if (*reinterpret_cast<volatile int*>(fail)) return false;
@@ -211,31 +220,61 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
   if (warp >= kWarpUnpack0 && warp < kWarpCtrl) {
     // ---------------- unpack: this thread's weight row -> operand tiles ----------------
     const int r = tid - kWarpUnpack0 * 32;
-    const int row = min(row0 + r, n_rows - 1);             // ragged last tile: duplicate, never stored
-    const unsigned char* wrow = w + static_cast<size_t>(row) * nb * kW4;
-    const uintptr_t wa = reinterpret_cast<uintptr_t>(w);
-    const int walign = (wa & 15u) == 0 ? 16 : ((wa & 3u) == 0 ? 4 : 2);
+    auto row_ptr = [&](const Item& I) {
+      const int row = min(I.row0 + r, n_rows - 1);         // ragged last tile: duplicate, never stored
+      return I.w + static_cast<size_t>(row) * nb * kW4;
+    };
+    auto align_of = [](const unsigned char* w) {
+      const uintptr_t wa = reinterpret_cast<uintptr_t>(w);
+      return (wa & 15u) == 0 ? 16 : ((wa & 3u) == 0 ? 4 : 2);
+    };
+    int it = next_item(blockIdx.x, true);
     uint4 cur[9];
+    if (it < n_items) {
+      const Item I0 = item_at(it);
+      const unsigned char* w0 = row_ptr(I0);
+      const int a0 = align_of(I0.w);
 #pragma unroll
-    for (int i = 0; i < 9; ++i) cur[i] = load16(wrow + 16 * i, walign);
-    int prev_abk = -1;
-    GP_T0();
-    for (; !jw.done(); jw.next()) {
+      for (int i = 0; i < 9; ++i) cur[i] = load16(w0 + 16 * i, a0);
+    }
+    int abk_base = 0;
+    while (it < n_items && !failed()) {
+      const Item I = item_at(it);
+      const unsigned char* wrow = row_ptr(I);
+      const int walign = align_of(I.w);
+      const int it_next = next_item(it + gridDim.x, true);
+      const unsigned char* wrow_next = nullptr;
+      int walign_next = 16;
+      if (it_next < n_items) {
+        const Item In = item_at(it_next);
+        wrow_next = row_ptr(In);
+        walign_next = align_of(In.w);
+      }
+      jw.start(I.m_e, nb);
+      int prev_abk = -1;
+      bool gave_up = false;
+      for (; !jw.done(); jw.next()) {
       if (jw.abk == prev_abk) continue;                     // one unpack per block column
       prev_abk = jw.abk;
-      const int buf = jw.abk % kABufs;
-      const unsigned ph = (jw.abk / kABufs) & 1;
-      // the next block column of this row (wraps to column 0 for the next pass) is requested now
+      const int abk = abk_base + jw.abk;
+      const int buf = abk % kABufs;
+      const unsigned ph = (abk / kABufs) & 1;
+      // the next block column in sequence is requested now: the next column of this row (column 0
+      // again for the next pass), or the first column of the next item's row
       uint4 nxt[9];
       {
-        const int nblk = jw.blk + 1 < nb ? jw.blk + 1 : 0;
-        const unsigned char* wn = wrow + static_cast<size_t>(nblk) * kW4;
+        const bool last_col = jw.blk + 1 == nb && (jw.pass + 1) * 2 * kGemmTok >= I.m_e;
+        const unsigned char* wn = last_col ? wrow_next : wrow + static_cast<size_t>(jw.blk + 1 < nb ? jw.blk + 1 : 0) * kW4;
+        const int an = last_col ? walign_next : walign;
+        if (wn != nullptr) {
 #pragma unroll
-        for (int i = 0; i < 9; ++i) nxt[i] = load16(wn + 16 * i, walign);
+          for (int i = 0; i < 9; ++i) nxt[i] = load16(wn + 16 * i, an);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 9; ++i) nxt[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
       }
-      if (r == 0) GP_ADD(1);
-      if (!wait(kBarAEmpty + buf, ph ^ 1u)) break;
-      if (r == 0) GP_ADD(0);
+      if (!wait(kBarAEmpty + buf, ph ^ 1u)) { gave_up = true; break; }
       unsigned char* a_tiles = a_base + static_cast<size_t>(buf) * kATiles * kTileA;
       const uint4 hdr = cur[0];
       const float d = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x & 0xFFFFu)));
@@ -272,11 +311,15 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
         *reinterpret_cast<uint4*>(tile_at(t_mn, r, 0)) = make_uint4(s6.mn[0], s6.mn[1], 0u, 0u);
         *reinterpret_cast<uint4*>(tile_at(t_mn, r, 1)) = make_uint4(0u, 0u, 0u, 0u);
       }
-      dd_sm[(jw.abk % kDdRing) * kGemmRows + r] = make_float2(d, dmin);
+      dd_sm[(abk % kDdRing) * kGemmRows + r] = make_float2(d, dmin);
       fence_proxy_async();                                 // operand tiles -> visible to the tensor core
       mbar_arrive_cta(&bar[kBarAFull + buf]);
 #pragma unroll
       for (int i = 0; i < 9; ++i) cur[i] = nxt[i];
+      }   // block columns of the item
+      if (gave_up) break;
+      abk_base += jw.abk;
+      it = it_next;
     }
   } else if (warp >= kWarpStage0) {
     // ---------------- stagers: activation codes, split sums and scales of a job's chunk ----------------
@@ -285,14 +328,18 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
     // 276-byte block, so their 16-byte pieces are not aligned: the lane reads the 17 aligned
     // pieces that cover them and picks each operand piece out of two neighbours by whole words.
     const int sg = warp - kWarpStage0;
-    GP_T0();
+    int j_base = 0;
+    bool ok = true;
+    for (int it = next_item(blockIdx.x, true); it < n_items && !failed(); it = next_item(it + gridDim.x, true)) {
+    const Item I = item_at(it);
+    const int row_off = I.row_off;
+    jw.start(I.m_e, nb);
     for (; !jw.done(); jw.next()) {
-      const int j = jw.j, buf = j % kBBufs;
+      const int j = j_base + jw.j, buf = j % kBBufs;
       if (j % kStageWarps != sg) continue;
       const unsigned ph = (j / kBBufs) & 1;
       const int t0 = jw.t0(), nt = jw.nt();
       unsigned char* b_tiles = b_base + static_cast<size_t>(buf) * kBTiles * kTileB;
-      bool ok = true;
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         const int s = lane + 32 * half;                    // token row of the chunk
@@ -311,9 +358,7 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
           pf[1] = __ldg(bs); pf[2] = __ldg(bs + 1); pf[3] = __ldg(bs + 2); pf[4] = __ldg(bs + 3);
         }
         if (half == 0) {
-          if (sg == 0 && lane == 0) GP_ADD(3);
           ok = __all_sync(0xFFFFFFFFu, wait(kBarBEmpty + buf, ph ^ 1u));
-          if (sg == 0 && lane == 0) GP_ADD(2);
           if (!ok) break;
         }
         if (s < nt) {
@@ -355,19 +400,27 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
       fence_proxy_async();
       mbar_arrive_cta(&bar[kBarBFull + buf]);
     }
+    if (!ok) break;
+    j_base += jw.j;
+    }   // items
   } else if (warp == kWarpCtrl) {
     // ---------------- MMA issue: one elected thread ----------------
     if (lane == 0) {
-      GP_T0();
+      int j_base = 0, abk_base = 0;
+      unsigned use[2] = {0u, 0u};                           // jobs issued so far into each accumulator set
+      bool ok = true;
+      for (int it = next_item(blockIdx.x, true); it < n_items && ok; it = next_item(it + gridDim.x, true)) {
+      const Item I = item_at(it);
+      jw.start(I.m_e, nb);
       for (; !jw.done(); jw.next()) {
-        const int j = jw.j, abuf = jw.abk % kABufs, bbuf = j % kBBufs, set = j & 1;
-        GP_ADD(7);
-        if (jw.first_of_block() && !wait(kBarAFull + abuf, (jw.abk / kABufs) & 1)) break;
-        GP_ADD(4);
+        const int j = j_base + jw.j, abk = abk_base + jw.abk;
+        const int abuf = abk % kABufs, bbuf = j % kBBufs, set = jw.j & 1;
+        ok = false;
+        if (jw.first_of_block() && !wait(kBarAFull + abuf, (abk / kABufs) & 1)) break;
         if (!wait(kBarBFull + bbuf, (j / kBBufs) & 1)) break;
-        GP_ADD(5);
-        if (!wait(kBarAccEmpty + set, ((j >> 1) & 1) ^ 1u)) break;
-        GP_ADD(6);
+        if (!wait(kBarAccEmpty + set, (use[set] & 1u) ^ 1u)) break;
+        ok = true;
+        ++use[set];
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // descriptors of consecutive tiles differ by the tile size in the address field
         const uint64_t da0 = umma_desc(a_base + static_cast<size_t>(abuf) * kATiles * kTileA);
@@ -388,6 +441,9 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
         umma_commit(&bar[kBarBEmpty + bbuf]);               // B tiles free
         if (jw.last_of_block()) umma_commit(&bar[kBarAEmpty + abuf]);   // A tiles free
       }
+      j_base += jw.j;
+      abk_base += jw.abk;
+      }   // items
     }
   } else {
     // ---------------- epilogue: two groups of four warps; this thread's row, the job's tokens ----------------
@@ -398,11 +454,24 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
 #pragma unroll
     for (int t = 0; t < kGemmTok; ++t) acc[t] = 0.f;
     bool ok = true;
+    int j_base = 0, abk_base = 0;
+    unsigned use = 0u;                                     // jobs this group has finished (the phase of its accumulator set)
+    for (int it = next_item(blockIdx.x, false); it < n_items; it = next_item(it + gridDim.x, false)) {
+    const Item I = item_at(it);
+    const int row0 = I.row0, row_off = I.row_off, m_e = I.m_e;
+    if (I.w == nullptr) {                                    // absent expert: zero rows
+      for (int i = tid; i < m_e * kGemmRows; i += kEpiWarps * 32) {
+        const int t = i / kGemmRows, r = row0 + (i % kGemmRows);
+        if (r < n_rows) y[static_cast<size_t>(row_off + t) * n_rows + r] = 0;
+      }
+      continue;
+    }
+    jw.start(m_e, nb);
     int pass_t0 = 0, pass_nc = jw.nc, pass_nt0 = 0, pass_nt1 = 0, cur_pass = 0;
     auto flush = [&]() {
       // end of a pass: one chunk -> group 1 hands its sums to group 0 through shared memory
       // (two halves of 32 tokens); two chunks -> each group stores its own chunk
-      const bool valid = row0 + row < n_rows && ok && !*reinterpret_cast<volatile int*>(fail);
+      const bool valid = row0 + row < n_rows && ok && !failed();
       if (pass_nc == 1) {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -434,7 +503,6 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
     };
     pass_nt0 = min(kGemmTok, m_e);
     pass_nt1 = min(kGemmTok, max(0, m_e - kGemmTok));
-    GP_T0();
     for (; !jw.done(); jw.next()) {
       if (jw.pass != cur_pass) {                            // both groups see the pass change at the same job
         flush();
@@ -444,14 +512,13 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
         pass_nt0 = min(kGemmTok, m_e - pass_t0);
         pass_nt1 = min(kGemmTok, max(0, m_e - pass_t0 - kGemmTok));
       }
-      const int j = jw.j;
-      if ((j & 1) != grp || !ok) continue;                 // (a group that gave up still walks the list: the
+      if ((jw.j & 1) != grp || !ok) continue;              // (a group that gave up still walks the list: the
                                                             //  barriers of the pass ends need both groups)
-      if (tid == 0) GP_ADD(9);
-      if (!__all_sync(0xFFFFFFFFu, wait(kBarAccFull + grp, (j >> 1) & 1))) { ok = false; continue; }
-      if (tid == 0) GP_ADD(8);
+      const int j = j_base + jw.j, abk = abk_base + jw.abk;
+      if (!__all_sync(0xFFFFFFFFu, wait(kBarAccFull + grp, use & 1u))) { ok = false; continue; }
+      ++use;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float2 dd = dd_sm[(jw.abk % kDdRing) * kGemmRows + row];
+      const float2 dd = dd_sm[(abk % kDdRing) * kGemmRows + row];
       const float* xd = xd_sm + (j % kXdRing) * kGemmTok;
       const int n_mma = (jw.nt() + 15) & ~15;
       const uint32_t accp = tmem + lane_base + grp * 4 * kGemmTok;
@@ -475,9 +542,10 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive_cta(&bar[kBarAccEmpty + grp]);
     }
-    if (tid == 0) GP_ADD(9);
     flush();
-    if (tid == 0) GP_ADD(10);
+    j_base += jw.j;
+    abk_base += jw.abk;
+    }   // items
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -507,9 +575,16 @@ SGR_API int sgr_moe_grouped_gemm_i8(const void* const* w_tab, const int* off, co
     return kErrLaunch;
   int* status = status_word();
   if (status == nullptr) return kErrLaunch;       // the kernel reports an expired wait through it
-  kern<<<dim3((n_rows + kGemmRows - 1) / kGemmRows, n_expert), kGemmThreads, kGemmSmem, as_stream(stream)>>>(
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    return kErrLaunch;
+  const int tiles = (n_rows + kGemmRows - 1) / kGemmRows;
+  const long long n_items = static_cast<long long>(tiles) * n_expert;
+  if (n_items > 0x7FFFFFFF) return kErrUnsupported;
+  kern<<<static_cast<unsigned>(n_items < sms ? n_items : sms), kGemmThreads, kGemmSmem, as_stream(stream)>>>(
       reinterpret_cast<const unsigned char* const*>(w_tab), off, static_cast<const unsigned char*>(xq), y,
-      n_rows, k / kQK, status);
+      n_rows, k / kQK, tiles, static_cast<int>(n_items), status);
   return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
