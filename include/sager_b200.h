@@ -247,8 +247,8 @@ typedef struct sgr_moe_layer {
   const void* shared_gate;  /* shared expert matrices, or all NULL */
   const void* shared_up;
   const void* shared_down;
-  uint16_t* x_f16;       /* optional [n][hidden]: residual in, residual + MoE out */
-  float* out_f32;        /* optional [n][hidden] fp32 copy of the result */
+  uint16_t* x_f16;       /* optional [n][hidden]: residual in, residual + MoE out (4-byte aligned) */
+  float* out_f32;        /* optional [n][hidden] fp32 copy of the result (8-byte aligned) */
   int* route_idx;        /* [n][n_used+1] */
   float* route_w;        /* [n][n_used+1] */
   int* mail;             /* optional [n_expert] absent-expert mailbox */
@@ -283,7 +283,8 @@ typedef struct sgr_moe_layer {
    *   owner side (routing_given): row t of the result is stored to
    *     ep_out[t / ep_home_rows] + (t % ep_home_rows) * hidden (this rank's slot in the home rank's
    *     return buffer) instead of out_f32, then the home ranks' words are set.
-   * Plain stores to peer memory only: no multicast, no library kernel touches a peer's memory. */
+   * ep_out[p] 8-byte aligned. Plain stores to peer memory only: no multicast, no library kernel
+   * touches a peer's memory. */
   void* const* ep_dst;
   unsigned* const* ep_flags;
   float* const* ep_out;

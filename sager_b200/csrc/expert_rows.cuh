@@ -59,7 +59,6 @@ constexpr int kHdr = 4096;
 constexpr size_t kSmem = kHdr + static_cast<size_t>(kStageCount) * kStageBytes;
 constexpr int kGateUpPairs = 128;               // pairs per gate/up group
 constexpr int kDownRows = 256;                  // rows per down group
-constexpr int kCombineRows = 64;
 constexpr int kFullArrivals = 1 + kXThreads;      // weight warp: one arrival; activation warps: a thread's copies landed
 constexpr int kMapRing = kStageCount + 1;        // descriptor slots per CTA: a slot is patched again only after every
                                                  // stage that could still reference it has been refilled (a tile has at
@@ -730,13 +729,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     if (tid == 0) atomicExch(L.status, 5);
     return;
   }
-  const int tgroups = (L.n + 15) / 16;
-  const int chunks = (L.H + kCombineRows - 1) / kCombineRows;
-  for (int job = blockIdx.x; job < chunks * tgroups; job += gridDim.x) {
-    const int c = job / tgroups, tg = job - c * tgroups;
-    combine_rows(L, c * kCombineRows, min(kCombineRows, L.H - c * kCombineRows), tg * 16, min(L.n, tg * 16 + 16),
-                 tid, kConsumers);
-  }
+  combine_flat(L, blockIdx.x * kConsumers + tid, gridDim.x * kConsumers);
   if (L.ep_out != nullptr) {
     // Owner side of an expert-parallel layer: the rows went straight into the home ranks' buffers;
     // the last CTA to finish tells the home ranks.

@@ -707,6 +707,60 @@ __device__ __forceinline__ void item_compute_dp4a(const unsigned char* w, int ws
 }
 
 // residual + sum_k w_k * y_k + shared expert for output rows [row0, row0+nrows), tokens [t_lo, t_hi)
+// The same blend as combine_rows over the whole layer, two columns per thread and every thread of the
+// grid at work: the routes of a token (slot, weight) are fetched eight at a time and their y rows
+// requested together, so an output costs two round trips to L2 instead of two per expert. Terms are
+// added in combine_rows' order (residual, experts in slot order, shared expert), so both give the same bits.
+__device__ __forceinline__ void combine_flat(const LayerDev& L, int gtid, int gthreads) {
+  const bool has_shared = L.sh[0] != nullptr;
+  const int half = L.H >> 1;
+  for (int idx = gtid; idx < L.n * half; idx += gthreads) {
+    const int tk = idx / half, r = (idx - tk * half) * 2;
+    const size_t o = static_cast<size_t>(tk) * L.H + r;
+    float a0 = 0.f, a1 = 0.f;
+    if (L.add_residual && L.x_f16 != nullptr) {
+      const uint32_t xv = *reinterpret_cast<const uint32_t*>(L.x_f16 + o);
+      a0 = h2f(static_cast<uint16_t>(xv & 0xFFFFu));
+      a1 = h2f(static_cast<uint16_t>(xv >> 16));
+    }
+    const float* wr = L.w + static_cast<size_t>(tk) * L.rstride;
+    for (int k0 = 0; k0 < L.K; k0 += 8) {
+      int gs[8];
+      float w[8];
+      float2 y[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool in = k0 + j < L.K;
+        gs[j] = in ? __ldcg(L.gslot + tk * L.K + k0 + j) : -1;
+        w[j] = in ? __ldcg(wr + k0 + j) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        y[j] = gs[j] >= 0 ? __ldcg(reinterpret_cast<const float2*>(L.ybuf + static_cast<size_t>(gs[j]) * L.H + r))
+                          : make_float2(0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (gs[j] >= 0) {
+          a0 += w[j] * y[j].x;
+          a1 += w[j] * y[j].y;
+        }
+      }
+    }
+    if (has_shared && tk >= L.sh_lo && tk < L.sh_hi) {
+      const float ws = __ldcg(wr + L.K);
+      const float2 ys = __ldcg(reinterpret_cast<const float2*>(L.ybuf + static_cast<size_t>(L.n_max * L.K + tk) * L.H + r));
+      a0 += ws * ys.x;
+      a1 += ws * ys.y;
+    }
+    if (L.ep_out != nullptr)
+      *reinterpret_cast<float2*>(L.ep_out[tk / L.ep_home] + static_cast<size_t>(tk % L.ep_home) * L.H + r) = make_float2(a0, a1);
+    else if (L.out_f32 != nullptr)
+      *reinterpret_cast<float2*>(L.out_f32 + o) = make_float2(a0, a1);
+    if (L.x_f16 != nullptr && L.add_residual)
+      *reinterpret_cast<uint32_t*>(L.x_f16 + o) = static_cast<uint32_t>(f2h(a0)) | (static_cast<uint32_t>(f2h(a1)) << 16);
+  }
+}
+
 __device__ __forceinline__ void combine_rows(const LayerDev& L, int row0, int nrows, int t_lo, int t_hi,
                                              int tid, int nthr) {
   const bool has_shared = L.sh[0] != nullptr;
@@ -1185,7 +1239,9 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   const WsLayout lay = ws_layout(a->n_max, a->hidden, a->n_ff, a->n_expert, a->n_used);
   if ((reinterpret_cast<uintptr_t>(a->workspace) & 255u) ||
       (a->xn && (reinterpret_cast<uintptr_t>(a->xn) & 15u)) ||
-      (a->xq_in && (reinterpret_cast<uintptr_t>(a->xq_in) & 3u)))
+      (a->xq_in && (reinterpret_cast<uintptr_t>(a->xq_in) & 3u)) ||
+      (a->x_f16 && (reinterpret_cast<uintptr_t>(a->x_f16) & 3u)) ||          // the blend moves two columns at a time
+      (a->out_f32 && (reinterpret_cast<uintptr_t>(a->out_f32) & 7u)))
     return kErrAlign;
 
   LayerDev L{};
