@@ -266,11 +266,14 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
 
   if (warp == kConsumerWarps) {
     // ---------------- weight warp ----------------
-    // Streams group k while it prepares group k + 1: the group number was drawn a group earlier, the
-    // tile's record is requested after the first stage of group k has been issued, the expert's
-    // pointers (and the token slots' source rows) after the last one, and the descriptors are
-    // patched once the group's copies are all issued - so none of these global round trips, nor the
-    // descriptor update, sits between two copies of the stream.
+    // Streams group k while it prepares group k + 1: the tile's record is requested between two
+    // copies of group k, the expert's pointers (and the token slots' source rows) after its last copy,
+    // and the descriptors are patched once the group's copies are all issued - so these global round
+    // trips and the descriptor update overlap the stream. A group's number is drawn as late as that
+    // allows: a number drawn is a group that no other CTA can take, and a gate/up group that waits
+    // long for its CTA delays its tile's h, on which eight down groups elsewhere depend. So the next
+    // number is drawn four stages before the current group ends - or, when the group it follows is a
+    // short down group, as soon as that one's number is known.
     unsigned char* smaps = smem + 1024;                                 // three 128-byte descriptors being patched
     uint32_t* tmpl = reinterpret_cast<uint32_t*>(smem + 1408);          // the two host-made descriptors
     unsigned char* gmaps = L.tmaps + static_cast<size_t>(blockIdx.x) * kMapRing * 3 * 128;
@@ -365,8 +368,8 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     cur.absent = false;
     cur.aligned = true;
     cur.ready = 0u;
-    int drawn = 0;                               // lane 0: the number of the group after the next one
-    if (lane == 0) drawn = static_cast<int>(atomicAdd(&L.cnt[10], 1u));
+    int drawn = 0;                               // lane 0: the number last drawn
+    bool id_ready = false;                       // ... which is that of the next group, not yet looked at
     if (cur.g.valid) {
       cur.rc = __ldcg(L.rec + cur.g.tile);
       load_ptrs(cur);
@@ -392,8 +395,8 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
         return;
       }
       Prep nx;
-      nx.id = __shfl_sync(0xFFFFFFFFu, drawn, 0);      // drawn while the previous group streamed
-      nx.g = sc.decode(nx.id);
+      nx.id = -1;
+      nx.g = sc.decode(-1);
       nx.rc = make_int4(0, 0, 0, 0);
       nx.w0 = nx.w1 = nx.w2 = nullptr;
       nx.maps = nullptr;
@@ -401,7 +404,8 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
       nx.absent = false;
       nx.aligned = true;
       nx.ready = 0u;
-      if (lane == 0) drawn = static_cast<int>(atomicAdd(&L.cnt[10], 1u));
+      const int draw_at = id_ready ? -1 : max(0, wk.nb - 4);                   // stage after which the number is drawn
+      const int look_at = id_ready ? 0 : min(wk.nb - 1, draw_at + 1);          // ... and after which it is looked at
       const int4 rc = cur.rc;
       const bool absent = cur.absent, aligned = cur.aligned;
       const unsigned char* maps = cur.maps;
@@ -455,8 +459,20 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
         __syncwarp();                            // every lane's part of the stage (and of its descriptor) is written
         if (lane == 0) mbar_arrive(&full[s]);
       }
-      // the next group's global reads, requested between this group's copies
-      if (blk == 0 && nx.g.valid) nx.rc = __ldcg(L.rec + nx.g.tile);
+      // the next group's number and global reads, requested between this group's copies
+      if (blk == draw_at && lane == 0) drawn = static_cast<int>(atomicAdd(&L.cnt[10], 1u));
+      if (blk == look_at) {
+        nx.id = __shfl_sync(0xFFFFFFFFu, drawn, 0);
+        nx.g = sc.decode(nx.id);
+        id_ready = false;
+        if (nx.g.valid) {
+          nx.rc = __ldcg(L.rec + nx.g.tile);
+          if (nx.g.kind == 1) {                  // a short group: have the number after it at hand when it starts
+            if (lane == 0) drawn = static_cast<int>(atomicAdd(&L.cnt[10], 1u));
+            id_ready = true;
+          }
+        }
+      }
       if (blk == wk.nb - 1 && nx.g.valid) load_ptrs(nx);
       }   // block columns of the group
       if (nx.g.valid) patch(nx);

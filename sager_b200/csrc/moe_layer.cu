@@ -204,7 +204,8 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   unsigned long long* mask = reinterpret_cast<unsigned long long*>(smem);       // [E]
   int* scan_rows = reinterpret_cast<int*>(smem + static_cast<size_t>(L.E) * 8);   // [65] warp totals, prefixes, total
   int* scan_tiles = scan_rows + 128;                                              // [65]
-  int* off_sh = scan_rows + 256;                                                  // [E] copy of L.off for the last pass
+  int* scan_heavy = scan_rows + 256;                                              // [65]
+  int* off_sh = scan_rows + 384;                                                  // [E] copy of L.off for the last pass
   __shared__ int bad_sh;
   const int tid = threadIdx.x;
   const int total = L.n * L.K;
@@ -228,56 +229,65 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   // exclusive prefixes of rows and tiles over experts: each thread owns a run of experts
   const int per = (L.E + blockDim.x - 1) / blockDim.x;
   const int e0 = tid * per, e1 = min(L.E, e0 + per);
-  int rows = 0, tiles = 0;
+  // Tile order: the shared expert's tiles, then the routed tiles of more than half a tile's rows
+  // ("heavy"), then the rest, each class in expert order. The expert kernels hand work out in tile
+  // order; tiles of many rows take longest, in the dot products and in the requantisation of h that
+  // must finish before their down projection can start, so they go first and the light ones fill the end.
+  auto is_heavy = [&](int rows_in_tile) { return 2 * rows_in_tile > TT; };
+  int rows = 0, tiles = 0, heavy = 0;
   for (int e = e0; e < e1; ++e) {
     const int c = __popcll(mask[e]);
     rows += c;
     tiles += (c + TT - 1) / TT;
+    heavy += c / TT + (is_heavy(c % TT) ? 1 : 0);
   }
   // exclusive scan over the threads: inside the warps with shuffles, across the warps by warp 0
   {
     const int lane = tid & 31, wp = tid >> 5, nw = (blockDim.x + 31) >> 5;
-    int ir = rows, it = tiles;
+    int ir = rows, it = tiles, ih = heavy;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
       const int ur = __shfl_up_sync(0xFFFFFFFFu, ir, off), ut = __shfl_up_sync(0xFFFFFFFFu, it, off);
-      if (lane >= off) { ir += ur; it += ut; }
+      const int uh = __shfl_up_sync(0xFFFFFFFFu, ih, off);
+      if (lane >= off) { ir += ur; it += ut; ih += uh; }
     }
-    if (lane == 31) { scan_rows[wp] = ir; scan_tiles[wp] = it; }
+    if (lane == 31) { scan_rows[wp] = ir; scan_tiles[wp] = it; scan_heavy[wp] = ih; }
     __syncthreads();
     if (wp == 0) {
       int wr = lane < nw ? scan_rows[lane] : 0, wt = lane < nw ? scan_tiles[lane] : 0;
-      const int own_r = wr, own_t = wt;
+      int wh = lane < nw ? scan_heavy[lane] : 0;
+      const int own_r = wr, own_t = wt, own_h = wh;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
         const int ur = __shfl_up_sync(0xFFFFFFFFu, wr, off), ut = __shfl_up_sync(0xFFFFFFFFu, wt, off);
-        if (lane >= off) { wr += ur; wt += ut; }
+        const int uh = __shfl_up_sync(0xFFFFFFFFu, wh, off);
+        if (lane >= off) { wr += ur; wt += ut; wh += uh; }
       }
       scan_rows[32 + lane] = wr - own_r;          // exclusive prefix of the warps
       scan_tiles[32 + lane] = wt - own_t;
-      if (lane == 31) { scan_rows[64] = wr; scan_tiles[64] = wt; }
+      scan_heavy[32 + lane] = wh - own_h;
+      if (lane == 31) { scan_rows[64] = wr; scan_tiles[64] = wt; scan_heavy[64] = wh; }
     }
     __syncthreads();
     rows = scan_rows[32 + wp] + ir - rows;        // this thread's exclusive prefixes
     tiles = scan_tiles[32 + wp] + it - tiles;
+    heavy = scan_heavy[32 + wp] + ih - heavy;
   }
+  const int sh_tiles = (L.sh[0] != nullptr && L.sh_hi > L.sh_lo) ? (L.sh_hi - L.sh_lo + TT - 1) / TT : 0;
+  const int heavy_total = scan_heavy[64];
   if (tid == 0) {
     const int ar = scan_rows[64], at = scan_tiles[64];
-    // shared expert: tiles over the rows [sh_lo, sh_hi), appended after the routed ones
-    int sh_tiles = 0;
-    if (L.sh[0] != nullptr && L.sh_hi > L.sh_lo) {
-      sh_tiles = (L.sh_hi - L.sh_lo + TT - 1) / TT;
-      for (int i = 0; i < sh_tiles; ++i) {
-        const int t0 = i * TT;
-        L.rec[at + i] = make_int4(L.E, min(TT, L.sh_hi - L.sh_lo - t0),
-                                  L.n_max * L.K + L.sh_lo + t0, L.sh_lo + t0);
-      }
+    // shared expert: tiles over the rows [sh_lo, sh_hi), ahead of the routed ones
+    for (int i = 0; i < sh_tiles; ++i) {
+      const int t0 = i * TT;
+      L.rec[i] = make_int4(L.E, min(TT, L.sh_hi - L.sh_lo - t0),
+                           L.n_max * L.K + L.sh_lo + t0, L.sh_lo + t0);
     }
     L.off[L.E] = ar;
     L.meta[0] = ar;
     L.meta[1] = at + sh_tiles;
     L.meta[2] = bad_sh;
-    L.meta[3] = at;
+    L.meta[3] = sh_tiles;                 // first routed tile
     if (L.mail_n != nullptr) *L.mail_n = 0;
     L.cnt[9] = 0u;                        // grid barrier of the expert kernel
     L.cnt[10] = static_cast<unsigned>(L.grid);   // row-streaming kernel: next group to hand out
@@ -285,14 +295,16 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   reset_tile_counters(L, tid, blockDim.x);
   __syncthreads();
   {
-    int ar = rows, at = tiles;
+    int ar = rows;
+    int at_heavy = sh_tiles + heavy, at_light = sh_tiles + heavy_total + (tiles - heavy);
     for (int e = e0; e < e1; ++e) {
       const int c = __popcll(mask[e]);
       L.off[e] = ar;
       off_sh[e] = ar;
       for (int t0 = 0; t0 < c; t0 += TT) {
-        L.rec[at] = make_int4(e, min(TT, c - t0), ar + t0, ar + t0);
-        ++at;
+        const int ct = min(TT, c - t0);
+        const int at = is_heavy(ct) ? at_heavy++ : at_light++;
+        L.rec[at] = make_int4(e, ct, ar + t0, ar + t0);
       }
       ar += c;
     }
@@ -310,7 +322,7 @@ __device__ void build_plan(const LayerDev& L, unsigned char* smem) {
   }
 }
 
-inline size_t plan_smem(int E, int, int) { return static_cast<size_t>(E) * 12 + 2 * 128 * 4; }
+inline size_t plan_smem(int E, int, int) { return static_cast<size_t>(E) * 12 + 3 * 128 * 4; }
 
 // ---- launch 1: route ------------------------------------------------------------------
 // grid (ceil(E / 16), ceil(n / 8)), 256 threads: a CTA computes the logits of sixteen
