@@ -16,9 +16,10 @@
 // The head is the largest matrix of a step (151,936 x 2048: 255 MB), so the GEMV is a
 // persistent kernel: one CTA per SM, a producer warp streaming stages of whole rows (1680
 // contiguous bytes each at k = 2048) into a shared-memory ring with bulk copies, eight
-// consumer warps. A lane owns one sub-group: sixteen 6-bit weights are two 16-byte runs of ql
-// and qh, read as words (blocks start on 2-byte boundaries only: odd blocks are realigned with a
-// funnel shift), turned into four packed words with two mask operations each and fed to dp4a.
+// eight consumer warps of four rows each. A lane owns a quarter of a block (64 weights, four sub-groups): two
+// 16-byte runs of ql and one of qh, read as words (blocks start on 2-byte boundaries only: odd
+// blocks are realigned with a funnel shift), each ql word giving two packed words of 6-bit values
+// and each qh word serving four of them, fed to dp4a; a row of k = 2048 is one pass of a warp.
 // The activation row is staged once per CTA with its sixteen 16-column sums per block.
 #include "api_util.cuh"
 #include "q4k_common.cuh"
@@ -28,9 +29,10 @@ namespace {
 
 constexpr int kQ6 = 210;                     // bytes per Q6_K super-block
 constexpr int kHeadWarps = 8;
+constexpr int kHeadRows = 4;                  // rows a warp works on at once
 constexpr int kHeadThreads = kHeadWarps * 32 + 32;
 constexpr int kHeadStages = 4;
-constexpr int kHeadStageBytes = 48 * 1024;   // whole rows, at most this many bytes per stage
+constexpr int kHeadStageBytes = 54 * 1024;   // whole rows, at most this many bytes per stage (and at most 32 rows)
 
 struct HeadArgs {
   const unsigned char* w;
@@ -108,13 +110,11 @@ __global__ void __launch_bounds__(kHeadThreads, 1) gemv_q6_stream_kernel(const H
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kHeadWarps * 32) : "memory");
 
-    // a lane owns sub-group (lane & 15) of two blocks per pass: lanes 0-15 block 2p, lanes 16-31 block 2p+1
-    const int t = lane & 15;
-    const int qslot = (t & 7) >> 1, is = t & 1, n_half = t >> 3;
-    const int ql_off = n_half * 64 + (qslot & 1) * 32 + is * 16;
-    const int qh_off = 128 + n_half * 32 + is * 16;
-    const int nib = (qslot & 2) ? 4 : 0, hshift = qslot * 2;
-    const int colbase = n_half * 128 + qslot * 32 + is * 16;
+    // A lane owns a quarter of a block: the sixteen columns (n, is) of all four qslots, i.e. the
+    // 16-byte runs ql[n*64 + is*16 ..], ql[n*64 + 32 + is*16 ..] and qh[n*32 + is*16 ..], which hold
+    // the sub-groups t = n*8 + 2*qslot + is, qslot = 0..3 (64 weights, four scales). A row of
+    // k = 2048 is one pass of the warp. Blocks start on 2-byte boundaries only: the runs are read
+    // as five aligned words each and realigned with a funnel shift (by 0 or 16 bits).
     int it = 0;
     for (int st = blockIdx.x; st < n_stages && ok; st += gridDim.x, ++it) {
       const int s = it % kHeadStages;
@@ -123,39 +123,76 @@ __global__ void __launch_bounds__(kHeadThreads, 1) gemv_q6_stream_kernel(const H
       const int r0 = st * a.rows_per_stage;
       const int nr = min(a.rows_per_stage, a.n_rows - r0);
       const unsigned char* stage = ring + static_cast<size_t>(s) * stage_bytes;
-      for (int r = warp; r < nr; r += kHeadWarps) {
-        const unsigned char* roww = stage + static_cast<size_t>(r) * row_bytes;
-        float acc = 0.f;
-        for (int b0 = 0; b0 < nb; b0 += 2) {
-          const int blk = b0 + (lane >> 4);
-          if (blk < nb) {
-            const unsigned char* blk6 = roww + blk * kQ6;
-            // sixteen bytes of ql and of qh as aligned words, realigned when the block starts 2 bytes in
-            const uintptr_t pl = reinterpret_cast<uintptr_t>(blk6 + ql_off), ph = reinterpret_cast<uintptr_t>(blk6 + qh_off);
-            const uint32_t* wl = reinterpret_cast<const uint32_t*>(pl & ~static_cast<uintptr_t>(3));
+      // four rows of the stage per warp and pass (rows warp, warp + 8, ...): their loads are in flight
+      // together, the activation words are fetched once for the four, and one transposing reduction
+      // (six shuffles) replaces four of five
+      for (int rb = warp; rb < nr; rb += kHeadWarps * kHeadRows) {
+        const unsigned char* roww[kHeadRows];
+#pragma unroll
+        for (int i = 0; i < kHeadRows; ++i)
+          roww[i] = stage + static_cast<size_t>(min(rb + i * kHeadWarps, nr - 1)) * row_bytes;
+        float acc[kHeadRows];
+#pragma unroll
+        for (int i = 0; i < kHeadRows; ++i) acc[i] = 0.f;
+        for (int u = lane; u < nb * 4; u += 32) {
+          const int blk = u >> 2, n_half = (u >> 1) & 1, is = u & 1;
+          const int off0 = blk * kQ6 + n_half * 64 + is * 16, offh = blk * kQ6 + 128 + n_half * 32 + is * 16;
+          const int8_t* xcol = xs + blk * 256 + n_half * 128 + is * 16;
+          const uint4 x0 = *reinterpret_cast<const uint4*>(xcol), x1 = *reinterpret_cast<const uint4*>(xcol + 32);
+          const uint4 x2 = *reinterpret_cast<const uint4*>(xcol + 64), x3 = *reinterpret_cast<const uint4*>(xcol + 96);
+          const uint32_t xa[4] = {x0.x, x0.y, x0.z, x0.w}, xb[4] = {x1.x, x1.y, x1.z, x1.w};
+          const uint32_t xc[4] = {x2.x, x2.y, x2.z, x2.w}, xe[4] = {x3.x, x3.y, x3.z, x3.w};
+          const int* xsp = xsum + blk * 16 + n_half * 8 + is;
+          // the zero point: every sum starts at -32 * (sum of the sub-group's activations)
+          const int z0 = -32 * xsp[0], z1 = -32 * xsp[2], z2 = -32 * xsp[4], z3 = -32 * xsp[6];
+          const float xdb = xd[blk];
+#pragma unroll
+          for (int i = 0; i < kHeadRows; ++i) {
+            const unsigned char* blk6 = roww[i] + blk * kQ6;
+            const uintptr_t p0 = reinterpret_cast<uintptr_t>(roww[i] + off0);
+            const uintptr_t ph = reinterpret_cast<uintptr_t>(roww[i] + offh);
+            const unsigned sh = static_cast<unsigned>(p0 & 3u) * 8u;      // the three runs share the block's alignment
+            const uint32_t* w0 = reinterpret_cast<const uint32_t*>(p0 & ~static_cast<uintptr_t>(3));
+            const uint32_t* w1 = w0 + 8;                                   // 32 bytes on
             const uint32_t* wh = reinterpret_cast<const uint32_t*>(ph & ~static_cast<uintptr_t>(3));
-            const unsigned sl = static_cast<unsigned>(pl & 3u) * 8u, sh = static_cast<unsigned>(ph & 3u) * 8u;
-            uint32_t l[5], h[5];
+            uint32_t l0[5], l1[5], hh[5];
 #pragma unroll
-            for (int i = 0; i < 5; ++i) { l[i] = wl[i]; h[i] = wh[i]; }
-            const uint4 xc = *reinterpret_cast<const uint4*>(xs + blk * 256 + colbase);
-            const uint32_t xw[4] = {xc.x, xc.y, xc.z, xc.w};
-            int isum = 0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const uint32_t lw = __funnelshift_r(l[i], l[i + 1], sl);
-              const uint32_t hw = __funnelshift_r(h[i], h[i + 1], sh);
-              const uint32_t q = ((lw >> nib) & 0x0F0F0F0Fu) | (((hw >> hshift) & 0x03030303u) << 4);
-              isum = __dp4a(static_cast<int>(q), static_cast<int>(xw[i]), isum);
-            }
-            const int sc = static_cast<int8_t>(blk6[192 + t]);
+            for (int j = 0; j < 5; ++j) { l0[j] = w0[j]; l1[j] = w1[j]; hh[j] = wh[j]; }
+            const int8_t* scp = reinterpret_cast<const int8_t*>(blk6 + 192 + n_half * 8 + is);
+            const int sc0 = scp[0], sc1 = scp[2], sc2 = scp[4], sc3 = scp[6];
             const float d = h2f(*reinterpret_cast<const uint16_t*>(blk6 + 208));
-            acc += xd[blk] * d * static_cast<float>(sc) * static_cast<float>(isum - 32 * xsum[blk * 16 + t]);
+            int i0 = z0, i1 = z1, i2 = z2, i3 = z3;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t a0 = __funnelshift_r(l0[j], l0[j + 1], sh);
+              const uint32_t a1 = __funnelshift_r(l1[j], l1[j + 1], sh);
+              const uint32_t hw = __funnelshift_r(hh[j], hh[j + 1], sh);
+              const uint32_t q0 = (a0 & 0x0F0F0F0Fu) | ((hw << 4) & 0x30303030u);
+              const uint32_t q1 = (a1 & 0x0F0F0F0Fu) | ((hw << 2) & 0x30303030u);
+              const uint32_t q2 = ((a0 >> 4) & 0x0F0F0F0Fu) | (hw & 0x30303030u);
+              const uint32_t q3 = ((a1 >> 4) & 0x0F0F0F0Fu) | ((hw >> 2) & 0x30303030u);
+              i0 = __dp4a(static_cast<int>(q0), static_cast<int>(xa[j]), i0);
+              i1 = __dp4a(static_cast<int>(q1), static_cast<int>(xb[j]), i1);
+              i2 = __dp4a(static_cast<int>(q2), static_cast<int>(xc[j]), i2);
+              i3 = __dp4a(static_cast<int>(q3), static_cast<int>(xe[j]), i3);
+            }
+            // |sc * i| < 2^7 * 2^18 and four of them: the scaled sum of the quarter block is exact in int32
+            acc[i] += xdb * d * static_cast<float>(sc0 * i0 + sc1 * i1 + sc2 * i2 + sc3 * i3);
           }
         }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) acc += __shfl_down_sync(0xFFFFFFFFu, acc, off);
-        if (lane == 0) a.y[r0 + r] = acc;
+        static_assert(kHeadRows == 4, "the reduction below transposes four rows");
+        // lanes 0-15 take rows 0 and 1, lanes 16-31 rows 2 and 3; then lanes with bit 3 clear the first of the two
+        const bool hi16 = (lane & 16) != 0, hi8 = (lane & 8) != 0;
+        float s0 = hi16 ? acc[2] : acc[0], s1 = hi16 ? acc[3] : acc[1];
+        s0 += __shfl_xor_sync(0xFFFFFFFFu, hi16 ? acc[0] : acc[2], 16);
+        s1 += __shfl_xor_sync(0xFFFFFFFFu, hi16 ? acc[1] : acc[3], 16);
+        float t = hi8 ? s1 : s0;
+        t += __shfl_xor_sync(0xFFFFFFFFu, hi8 ? s0 : s1, 8);
+        t += __shfl_xor_sync(0xFFFFFFFFu, t, 4);
+        t += __shfl_xor_sync(0xFFFFFFFFu, t, 2);
+        t += __shfl_xor_sync(0xFFFFFFFFu, t, 1);
+        const int row = rb + (lane >> 3) * kHeadWarps;          // lanes 8i .. 8i+7 hold row i of the pass
+        if ((lane & 7) == 0 && row < nr) a.y[r0 + row] = t;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive_one(empty + s);
@@ -233,7 +270,7 @@ int gemv_q6(const void* w, const void* xq, float* y, int n_rows, int k, cudaStre
   const bool streamable = (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && row_bytes % 16 == 0 &&
                           row_bytes <= kHeadStageBytes && n_rows >= 4 * sms;
   if (!streamable) return launch_head(gemv_q6_direct_kernel, dim3((n_rows + 7) / 8), 256, 0, stream, a);
-  a.rows_per_stage = kHeadStageBytes / row_bytes;
+  a.rows_per_stage = std::min(kHeadWarps * kHeadRows, kHeadStageBytes / row_bytes);
   const int stage_bytes = (a.rows_per_stage * row_bytes + 127) & ~127;
   const size_t smem = 128 + static_cast<size_t>(kHeadStages) * stage_bytes + head_x_bytes(a.nb);
   if (smem > 227 * 1024) return launch_head(gemv_q6_direct_kernel, dim3((n_rows + 7) / 8), 256, 0, stream, a);
@@ -249,11 +286,17 @@ int gemv_q6(const void* w, const void* xq, float* y, int n_rows, int k, cudaStre
 // -3.4e38 (that sentinel, -inf, NaN) is never picked, and when fewer than k values qualify the rest
 // of the output is (-3.4e38, -1). k is capped at 64. The logits are not modified.
 //
-// Phase 1: one WARP per 2048-value segment, the segment in registers (64 values per lane, value i
-// of lane l is element 32 * i + l, so a lane's values ascend in index). A round is two warp
-// reductions - the largest order-preserving key, then the lowest index holding it - and only the
-// winning lane rescans its registers. No shared memory, no CTA barrier. Phase 2: one CTA merges
-// the segments' candidates the same way, eight warps first, then one.
+// Both phases merge sorted runs: a candidate becomes one 64-bit word - the value's order-preserving
+// key above the complement of its index - so that descending order of the words IS the output order
+// (larger value first, lower index first among equals) and an entry that never qualifies is the word
+// 0. A run is 64 words in descending order held by one warp; the 64 largest of two runs are a
+// lane-wise maximum against the reversed partner plus a six-step bitonic merge, all in shuffles.
+// Phase 1: a CTA of 32 warps per 2048-value segment, each warp sorts 64 values, five rounds of
+// pairwise selection leave the segment's best 64. Phase 2: one CTA does the same over the segments'
+// candidate lists (up to 128 segments). Values are read back from the logits by index, so what is
+// returned are the caller's own bits. (Selection by repeated arg-max - a warp per segment, k rounds
+// of two warp reductions and a rescan - is kept for more than 128 segments; it took 110 us for
+// 151,936 logits and k = 40, as slow as the reference's kernels.)
 constexpr float kTopkNone = -3.4e38f;
 constexpr int kTopkSeg = 2048;               // the reference's segment size: the caller's scratch is sized by it
 constexpr int kTopkPerLane = kTopkSeg / 32;
@@ -296,6 +339,146 @@ __device__ __forceinline__ void warp_topk(float (&v)[PER], IndexOf index_of, int
       out_i[it] = win;
       rescan();
     }
+  }
+}
+
+__device__ __forceinline__ unsigned long long topk_word(float x, int index) {
+  if (!(x > kTopkNone)) return 0ull;             // NaN and anything at or below the sentinel never qualify
+  const unsigned key = static_cast<unsigned>(order_key(x)) ^ 0x80000000u;
+  return (static_cast<unsigned long long>(key) << 32) | static_cast<unsigned>(~index);
+}
+
+// A run of 64 words lives in one warp: lane l holds elements l and l + 32 (x[0], x[1]).
+__device__ __forceinline__ unsigned long long shfl64(unsigned long long v, int src) {
+  const unsigned lo = __shfl_sync(0xFFFFFFFFu, static_cast<unsigned>(v), src);
+  const unsigned hi = __shfl_sync(0xFFFFFFFFu, static_cast<unsigned>(v >> 32), src);
+  return (static_cast<unsigned long long>(hi) << 32) | lo;
+}
+// One compare-exchange step at distance `stride` < 32 inside both halves; desc0 / desc1: the direction
+// of this lane's element in x[0] / x[1]
+__device__ __forceinline__ void run_step(unsigned long long (&x)[2], int stride, bool desc0, bool desc1, int lane) {
+  const bool lower = (lane & stride) == 0;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const unsigned long long y = shfl64(x[j], lane ^ stride);
+    const bool keep_max = lower == (j == 0 ? desc0 : desc1);
+    x[j] = keep_max ? (x[j] > y ? x[j] : y) : (x[j] < y ? x[j] : y);
+  }
+}
+// Bitonic run (first half descending, second ascending, or any bitonic order) -> descending run
+__device__ __forceinline__ void run_merge_desc(unsigned long long (&x)[2], int lane) {
+  const unsigned long long a = x[0], b = x[1];
+  x[0] = a > b ? a : b;
+  x[1] = a > b ? b : a;
+#pragma unroll
+  for (int stride = 16; stride > 0; stride >>= 1) run_step(x, stride, true, true, lane);
+}
+// Any 64 words -> descending run
+__device__ __forceinline__ void run_sort_desc(unsigned long long (&x)[2], int lane) {
+#pragma unroll
+  for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      // element index i = lane + 32 j: bit `size` of i is bit `size` of the lane below 32, and j at 32
+      const bool d0 = size < 32 ? (lane & size) == 0 : true;
+      const bool d1 = size < 32 ? (lane & size) == 0 : false;
+      run_step(x, stride, d0, d1, lane);
+    }
+  }
+  run_merge_desc(x, lane);
+}
+// The 64 largest words of two descending runs, as a descending run: element i of the one against
+// element 63 - i of the other leaves a bitonic run that holds them.
+__device__ __forceinline__ void run_select(unsigned long long (&a)[2], const unsigned long long (&b)[2], int lane) {
+  const unsigned long long b1 = shfl64(b[1], 31 - lane), b0 = shfl64(b[0], 31 - lane);
+  a[0] = a[0] > b1 ? a[0] : b1;
+  a[1] = a[1] > b0 ? a[1] : b0;
+  run_merge_desc(a, lane);
+}
+
+// grid: one CTA of 32 warps per segment. Every warp sorts 64 values, then five rounds halve the runs.
+__global__ void __launch_bounds__(1024) topk_seg_sort_kernel(const float* __restrict__ logits, float* __restrict__ seg_v,
+                                                            int* __restrict__ seg_i, int n, int k) {
+  __shared__ unsigned long long runs[32][64];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int base = blockIdx.x * kTopkSeg + warp * 64;
+  unsigned long long x[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int gi = base + lane + 32 * j;
+    x[j] = gi < n ? topk_word(__ldg(logits + gi), gi) : 0ull;
+  }
+  run_sort_desc(x, lane);
+  runs[warp][lane] = x[0];
+  runs[warp][lane + 32] = x[1];
+  for (int r = 0; r < 5; ++r) {
+    __syncthreads();
+    if (warp < (16 >> r)) {
+      const int sa = warp << (r + 1), sb = sa + (1 << r);
+      unsigned long long a[2] = {runs[sa][lane], runs[sa][lane + 32]};
+      const unsigned long long b[2] = {runs[sb][lane], runs[sb][lane + 32]};
+      run_select(a, b, lane);
+      runs[sa][lane] = a[0];
+      runs[sa][lane + 32] = a[1];
+    }
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    const unsigned long long w = runs[0][j];
+    const int gi = w != 0ull ? static_cast<int>(~static_cast<unsigned>(w)) : -1;
+    seg_i[static_cast<size_t>(blockIdx.x) * k + j] = gi;
+    seg_v[static_cast<size_t>(blockIdx.x) * k + j] = gi >= 0 ? __ldg(logits + gi) : kTopkNone;
+  }
+}
+
+// One CTA merges the candidates of up to 128 segments: a segment's k candidates are a descending run
+// already. The first round reads pairs of runs from global memory, six more halve the 64 that remain.
+__global__ void __launch_bounds__(1024) topk_merge_sort_kernel(const float* __restrict__ logits,
+                                                              const float* __restrict__ seg_v,
+                                                              const int* __restrict__ seg_i, float* __restrict__ out_v,
+                                                              int* __restrict__ out_i, int nseg, int k) {
+  __shared__ unsigned long long runs[64][64];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  auto load_run = [&](int seg, unsigned long long (&x)[2]) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int e = lane + 32 * j;
+      x[j] = 0ull;
+      if (seg < nseg && e < k) {
+        const int gi = seg_i[static_cast<size_t>(seg) * k + e];
+        if (gi >= 0) x[j] = topk_word(seg_v[static_cast<size_t>(seg) * k + e], gi);
+      }
+    }
+  };
+  for (int pr = warp; pr < 64; pr += 32) {
+    unsigned long long a[2], b[2];
+    load_run(2 * pr, a);
+    load_run(2 * pr + 1, b);
+    run_select(a, b, lane);
+    runs[pr][lane] = a[0];
+    runs[pr][lane + 32] = a[1];
+  }
+  for (int r = 0; r < 6; ++r) {
+    __syncthreads();
+    if (warp < (32 >> r)) {
+      const int sa = warp << (r + 1), sb = sa + (1 << r);
+      unsigned long long a[2] = {runs[sa][lane], runs[sa][lane + 32]};
+      const unsigned long long b[2] = {runs[sb][lane], runs[sb][lane + 32]};
+      run_select(a, b, lane);
+      runs[sa][lane] = a[0];
+      runs[sa][lane + 32] = a[1];
+    }
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    const unsigned long long w = runs[0][j];
+    const int gi = w != 0ull ? static_cast<int>(~static_cast<unsigned>(w)) : -1;
+    out_i[j] = gi;
+    out_v[j] = gi >= 0 ? __ldg(logits + gi) : kTopkNone;
   }
 }
 
@@ -445,6 +628,16 @@ SGR_API int sgr_topk_select_f32_2p(const float* logits, float* seg_v, int* seg_i
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cfg.stream = s;
+  if (nseg <= 128) {
+    cfg.blockDim = dim3(1024);
+    cfg.gridDim = dim3(nseg);
+    if (cudaLaunchKernelEx(&cfg, topk_seg_sort_kernel, logits, seg_v, seg_i, n, k) != cudaSuccess) return kErrLaunch;
+    cfg.gridDim = dim3(1);
+    return cudaLaunchKernelEx(&cfg, topk_merge_sort_kernel, logits, static_cast<const float*>(seg_v),
+                              static_cast<const int*>(seg_i), out_v, out_i, nseg, k) == cudaSuccess
+               ? kOk
+               : kErrLaunch;
+  }
   cfg.blockDim = dim3(64);                        // two segments per CTA: the segments spread over the SMs
   cfg.gridDim = dim3((nseg + 1) / 2);
   if (cudaLaunchKernelEx(&cfg, topk_seg_kernel, logits, seg_v, seg_i, n, k) != cudaSuccess) return kErrLaunch;
