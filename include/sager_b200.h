@@ -275,8 +275,8 @@ typedef struct sgr_moe_layer {
   long long tab_stride;
   /* Expert parallelism with both exchanges done by the layer's own kernels over peer memory (all
    * NULL / 0: off). ep_flags[p] is this rank's address of an arrival word of rank p, set to
-   * *ep_step * ep_mul + ep_add by one st.release.sys of the kernel's last CTA (it follows an
-   * acq_rel count of the CTAs that stored; no other system-scope fence) once the data are there.
+   * *ep_step * ep_mul + ep_add by the kernel's last CTA (an acq_rel count of the CTAs that stored, one
+   * system-scope fence, then the words as relaxed stores) once the data are there.
    *   home side (stages 1 | 8 with xq_out = the record block of ep_rec_bytes per row): after the
    *     selection the records are stored into ep_dst[p] (this rank's slot in rank p's receive
    *     buffer) for every p < ep_world, then the owners' words are set;

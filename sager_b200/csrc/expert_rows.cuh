@@ -749,14 +749,13 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
   if (L.ep_out != nullptr) {
     // Owner side of an expert-parallel layer: the rows went straight into the home ranks' buffers;
     // the last CTA to finish tells the home ranks.
-    // (CTA barrier, then one thread's acquire-release count; the release stores are cumulative)
+    // (CTA barrier, then one thread's acquire-release count; its system-scope fence is cumulative)
     rs_consumers_sync();
     if (tid == 0) {
       if (atom_add_acq_rel(&L.cnt[11], 1u) == gridDim.x - 1) {
         L.cnt[11] = 0u;
         const unsigned v = *L.ep_step * L.ep_mul + L.ep_add;
-        for (int p = 0; p < L.ep_world; ++p)
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(L.ep_flags[p]), "r"(v) : "memory");
+        set_arrival_words(L.ep_flags, L.ep_world, v);
       }
     }
   }
