@@ -652,29 +652,34 @@ def run_tc_bench(args, device):
         x = torch.randn(tok, k, generator=g, device=device).half()
         y = torch.zeros(tok, rows, dtype=torch.float16, device=device)
 
-        def sweep():
-            for c in range(copies):
-                ops.tc_gemm_f16_raw(w[c], x, y, rows, k, tok)
-        sweep()
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        def timed(sweep):
             sweep()
-        for _ in range(max(args.warmup, 3)):
-            graph.replay()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            graph.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / (args.steps * copies)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                sweep()
+            for _ in range(max(args.warmup, 3)):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e3 / (args.steps * copies)
+
+        us = timed(lambda: [ops.tc_gemm_f16_raw(w[c], x, y, rows, k, tok) for c in range(copies)])
+        # what the reference calls at this point (cublasGemmEx, fp16 operands, fp32 accumulate,
+        # src/kernels/cuda/tc_gemm.cu:193-199), reached through torch: a baseline, not on any product path
+        y_lib = torch.zeros(tok, rows, dtype=torch.float16, device=device)
+        lib_us = timed(lambda: [torch.mm(x, w[c].t(), out=y_lib) for c in range(copies)])
         flops = 2.0 * rows * k * tok
         nbytes = 2.0 * (rows * k + tok * k + tok * rows)
         out.append({"rows": rows, "k": k, "tokens": tok, "us": us, "tflops": flops / us / 1e6,
                     "tensor_frac": flops / us / 1e6 / peak_tf, "gbs": nbytes / us / 1e3,
-                    "hbm_frac": nbytes / us / 1e3 / peak_bw, "weight_copies": copies})
+                    "hbm_frac": nbytes / us / 1e3 / peak_bw, "weight_copies": copies,
+                    "library_gemm_us": lib_us})
     clocks = sampler.stop()
     head = out[0]
     line = {
