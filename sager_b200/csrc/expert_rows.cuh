@@ -56,7 +56,17 @@ constexpr int kXBytes = kXCodes + kTok * 16 + kTok * 16;
 constexpr int kStageBytes = (kWBytes + kXBytes + 127) & ~127;
 constexpr int kHq = 288;                        // padded Q8_K block of h: d | 12 bytes | 256 codes | 8 sums
 constexpr int kHdr = 4096;
-constexpr size_t kSmem = kHdr + static_cast<size_t>(kStageCount) * kStageBytes;
+// The plan of a layer, built by every CTA for itself when the routing was made by this call's own
+// route kernel: row masks [E] | offsets [E + 1] | scan scratch | tile records | rows of the slots | slot
+// of every route. One round trip for the routing and a few barriers per CTA, all CTAs at once, instead
+// of one CTA planning in global memory while 147 wait (8 us per layer at 64 rows).
+constexpr int kPlanExperts = 256, kPlanRoutes = 512;
+constexpr int kPlanTiles = kPlanExperts + kPlanRoutes / kTok + 8;     // a tile per expert, per further 16 rows, shared expert's
+constexpr int kPlanOffMask = 0, kPlanOffOff = kPlanExperts * 8, kPlanOffScan = kPlanOffOff + 1152;
+constexpr int kPlanOffRec = kPlanOffScan + 512, kPlanOffRows = kPlanOffRec + kPlanTiles * 16;
+constexpr int kPlanOffSlot = kPlanOffRows + kPlanRoutes * 4;
+constexpr int kPlanBytes = (kPlanOffSlot + kPlanRoutes * 4 + 127) & ~127;
+constexpr size_t kSmem = kHdr + kPlanBytes + static_cast<size_t>(kStageCount) * kStageBytes;
 constexpr int kGateUpPairs = 128;               // pairs per gate/up group
 constexpr int kDownRows = 256;                  // rows per down group
 constexpr int kFullArrivals = 1 + kXThreads;      // weight warp: one arrival; activation warps: a thread's copies landed
@@ -216,6 +226,97 @@ __device__ __forceinline__ void quantize_h_block(const LayerDev& L, int hrow0, i
   }
 }
 
+// Every thread of the CTA: the plan of build_plan (moe_layer.cu) in shared memory - same masks, same
+// tile order (shared expert's tiles, tiles of more than half a tile's rows, the rest, each in expert
+// order), same slots. CTA 0 also silences rows with ids outside [0, E) as moe_dispatch_scan does
+// (moe.cu:385-398 of the reference) and leaves the counts in meta. Returns the number of tiles.
+__device__ __forceinline__ int build_plan_shared(const LayerDev& L, unsigned char* ps, int tid) {
+  unsigned long long* mask = reinterpret_cast<unsigned long long*>(ps + kPlanOffMask);
+  int* off_s = reinterpret_cast<int*>(ps + kPlanOffOff);
+  int* scan = reinterpret_cast<int*>(ps + kPlanOffScan);          // [3][40]: warp totals of rows, tiles, heavy tiles; [120]: bad ids
+  int4* rec_s = reinterpret_cast<int4*>(ps + kPlanOffRec);
+  int* rows_s = reinterpret_cast<int*>(ps + kPlanOffRows);
+  int* slot_s = reinterpret_cast<int*>(ps + kPlanOffSlot);
+  const int lane = tid & 31, wp = tid >> 5;
+  const int total = L.n * L.K;
+  // (the masks and the count of bad ids were cleared before the wait for the route kernel)
+  int my_e = -1, my_r = 0;
+  if (tid < total) {                            // kPlanRoutes <= kThreads: a route per thread
+    my_r = tid / L.K;
+    const int kk = tid - my_r * L.K;
+    my_e = __ldcg(L.idx + static_cast<size_t>(my_r) * L.rstride + kk);
+    if (my_e < 0 || my_e >= L.E) {
+      if (blockIdx.x == 0) {
+        for (int q = 0; q <= L.K; ++q) L.w[static_cast<size_t>(my_r) * L.rstride + q] = 0.f;
+        atomicAdd(&scan[120], 1);
+      }
+      my_e = -1;
+    } else if (my_e >= L.e_lo && my_e < L.e_hi) {
+      atomicOr(&mask[my_e], 1ull << my_r);
+    } else {
+      my_e = -1;
+    }
+  }
+  __syncthreads();
+  auto is_heavy = [](int rows_in_tile) { return 2 * rows_in_tile > kTok; };
+  int c = 0, t = 0, h = 0;
+  if (tid < L.E) {
+    c = __popcll(mask[tid]);
+    t = (c + kTok - 1) / kTok;
+    h = c / kTok + (is_heavy(c % kTok) ? 1 : 0);
+  }
+  int ic = c, it = t, ih = h;                   // inclusive scans inside the warps that hold experts
+  if (tid < kPlanExperts) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int uc = __shfl_up_sync(0xFFFFFFFFu, ic, o), ut = __shfl_up_sync(0xFFFFFFFFu, it, o);
+      const int uh = __shfl_up_sync(0xFFFFFFFFu, ih, o);
+      if (lane >= o) { ic += uc; it += ut; ih += uh; }
+    }
+    if (lane == 31) { scan[wp] = ic; scan[40 + wp] = it; scan[80 + wp] = ih; }
+  }
+  __syncthreads();
+  int rows_total = 0, tiles_total = 0, heavy_total = 0, pc = 0, pt = 0, phv = 0;
+#pragma unroll
+  for (int w = 0; w < kPlanExperts / 32; ++w) {
+    if (w < wp) { pc += scan[w]; pt += scan[40 + w]; phv += scan[80 + w]; }
+    rows_total += scan[w]; tiles_total += scan[40 + w]; heavy_total += scan[80 + w];
+  }
+  const int sh_tiles = (L.sh[0] != nullptr && L.sh_hi > L.sh_lo) ? (L.sh_hi - L.sh_lo + kTok - 1) / kTok : 0;
+  if (tid < L.E) {
+    const int ar = pc + ic - c;                 // exclusive prefixes of this expert
+    int at_heavy = sh_tiles + (phv + ih - h), at_light = sh_tiles + heavy_total + ((pt + it - t) - (phv + ih - h));
+    off_s[tid] = ar;
+    for (int t0 = 0; t0 < c; t0 += kTok) {
+      const int ct = min(kTok, c - t0);
+      const int at = is_heavy(ct) ? at_heavy++ : at_light++;
+      rec_s[at] = make_int4(tid, ct, ar + t0, ar + t0);
+    }
+  }
+  if (tid == 0) off_s[L.E] = rows_total;
+  if (tid < sh_tiles) {
+    const int t0 = tid * kTok;
+    rec_s[tid] = make_int4(L.E, min(kTok, L.sh_hi - L.sh_lo - t0), L.n_max * L.K + L.sh_lo + t0, L.sh_lo + t0);
+  }
+  __syncthreads();
+  if (tid < total) {
+    int pos = -1;
+    if (my_e >= 0) {
+      pos = off_s[my_e] + __popcll(mask[my_e] & ((1ull << my_r) - 1ull));
+      rows_s[pos] = my_r;
+    }
+    slot_s[tid] = pos;
+  }
+  if (blockIdx.x == 0 && tid == 0) {
+    L.meta[0] = rows_total;
+    L.meta[1] = tiles_total + sh_tiles;
+    L.meta[2] = scan[120];
+    L.meta[3] = sh_tiles;
+  }
+  __syncthreads();
+  return tiles_total + sh_tiles;
+}
+
 __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev L) {
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -226,7 +327,8 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
   Done* done_q = reinterpret_cast<Done*>(smem + 640);               // [kDoneSlots]
   volatile unsigned* done_tail = reinterpret_cast<volatile unsigned*>(smem + 136);   // groups handed over
   volatile unsigned* done_head = reinterpret_cast<volatile unsigned*>(smem + 140);   // groups taken by the finisher
-  unsigned char* stages = smem + kHdr;
+  unsigned char* plan_s = smem + kHdr;
+  unsigned char* stages = smem + kHdr + kPlanBytes;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
@@ -240,15 +342,26 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     *reinterpret_cast<volatile unsigned*>(smem + 144) = 0u;
     fence_barrier_init();
   }
+  if (L.plan_in_kernel) {           // shared memory of the plan that must start out clear
+    for (int e = tid; e < kPlanExperts; e += kThreads) reinterpret_cast<unsigned long long*>(plan_s + kPlanOffMask)[e] = 0ull;
+    if (tid == 0) reinterpret_cast<int*>(plan_s + kPlanOffScan)[120] = 0;
+  }
   __syncthreads();
-  pdl_wait();                       // plan, routing and quantised rows come from the route kernel
+  pdl_wait();                       // routing and quantised rows (and, without a plan of its own, the plan) come from the route kernel
   pdl_launch_dependents();
 
   Sched sc;
   sc.gpt_gu = L.FF / kGateUpPairs; sc.gpt_dn = L.H / kDownRows;      // groups per tile
   sc.nbh = L.nbh; sc.nbf = L.nbf;
-  sc.n_gu = L.meta[1] * sc.gpt_gu;
-  sc.total = sc.n_gu + L.meta[1] * sc.gpt_dn;
+  // the plan: this CTA's own copy in shared memory, or the one a plan kernel left in the workspace
+  const bool plan_own = L.plan_in_kernel != 0;
+  const int n_tiles = plan_own ? build_plan_shared(L, plan_s, tid) : L.meta[1];
+  const int4* rec_p = plan_own ? reinterpret_cast<const int4*>(plan_s + kPlanOffRec) : L.rec;
+  const int* rows_p = plan_own ? reinterpret_cast<const int*>(plan_s + kPlanOffRows) : L.grows;
+  const int* slot_p = plan_own ? reinterpret_cast<const int*>(plan_s + kPlanOffSlot) : L.gslot;
+  auto tile_rec = [&](int tile) { return plan_own ? rec_p[tile] : __ldcg(rec_p + tile); };
+  sc.n_gu = n_tiles * sc.gpt_gu;
+  sc.total = sc.n_gu + n_tiles * sc.gpt_dn;
   const int rb_h = L.nbh * kW4, rb_f = L.nbf * kW4;
   GEntry* glist = reinterpret_cast<GEntry*>(smem + 2048);                       // [kListSlots] this CTA's groups
   volatile unsigned* g_pub = reinterpret_cast<volatile unsigned*>(smem + 144);  // entries of glist published
@@ -302,7 +415,8 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
       p.w1 = shared ? L.sh[1] : L.tab[L.tab_stride + p.rc.x];
       p.w2 = shared ? L.sh[2] : L.tab[2 * L.tab_stride + p.rc.x];
       p.row = 0;
-      if (p.g.kind == 0 && lane < p.rc.y) p.row = shared ? p.rc.w + lane : __ldcg(L.grows + p.rc.w + lane);
+      if (p.g.kind == 0 && lane < p.rc.y)
+        p.row = shared ? p.rc.w + lane : (plan_own ? rows_p[p.rc.w + lane] : __ldcg(rows_p + p.rc.w + lane));
       // a down group's activation rows are the tile's quantised h: seen complete here (acquire), the
       // activation warps need not look again (they run after this warp's publication of the entry)
       p.ready = p.g.kind == 1 ? ld_acquire(L.ready + p.g.tile) : 0u;
@@ -371,7 +485,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     int drawn = 0;                               // lane 0: the number last drawn
     bool id_ready = false;                       // ... which is that of the next group, not yet looked at
     if (cur.g.valid) {
-      cur.rc = __ldcg(L.rec + cur.g.tile);
+      cur.rc = tile_rec(cur.g.tile);
       load_ptrs(cur);
       patch(cur);
     }
@@ -466,7 +580,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
         nx.g = sc.decode(nx.id);
         id_ready = false;
         if (nx.g.valid) {
-          nx.rc = __ldcg(L.rec + nx.g.tile);
+          nx.rc = tile_rec(nx.g.tile);
           if (nx.g.kind == 1) {                  // a short group: have the number after it at hand when it starts
             if (lane == 0) drawn = static_cast<int>(atomicAdd(&L.cnt[10], 1u));
             id_ready = true;
@@ -651,7 +765,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     if (d_kind == 0) {
       if (d_mode == 1) {
         if (d.row0 == 0 && warp == 0 && lane == 0 && L.mail != nullptr) {
-          const int e = __ldcg(&L.rec[d.tile].x);
+          const int e = tile_rec(d.tile).x;
           if (e != L.E) {
             const int mi = atomicAdd(L.mail_n, 1);
             if (mi < L.E) L.mail[mi] = e;
@@ -745,7 +859,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     if (tid == 0) atomicExch(L.status, 5);
     return;
   }
-  combine_flat(L, blockIdx.x * kConsumers + tid, gridDim.x * kConsumers);
+  combine_flat(L, blockIdx.x * kConsumers + tid, gridDim.x * kConsumers, slot_p, plan_own);
   if (L.ep_out != nullptr) {
     // Owner side of an expert-parallel layer: the rows went straight into the home ranks' buffers;
     // the last CTA to finish tells the home ranks.

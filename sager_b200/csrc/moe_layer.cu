@@ -72,6 +72,7 @@ struct LayerDev {
   int n, H, FF, E, K, nbh, nbf;
   int e_lo, e_hi, sh_lo, sh_hi;
   int add_residual, routing_given, skip_plan;
+  int plan_in_kernel;  // the row-streaming kernel builds the plan itself, in shared memory, from the routing
   int rstride;     // elements between consecutive rows of idx / w (K+1 when packed)
   int xq_stride;   // bytes between consecutive Q8_K rows
   float shared_w;
@@ -420,6 +421,16 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
   }
   pdl_wait();
   pdl_launch_dependents();
+  if (L.plan_in_kernel && !L.skip_plan && blockIdx.x == 0 && blockIdx.y == 0) {
+    // the expert kernel builds its plan itself: all it needs from here are fresh counters (the
+    // previous kernel on this workspace has finished)
+    reset_tile_counters(L, tid, blockDim.x);
+    if (tid == 0) {
+      L.cnt[9] = 0u;
+      L.cnt[10] = static_cast<unsigned>(L.grid);
+      if (L.mail_n != nullptr) *L.mail_n = 0;
+    }
+  }
 
   // Q8_K rows of the tile (packed, and padded for the row-streaming kernel): block
   // b of the tile goes to warp b / gridDim.x of CTA b % gridDim.x
@@ -493,6 +504,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
     }
     return;
   }
+  if (L.plan_in_kernel) return;
   // last token tile plans
   __syncthreads();
   if (tid == 0) last_sh = atom_add_acq_rel(&L.cnt[8], 1u) == gridDim.y - 1 ? 1 : 0;
@@ -732,7 +744,7 @@ __device__ __forceinline__ void item_compute_dp4a(const unsigned char* w, int ws
 // grid at work: the routes of a token (slot, weight) are fetched eight at a time and their y rows
 // requested together, so an output costs two round trips to L2 instead of two per expert. Terms are
 // added in combine_rows' order (residual, experts in slot order, shared expert), so both give the same bits.
-__device__ __forceinline__ void combine_flat(const LayerDev& L, int gtid, int gthreads) {
+__device__ __forceinline__ void combine_flat(const LayerDev& L, int gtid, int gthreads, const int* gslot, bool gslot_shared) {
   const bool has_shared = L.sh[0] != nullptr;
   const int half = L.H >> 1;
   for (int idx = gtid; idx < L.n * half; idx += gthreads) {
@@ -752,7 +764,7 @@ __device__ __forceinline__ void combine_flat(const LayerDev& L, int gtid, int gt
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const bool in = k0 + j < L.K;
-        gs[j] = in ? __ldcg(L.gslot + tk * L.K + k0 + j) : -1;
+        gs[j] = in ? (gslot_shared ? gslot[tk * L.K + k0 + j] : __ldcg(gslot + tk * L.K + k0 + j)) : -1;
         w[j] = in ? __ldcg(wr + k0 + j) : 0.f;
       }
 #pragma unroll
@@ -1371,6 +1383,10 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
       L.xq_stride = L.nbh * kX8;
     }
   }
+  // the row-streaming kernel plans for itself when the routing is this call's own and the plan fits
+  // the shared memory set aside for it
+  L.plan_in_kernel = (use_rows && !a->routing_given && L.E <= rs::kPlanExperts &&
+                      a->n_max * a->n_used <= rs::kPlanRoutes) ? 1 : 0;
   if (use_rows && (!matrix_tmap(L.nbh * kW4, L.FF, a->workspace, L.tmap_gu) ||
                    !matrix_tmap(L.nbf * kW4, L.H, a->workspace, L.tmap_dn)))
     return kErrUnsupported;
