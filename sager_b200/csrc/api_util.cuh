@@ -21,4 +21,8 @@ inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 // Device address of the library's status word on the current device.
 int* status_word();
 
+// One Q4_K matrix over n_tok Q8_K rows on the int8 tensor-core kernel of the grouped GEMM
+// (grouped_gemm_i8.cu): y[t][r], fp16. xq 16-byte aligned.
+int gemm_i8_dense(const void* w, const void* xq, uint16_t* y, int n_tok, int n_rows, int k, cudaStream_t stream);
+
 }  // namespace sgr

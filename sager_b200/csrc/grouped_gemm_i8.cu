@@ -154,17 +154,26 @@ struct Item {
   const unsigned char* w;
 };
 
-// grid: one CTA per SM (or per item when there are fewer); item i = expert i / tiles, row tile i % tiles
+// grid: one CTA per SM (or per item when there are fewer); item i = expert i / tiles, row tile i % tiles.
+// With single_w the kernel serves ONE matrix over single_rows token rows (a dense projection, the shared
+// expert of a prefill chunk): item i = token pass i / tiles (128 rows each), row tile i % tiles.
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int* __restrict__ off,
                        const unsigned char* __restrict__ xq, uint16_t* __restrict__ y, int n_rows,
-                       int nb, int tiles, int n_items, int* status) {
+                       int nb, int tiles, int n_items, const unsigned char* single_w, int single_rows,
+                       int* status) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   auto item_at = [&](int it) {
     Item r;
     r.e = it / tiles;
     r.row0 = (it - r.e * tiles) * kGemmRows;
+    if (single_w != nullptr) {                   // r.e is the token pass
+      r.row_off = r.e * 2 * kGemmTok;
+      r.m_e = min(2 * kGemmTok, single_rows - r.row_off);
+      r.w = single_w;
+      return r;
+    }
     r.row_off = __ldg(off + r.e);
     r.m_e = __ldg(off + r.e + 1) - r.row_off;
     r.w = w_tab[r.e];
@@ -562,6 +571,30 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
 
 using namespace sgr;
 
+// y[t][r] = W[r][:] . xq[t][:] for one matrix and n_tok token rows on the same tensor-core kernel
+// (the shared expert of a prefill chunk: one "expert" that every row visits).
+int sgr::gemm_i8_dense(const void* w, const void* xq, uint16_t* y, int n_tok, int n_rows, int k, cudaStream_t stream) {
+  if (n_tok <= 0 || n_rows <= 0) return kOk;
+  if (!w || !xq || !y || k <= 0 || k % kQK != 0) return kErrArg;
+  if (reinterpret_cast<uintptr_t>(xq) & 15u) return kErrAlign;
+  auto kern = grouped_gemm_i8_kernel;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) != cudaSuccess)
+    return kErrLaunch;
+  int* status = status_word();
+  if (status == nullptr) return kErrLaunch;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    return kErrLaunch;
+  const int tiles = (n_rows + kGemmRows - 1) / kGemmRows;
+  const long long n_items = static_cast<long long>(tiles) * ((n_tok + 2 * kGemmTok - 1) / (2 * kGemmTok));
+  if (n_items > 0x7FFFFFFF) return kErrUnsupported;
+  kern<<<static_cast<unsigned>(n_items < sms ? n_items : sms), kGemmThreads, kGemmSmem, stream>>>(
+      nullptr, nullptr, static_cast<const unsigned char*>(xq), y, n_rows, k / kQK, tiles, static_cast<int>(n_items),
+      static_cast<const unsigned char*>(w), n_tok, status);
+  return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
 // y[off[e] + t][r] = W_e[r][:] . xq[off[e] + t][:] for every expert e and its rows
 // t < off[e+1] - off[e]; fp16 out, row length n_rows. w_tab[e] == null: zero rows.
 SGR_API int sgr_moe_grouped_gemm_i8(const void* const* w_tab, const int* off, const void* xq,
@@ -584,7 +617,7 @@ SGR_API int sgr_moe_grouped_gemm_i8(const void* const* w_tab, const int* off, co
   if (n_items > 0x7FFFFFFF) return kErrUnsupported;
   kern<<<static_cast<unsigned>(n_items < sms ? n_items : sms), kGemmThreads, kGemmSmem, as_stream(stream)>>>(
       reinterpret_cast<const unsigned char* const*>(w_tab), off, static_cast<const unsigned char*>(xq), y,
-      n_rows, k / kQK, tiles, static_cast<int>(n_items), status);
+      n_rows, k / kQK, tiles, static_cast<int>(n_items), nullptr, 0, status);
   return cudaPeekAtLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 

@@ -56,10 +56,23 @@ SGR_API int sgr_moe_layer_prefill(const sgr_moe_prefill* a, void* stream) {
   SGR_STEP(sgr_moe_grouped_gemm_i8(tab_d, a->off, a->hq, a->y_grouped, H, F, E, stream));
   SGR_STEP(sgr_scatter_routed_f16(a->expert_y, a->y_grouped, a->gslot, n, K, H, stream));
   if (shared) {
-    SGR_STEP(sgr_gemv2_q4_k_q8_f16out_mtok(a->shared_gate, a->shared_up, a->xq, a->sh_g, a->sh_u, F, H, n, stream));
+    // the shared expert is one expert that every row visits: the same tensor-core kernel as the routed
+    // ones when its row buffers allow 16-byte reads (the multi-token GEMV of the reference's sequence,
+    // gemv2_q4_k_q8_f16out_mtok, took 0.42 ms for gate and up of a 2048-row chunk)
+    const bool tc = ((reinterpret_cast<uintptr_t>(a->xq) | reinterpret_cast<uintptr_t>(a->sh_q)) & 15u) == 0;
+    if (tc) {
+      SGR_STEP(gemm_i8_dense(a->shared_gate, a->xq, a->sh_g, n, F, H, as_stream(stream)));
+      SGR_STEP(gemm_i8_dense(a->shared_up, a->xq, a->sh_u, n, F, H, as_stream(stream)));
+    } else {
+      SGR_STEP(sgr_gemv2_q4_k_q8_f16out_mtok(a->shared_gate, a->shared_up, a->xq, a->sh_g, a->sh_u, F, H, n, stream));
+    }
     SGR_STEP(sgr_silu_mul_f16(a->sh_g, a->sh_g, a->sh_u, n, F, stream));
     SGR_STEP(sgr_quantize_q8_k(a->sh_g, a->sh_q, static_cast<long long>(n) * F, stream));
-    SGR_STEP(sgr_gemv_q4_k_q8_f16out_mtok(a->shared_down, a->sh_q, a->sh_y, H, F, n, stream));
+    if (tc) {
+      SGR_STEP(gemm_i8_dense(a->shared_down, a->sh_q, a->sh_y, n, H, F, as_stream(stream)));
+    } else {
+      SGR_STEP(sgr_gemv_q4_k_q8_f16out_mtok(a->shared_down, a->sh_q, a->sh_y, H, F, n, stream));
+    }
     if (a->shared_gate_w != nullptr) {           // scalar gate sigmoid(w_sg . x) on the shared rows (layer.cpp:128-134)
       if (a->sgate == nullptr) return kErrArg;
       SGR_STEP(sgr_gemv_f32_out_f16x_batched(a->shared_gate_w, a->xn, a->sgate, 1, H, n, stream));
