@@ -290,6 +290,14 @@ typedef struct sgr_moe_layer {
   float* const* ep_out;
   const unsigned* ep_step;
   int ep_world, ep_rec_bytes, ep_home_rows, ep_mul, ep_add;
+  /* Expert parallelism, one launch less on the owner side: the route stage of this (home) call also
+   * re-arms the counters of a second workspace - that of the owner call which follows it on the same
+   * stream, made for rearm_n_max rows and otherwise this call's geometry - and clears that call's
+   * mailbox count. The owner call may then be issued as stages 2 | 4 | 128: no plan launch, every CTA of
+   * its expert kernel waits for the arrival words and plans for itself. NULL / 0: off. */
+  void* rearm_workspace;
+  int* rearm_mail_n;
+  int rearm_n_max;
 } sgr_moe_layer;
 
 size_t sgr_moe_layer_workspace_bytes(int n_max, int hidden, int n_ff, int n_expert, int n_used);

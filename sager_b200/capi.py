@@ -107,6 +107,7 @@ class MoeLayerArgs(C.Structure):
         ("ep_dst", C.c_void_p), ("ep_flags", C.c_void_p), ("ep_out", C.c_void_p), ("ep_step", C.c_void_p),
         ("ep_world", C.c_int), ("ep_rec_bytes", C.c_int), ("ep_home_rows", C.c_int), ("ep_mul", C.c_int),
         ("ep_add", C.c_int),
+        ("rearm_workspace", C.c_void_p), ("rearm_mail_n", C.c_void_p), ("rearm_n_max", C.c_int),
     ]
 
 

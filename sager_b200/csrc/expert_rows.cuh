@@ -355,6 +355,20 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
   sc.nbh = L.nbh; sc.nbf = L.nbf;
   // the plan: this CTA's own copy in shared memory, or the one a plan kernel left in the workspace
   const bool plan_own = L.plan_in_kernel != 0;
+  if (plan_own && L.wait_flags != nullptr) {
+    // owner side of an expert-parallel layer: the routing is in the records the home ranks store into
+    // this rank's memory; every CTA waits (bounded) for their arrival words. A word that never comes
+    // raises the status; the CTA then goes on with the records of an earlier step (valid memory).
+    if (tid < L.wait_count) {
+      const unsigned want = *L.wait_step * L.wait_mul + L.wait_add;
+      unsigned it = 0, v;
+      do {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(L.wait_flags + tid) : "memory");
+      } while (static_cast<int>(v - want) < 0 && ++it < L.wait_limit && (__nanosleep(64), true));
+      if (static_cast<int>(v - want) < 0) atomicExch(L.status, 8);
+    }
+    __syncthreads();
+  }
   const int n_tiles = plan_own ? build_plan_shared(L, plan_s, tid) : L.meta[1];
   const int4* rec_p = plan_own ? reinterpret_cast<const int4*>(plan_s + kPlanOffRec) : L.rec;
   const int* rows_p = plan_own ? reinterpret_cast<const int*>(plan_s + kPlanOffRows) : L.grows;

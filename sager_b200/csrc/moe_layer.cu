@@ -73,6 +73,10 @@ struct LayerDev {
   int e_lo, e_hi, sh_lo, sh_hi;
   int add_residual, routing_given, skip_plan;
   int plan_in_kernel;  // the row-streaming kernel builds the plan itself, in shared memory, from the routing
+  // a second workspace whose counters this call's route stage re-arms (expert parallelism: the owner call that follows)
+  unsigned *rearm_cnt, *rearm_tile_cnt, *rearm_blk_cnt, *rearm_ready;
+  int* rearm_mail_n;
+  int rearm_tiles;
   int rstride;     // elements between consecutive rows of idx / w (K+1 when packed)
   int xq_stride;   // bytes between consecutive Q8_K rows
   float shared_w;
@@ -429,6 +433,20 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(const LayerDev 
       L.cnt[9] = 0u;
       L.cnt[10] = static_cast<unsigned>(L.grid);
       if (L.mail_n != nullptr) *L.mail_n = 0;
+    }
+  }
+  if (L.rearm_cnt != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
+    // the owner call that follows this one on the stream plans inside its expert kernel: its
+    // workspace is idle now (every earlier kernel of the stream has finished) and gets fresh counters
+    for (int i = tid; i < L.rearm_tiles; i += blockDim.x) {
+      L.rearm_tile_cnt[i] = 0u;
+      L.rearm_ready[i] = 0u;
+    }
+    for (int i = tid; i < L.rearm_tiles * L.nbf; i += blockDim.x) L.rearm_blk_cnt[i] = 0u;
+    if (tid == 0) {
+      L.rearm_cnt[9] = 0u;
+      L.rearm_cnt[10] = static_cast<unsigned>(L.grid);
+      if (L.rearm_mail_n != nullptr) *L.rearm_mail_n = 0;
     }
   }
 
@@ -1385,8 +1403,27 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
   }
   // the row-streaming kernel plans for itself when the routing is this call's own and the plan fits
   // the shared memory set aside for it
-  L.plan_in_kernel = (use_rows && !a->routing_given && L.E <= rs::kPlanExperts &&
-                      a->n_max * a->n_used <= rs::kPlanRoutes) ? 1 : 0;
+  const bool plan_fits = L.E <= rs::kPlanExperts && a->n_max * a->n_used <= rs::kPlanRoutes;
+  L.plan_in_kernel = (use_rows && !a->routing_given && plan_fits) ? 1 : 0;
+  if (stages & 128) {
+    // owner side of an expert-parallel layer without a plan launch: routing given in records of padded
+    // blocks, counters re-armed by the home call's route stage (rearm_workspace of that call)
+    if ((stages & 7) != 6 || !use_rows || !a->routing_given || !a->xq_in || !L.xq_padded || !plan_fits) return kErrUnsupported;
+    L.plan_in_kernel = 1;
+  }
+  if (a->rearm_workspace != nullptr) {
+    if (!(stages & 1) || a->routing_given || a->rearm_n_max <= 0 || a->rearm_n_max > kMaxRows ||
+        (reinterpret_cast<uintptr_t>(a->rearm_workspace) & 255u))
+      return kErrArg;
+    const WsLayout lay2 = ws_layout(a->rearm_n_max, a->hidden, a->n_ff, a->n_expert, a->n_used);
+    unsigned char* ws2 = static_cast<unsigned char*>(a->rearm_workspace);
+    L.rearm_cnt = reinterpret_cast<unsigned*>(ws2 + lay2.cnt);
+    L.rearm_tile_cnt = reinterpret_cast<unsigned*>(ws2 + lay2.tile_cnt);
+    L.rearm_blk_cnt = reinterpret_cast<unsigned*>(ws2 + lay2.blk_cnt);
+    L.rearm_ready = reinterpret_cast<unsigned*>(ws2 + lay2.ready);
+    L.rearm_tiles = a->rearm_n_max * a->n_used + a->rearm_n_max;
+    L.rearm_mail_n = a->rearm_mail_n;
+  }
   if (use_rows && (!matrix_tmap(L.nbh * kW4, L.FF, a->workspace, L.tmap_gu) ||
                    !matrix_tmap(L.nbf * kW4, L.H, a->workspace, L.tmap_dn)))
     return kErrUnsupported;
@@ -1429,7 +1466,7 @@ SGR_API int sgr_moe_layer_decode_stages(const sgr_moe_layer* a, int stages, void
 
   if ((stages & 6) && use_rows) {
     const int sms = L.grid;
-    if (!(stages & 1)) {
+    if (!(stages & 1) && !(stages & 128)) {
       rc = launch_pdl(rearm_kernel, dim3(1), 256, 0, s, L);
       if (rc != kOk) return rc;
     }

@@ -36,4 +36,4 @@ SGR_API int sgr_status(int clear) {
   return v;
 }
 
-SGR_API int sgr_abi_version(void) { return 3; }
+SGR_API int sgr_abi_version(void) { return 4; }

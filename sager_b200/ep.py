@@ -264,6 +264,12 @@ class EpStack:
         a.xq_padded = int(self.padded)
         a.ep_dst, a.ep_flags, a.ep_step = self._ptr(px.dst_recv), self._ptr(px.dst_flag_d), self._ptr(px.step)
         a.ep_world, a.ep_rec_bytes, a.ep_mul, a.ep_add = self.world, px.rec, mul, add
+        # the owner call below plans inside its expert kernel (no plan launch) when the records carry
+        # padded blocks and the plan fits shared memory; this call's route stage re-arms its counters
+        own_plan = self.padded and w.n_expert <= 256 and self.tokens * self.home.n_used <= 512
+        if own_plan:
+            a.rearm_workspace, a.rearm_mail_n = self._ptr(self.owner.ws), self._ptr(self.owner.mail_n)
+            a.rearm_n_max = self.owner.n_max
         L.call("sgr_moe_layer_decode_stages", C.byref(a), 1 | 8, sp)
         h0 = self.rank * self.n_home
         b = self.owner.args(self.tokens, None, None, self.tables[li], w.shared_ptrs(), out_f32=None,
@@ -278,7 +284,7 @@ class EpStack:
         b.xq_padded = int(self.padded)
         b.ep_out, b.ep_flags, b.ep_step = self._ptr(px.dst_back), self._ptr(px.dst_flag_r), self._ptr(px.step)
         b.ep_world, b.ep_home_rows, b.ep_mul, b.ep_add = self.world, self.n_home, mul, add
-        L.call("sgr_moe_layer_decode_stages", C.byref(b), 7, sp)
+        L.call("sgr_moe_layer_decode_stages", C.byref(b), (6 | 128) if own_plan else 7, sp)
         n = self.n_home * w.hidden
         L.call("sgr_ep_reduce_add_f16_wait", self._ptr(self.x), self._ptr(px.back), self.world, n, n,
                self._ptr(px.flag_r), self._ptr(px.step), mul, add, sp)
@@ -438,7 +444,7 @@ def run_ep_bench(args, rank, world, device):
         "dtype": "int8 dots, fp32 accumulate", "data": "synthetic",
         "config": dict(bench.workload_config(world), layers=layers_n, tokens=tokens, zipf_alpha=alpha,
                        exchange=(("records and partial sums stored into peer memory over NVLink by the layer's own "
-                                  "kernels (route and expert kernel), arrival words, 4 launches per layer") if st.fused else
+                                  "kernels (route and expert kernel), arrival words, 3 launches per layer (route, experts with their own plan, home reduction)") if st.fused else
                                  ("records and partial sums stored into peer memory over NVLink by copy kernels "
                                   "between the layer's launches, arrival words, 6 launches per layer")) if st.peer is not None
                        else "2 NCCL all-to-alls per layer, fixed capacity, captured in the step graph"),

@@ -114,6 +114,12 @@ class MoeWeights:
     def table(self, absent=()):
         """int64 [3][E] device pointer table; experts outside this shard and `absent`
         ones get null entries."""
+        # Callers hand the table to the library by its device address only, so the tensor must outlive
+        # every launch that reads it: tables are kept with the weights (one per set of absent experts).
+        key = tuple(sorted(absent))
+        cache = self.__dict__.setdefault("_tables", {})
+        if key in cache:
+            return cache[key]
         base = self.blob.data_ptr()
         t = torch.zeros(3, self.n_expert, dtype=torch.int64)
         o = [0, self.gu_bytes, 2 * self.gu_bytes]
@@ -121,7 +127,8 @@ class MoeWeights:
             t[m, self.lo:self.hi] = base + torch.arange(self.hi - self.lo, dtype=torch.int64) * self.expert_bytes + o[m]
         for e in absent:
             t[:, e] = 0
-        return t.to(self.blob.device)
+        cache[key] = t.to(self.blob.device)
+        return cache[key]
 
     def shared_ptrs(self):
         base = self.blob.data_ptr() + (self.hi - self.lo) * self.expert_bytes

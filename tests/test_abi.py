@@ -14,7 +14,7 @@ def test_library_builds_and_exports_header_symbols():
     assert os.path.exists(path)
     lib = capi.Lib(path)            # raises if a declared symbol is missing
     assert len(lib.protos) >= 39
-    assert lib.raw("sgr_abi_version")() == 3
+    assert lib.raw("sgr_abi_version")() == 4
     out = subprocess.run(["nm", "-D", "--defined-only", path], capture_output=True, text=True).stdout
     exported = {ln.split()[-1] for ln in out.splitlines() if " T " in ln}
     assert set(lib.protos) <= exported

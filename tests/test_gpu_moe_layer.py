@@ -478,8 +478,9 @@ def test_token_kernel_agrees_with_the_two_launch_path(full_w):
     assert lib().raw("sgr_status")(0) == 0
 
 
+@pytest.mark.parametrize("own_plan", [False, True])
 @pytest.mark.parametrize("tokens", [8, 64])
-def test_fused_exchange_entry_points_with_one_rank(full_w, tokens):
+def test_fused_exchange_entry_points_with_one_rank(full_w, tokens, own_plan):
     """The expert-parallel layer with the exchanges done by its own kernels, this device being its
     own only peer: the route kernel stores the records into the 'owner's' receive slot and sets the
     arrival word, the owner call waits for it and stores its rows into the 'home rank's' return
@@ -503,23 +504,40 @@ def test_fused_exchange_entry_points_with_one_rank(full_w, tokens):
     L, sp = lib(), stream_ptr()
     home = MoeLayerRunner(tokens, H, w.n_ff, w.n_expert, k, DEV)
     x = x16.clone()
-    a = home.args(tokens, x16, w.router, w.table(), None, x_f16=x)
+    tab = w.table()                               # kept alive: the calls hold its device address only
+    a = home.args(tokens, x16, w.router, tab, None, x_f16=x)
     a.xq_out, a.xq_stride, a.xq_padded = ptr(send), rec, 1
     a.route_idx, a.route_w, a.route_stride = ptr(send, idx_off), ptr(send, w_off), rec // 4
     a.ep_dst, a.ep_flags, a.ep_step = ptr(dst_recv), ptr(fl_d), ptr(step)
     a.ep_world, a.ep_rec_bytes, a.ep_mul, a.ep_add = 1, rec, 3, 2
-    L.call("sgr_moe_layer_decode_stages", C.byref(a), 1 | 8, sp)
     owner = MoeLayerRunner(64, H, w.n_ff, w.n_expert, k, DEV)
-    b = owner.args(tokens, None, None, w.table(), w.shared_ptrs(), xq_in=recv, routing_given=True, no_residual=True)
+    if own_plan:
+        # the owner call plans inside its expert kernel (stage bit 7, no plan launch); the home call's
+        # route stage re-arms the owner workspace's counters
+        a.rearm_workspace, a.rearm_mail_n, a.rearm_n_max = ptr(owner.ws), ptr(owner.mail_n), 64
+    L.call("sgr_moe_layer_decode_stages", C.byref(a), 1 | 8, sp)
+    b = owner.args(tokens, None, None, tab, w.shared_ptrs(), xq_in=recv, routing_given=True, no_residual=True)
     b.xq_stride, b.route_stride, b.xq_padded = rec, rec // 4, 1
     b.route_idx, b.route_w = ptr(recv, idx_off), ptr(recv, w_off)
     b.wait_flags, b.wait_step, b.wait_count, b.wait_mul, b.wait_add = ptr(flags), ptr(step), 1, 3, 2
     b.ep_out, b.ep_flags, b.ep_step = ptr(dst_back), ptr(fl_r), ptr(step)
     b.ep_world, b.ep_home_rows, b.ep_mul, b.ep_add = 1, tokens, 3, 2
-    L.call("sgr_moe_layer_decode_stages", C.byref(b), 7 | 16, sp)
+    def issue():
+        L.call("sgr_moe_layer_decode_stages", C.byref(a), 1 | 8, sp)
+        L.call("sgr_moe_layer_decode_stages", C.byref(b), (6 | 16 | 128) if own_plan else (7 | 16), sp)
+        L.call("sgr_ep_reduce_add_f16_wait", ptr(x), ptr(back), 1, tokens * H, tokens * H, ptr(flags, 4), ptr(step), 3, 2, sp)
+    L.call("sgr_moe_layer_decode_stages", C.byref(b), (6 | 16 | 128) if own_plan else (7 | 16), sp)
     L.call("sgr_ep_reduce_add_f16_wait", ptr(x), ptr(back), 1, tokens * H, tokens * H, ptr(flags, 4), ptr(step), 3, 2, sp)
     torch.cuda.synchronize()
     assert flags.tolist() == [17, 17]
+    if own_plan:                                  # a second layer on the same workspaces: the re-armed counters hold
+        x_once = x.clone()
+        x.copy_(x16)
+        step.fill_(6)
+        issue()
+        torch.cuda.synchronize()
+        assert flags.tolist() == [20, 20]
+        assert torch.equal(x, x_once)
     assert torch.equal(recv, send)
     assert rel(x.float().cpu().numpy(), x_full.float().cpu().numpy()) <= 2.0 ** -10      # fp16 store after another add order
     assert lib().raw("sgr_status")(0) == 0
