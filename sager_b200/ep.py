@@ -202,7 +202,8 @@ class EpStack:
         self.x = self.x0.clone()
         self.graph = None
         # route, (push,) plan, experts, (push,) reduce
-        self.launches_per_step = ((4 if self.fused else 6) if self.peer is not None else 4) * len(layers)
+        own_plan = self.padded and layers[0].n_expert <= 256 and tokens * n_used <= 512     # see issue_layer_fused
+        self.launches_per_step = (((3 if own_plan else 4) if self.fused else 6) if self.peer is not None else 4) * len(layers)
         self.n_layers = len(layers)
 
     def _ptr(self, t, off=0):
