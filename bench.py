@@ -481,7 +481,10 @@ def gemv_measure(args, device, shapes=None, sampler=None):
     from sager_b200 import lib, ops, synth
     peak, kind = load_peaks()
     shapes = shapes or [(4096, 2048), (2048, 4096), (512, 2048), (2048, 512), (151936, 2048)]
-    if args.shape:
+    q6_only = args.shape == "q6head"             # profiling captures: only the Q6_K head and its top-k
+    if q6_only:
+        shapes = []
+    elif args.shape:
         shapes = [tuple(int(v) for v in args.shape.split(","))]
     rows_out = []
     ref = None
@@ -538,8 +541,19 @@ def gemv_measure(args, device, shapes=None, sampler=None):
                 row["reference_cuda_us"] = ref_us
                 row["reference_cuda_gbs"] = wbytes / ref_us / 1e3
             rows_out.append(row)
-    q6 = None if args.shape else q6_head_measure(args, device, ops, ref, peak)
+    q6 = q6_head_measure(args, device, ops, ref, peak) if (q6_only or not args.shape) else None
     clocks = sampler.stop() if own_sampler else None
+    if q6_only:
+        return {"metric": "q6k_head_hbm_gbs", "value": q6["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": q6["us"] * 1e-3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "int8 dots, fp32 accumulate", "data": "synthetic",
+                "config": {"workload": "Q6_K LM head 151936 x 2048 at batch 1 and the two-phase top-k of its logits",
+                           "l2": "two weight copies of 255 MB alternate"},
+                "e2e": None, "gpu_launches": args.steps * 18, "clocks": clocks,
+                "roofline": {"kernel": "gemv_q6_stream_kernel (head.cu)", "bound": "hbm", "achieved": q6["gbs"],
+                             "peak": peak, "unit": "GB/s", "frac": q6["frac"],
+                             "peak_source": f"{kind} copy bandwidth (burst)", "traffic": None},
+                "q6k_head": q6}
     head = max((r for r in rows_out if r["batch"] == 1), key=lambda r: r["rows"] * r["k"])
     line = {
         "metric": "q4k_gemv_hbm_gbs", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
@@ -724,7 +738,7 @@ def main():
     ap.add_argument("--chain", action="store_true",
                     help="decode: every layer's input rows are rmsnorm_quant_f16 of the residual its predecessor "
                          "wrote (one more launch per layer) instead of pre-drawn matrices")
-    ap.add_argument("--shape", default=None, help="gemv workload: only this ROWS,K shape; tc workload: ROWS,K,TOKENS (profiling captures)")
+    ap.add_argument("--shape", default=None, help="gemv workload: only this ROWS,K shape, or q6head; tc workload: ROWS,K,TOKENS (profiling captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     LAYERS, TOKENS = args.layers, args.tokens
