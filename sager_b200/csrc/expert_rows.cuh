@@ -320,7 +320,8 @@ __device__ __forceinline__ int build_plan_shared(const LayerDev& L, unsigned cha
 __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev L) {
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  uint64_t* empty = reinterpret_cast<uint64_t*>(smem + 64);
+  uint64_t* empty = reinterpret_cast<uint64_t*>(smem + 64);      // a stage's activation part may be refilled
+  uint64_t* wempty = reinterpret_cast<uint64_t*>(smem + 192);    // a stage's weight part may be refilled
   int* flag = reinterpret_cast<int*>(smem + 128);
   unsigned* grp_cnt = reinterpret_cast<unsigned*>(smem + 256);      // [8] consumer warps done with a group
   Desc* desc = reinterpret_cast<Desc*>(smem + 384);
@@ -335,6 +336,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
     for (int s = 0; s < kStageCount; ++s) {
       mbar_init(&full[s], kFullArrivals);
       mbar_init(&empty[s], kConsumerWarps);
+      mbar_init(&wempty[s], kConsumerWarps);
     }
     for (int i = 0; i < 8; ++i) grp_cnt[i] = 0u;
     *done_tail = 0u;
@@ -510,7 +512,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
       if (!wk.valid) {                           // end of the list: one last stage that only says so
         const int s = q % kStageCount;
         const unsigned ph = (q / kStageCount) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1u)) {
+        if (!mbar_wait(&wempty[s], ph ^ 1u)) {
           if (lane == 0) atomicExch(L.status, 2);
           return;
         }
@@ -540,7 +542,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
       for (int blk = 0; blk < wk.nb; ++blk, ++q) {
       const int s = q % kStageCount;
       const unsigned ph = (q / kStageCount) & 1;
-      if (!mbar_wait(&empty[s], ph ^ 1u)) {
+      if (!mbar_wait(&wempty[s], ph ^ 1u)) {
         if (lane == 0) atomicExch(L.status, 2);
         return;
       }
@@ -743,6 +745,7 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[0][j] = acc[1][j] = 0.f;
     }
+    bool w_released = false;
     if (d_mode == 0) {
       XTile xt;
       xt.qs = reinterpret_cast<int8_t*>(st + kWBytes);
@@ -758,20 +761,35 @@ __global__ void __launch_bounds__(kThreads, 1) expert_rows_kernel(const LayerDev
         return d_kind == 0 ? ((u & 7) + 8 * warp) * kW4 + (u >> 3) * kHalfBytes : (16 * warp + u) * kW4;
       };
       if (d_ntok <= 2) {
+        // the lane's half block goes to registers and the weight part of the stage back to the
+        // weight warp before the arithmetic: its refill is the long round trip of the ring
         float a2[2] = {acc[0][0], acc[0][1]};
-        half_block_dot<2>(reinterpret_cast<const uint4*>(st + row_at(lane >> 1)), lane & 1, xt, d_ntok, a2);
+        uint4 hdr, wq[4];
+        half_block_load(reinterpret_cast<const uint4*>(st + row_at(lane >> 1)), lane & 1, hdr, wq);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&wempty[s]);
+        w_released = true;
+        half_block_dot_regs<2>(hdr, wq, lane & 1, xt, d_ntok, a2);
         acc[0][0] = a2[0];
         acc[0][1] = a2[1];
       } else {
         const unsigned char* a_ptr = st + row_at((lane & 7) + ((lane >> 3) & 1) * 8) + 16 + (lane >> 4) * 16;
         const unsigned char* h_lo = st + row_at(lane >> 2);
         const unsigned char* h_hi = st + row_at((lane >> 2) + 8);
-        if (d_ntok <= 8) warp_mma_block<1>(a_ptr, h_lo, h_hi, xt, acc);
-        else warp_mma_block<2>(a_ptr, h_lo, h_hi, xt, acc);
+        auto loaded = [&]() {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&wempty[s]);
+        };
+        w_released = true;
+        if (d_ntok <= 8) warp_mma_block<1>(a_ptr, h_lo, h_hi, xt, acc, loaded);
+        else warp_mma_block<2>(a_ptr, h_lo, h_hi, xt, acc, loaded);
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[s]);       // this warp no longer reads the stage
+    if (lane == 0) {                             // this warp no longer reads the stage
+      if (!w_released) mbar_arrive(&wempty[s]);
+      mbar_arrive(&empty[s]);
+    }
     if (!d_last) continue;
 
     // ---- the group is complete for this warp's rows ----

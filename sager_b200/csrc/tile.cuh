@@ -302,10 +302,11 @@ __device__ __forceinline__ void warp_mma_rows(const unsigned char* w, int wstrid
 // rows gid and gid + 8). Activations: block 0 of a tile staged with nb == 1 (codes, int16
 // sums and scales; the split sums of the staged layout are not used).
 // Accumulates into acc (same ownership as warp_mma_rows).
-template <int NT, int NACC>
+// `loaded()` runs once the weight bytes are in registers: from then on only the activations are read.
+template <int NT, int NACC, typename Loaded>
 __device__ __forceinline__ void warp_mma_block(const unsigned char* a_ptr, const unsigned char* h_lo,
                                                const unsigned char* h_hi, const XTile& xt,
-                                               float (&acc)[NACC][4]) {
+                                               float (&acc)[NACC][4], Loaded loaded) {
   static_assert(NT <= NACC, "accumulator rows");
   const int lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
@@ -319,6 +320,10 @@ __device__ __forceinline__ void warp_mma_block(const unsigned char* a_ptr, const
   const float m_hi = __half2float(__ushort_as_half(static_cast<uint16_t>(h1.x >> 16)));
   const Scales6 s_lo = unpack_scales6(h0.y, h0.z, h0.w);
   const Scales6 s_hi = unpack_scales6(h1.y, h1.z, h1.w);
+  uint32_t raw[4][4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) ldmatrix_x4(raw[g], a_ptr + g * 32);
+  loaded();
   int isum[NT][4];
 #pragma unroll
   for (int n = 0; n < NT; ++n)
@@ -330,13 +335,11 @@ __device__ __forceinline__ void warp_mma_block(const unsigned char* a_ptr, const
     uint32_t b[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n) ldmatrix_x4(b[n], xt.code_ptr(8 * n + b_tok, 0, 2 * g) + b_off);
-    uint32_t raw[4];
-    ldmatrix_x4(raw, a_ptr + g * 32);
     uint32_t lo[4], hi[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      lo[j] = raw[j] & 0x0F0F0F0Fu;
-      hi[j] = raw[j] & 0xF0F0F0F0u;               // 16 * q: see warp_mma_rows
+      lo[j] = raw[g][j] & 0x0F0F0F0Fu;
+      hi[j] = raw[g][j] & 0xF0F0F0F0u;            // 16 * q: see warp_mma_rows
     }
     const int sh = 16 * (g & 1);
     const int sc0_lo = ((s_lo.sc[g >> 1] >> sh) & 0xFF) << 4, sc1_lo = (s_lo.sc[g >> 1] >> (sh + 8)) & 0xFF;
@@ -381,9 +384,8 @@ __device__ __forceinline__ void warp_mma_block(const unsigned char* a_ptr, const
 // lanes that share the row: the integer sums of the two halves are added across
 // the pair before the one fp32 rounding, so the result equals block_dot's.
 template <int TT>
-__device__ __forceinline__ void half_block_dot(const uint4* wrow, int half, const XTile& xt, int nt,
-                                               float (&acc)[TT]) {
-  const uint4 hdr = wrow[0];
+__device__ __forceinline__ void half_block_dot_regs(const uint4 hdr, const uint4 (&wq)[4], int half, const XTile& xt,
+                                                    int nt, float (&acc)[TT]) {
   const float d = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x & 0xFFFFu)));
   const float dmin = __half2float(__ushort_as_half(static_cast<uint16_t>(hdr.x >> 16)));
   const Scales6 s6 = unpack_scales6(hdr.y, hdr.z, hdr.w);
@@ -395,7 +397,7 @@ __device__ __forceinline__ void half_block_dot(const uint4* wrow, int half, cons
 #pragma unroll
   for (int gg = 0; gg < 2; ++gg) {
     const int g = 2 * half + gg;
-    const uint4 q0 = wrow[1 + 2 * g], q1 = wrow[2 + 2 * g];
+    const uint4 q0 = wq[2 * gg], q1 = wq[2 * gg + 1];
     const uint32_t raw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
     uint32_t lo[8], hi[8];
 #pragma unroll
@@ -424,6 +426,21 @@ __device__ __forceinline__ void half_block_dot(const uint4* wrow, int half, cons
       acc[t] += xt.scale(t, 0) * (d * static_cast<float>(is) - dmin * static_cast<float>(ms));
     }
   }
+}
+
+// The same from shared memory: the lane's half of the block is read first, so a caller that wants
+// to hand the weight bytes back before the arithmetic can use the two steps separately.
+__device__ __forceinline__ void half_block_load(const uint4* wrow, int half, uint4& hdr, uint4 (&wq)[4]) {
+  hdr = wrow[0];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) wq[i] = wrow[1 + 4 * half + i];
+}
+template <int TT>
+__device__ __forceinline__ void half_block_dot(const uint4* wrow, int half, const XTile& xt, int nt,
+                                               float (&acc)[TT]) {
+  uint4 hdr, wq[4];
+  half_block_load(wrow, half, hdr, wq);
+  half_block_dot_regs<TT>(hdr, wq, half, xt, nt, acc);
 }
 
 // Four warps cover the tile: with at least four 16-row groups each warp takes
