@@ -237,12 +237,21 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
       const uintptr_t wa = reinterpret_cast<uintptr_t>(w);
       return (wa & 15u) == 0 ? 16 : ((wa & 3u) == 0 ? 4 : 2);
     };
+    // this thread's whole weight row of an item (nb blocks, contiguous) asked into L2: the loads that
+    // follow an item later find it there instead of waiting for DRAM one block column at a time
+    auto prefetch_row = [&](const unsigned char* p) {
+      const unsigned char* end = p + static_cast<size_t>(nb) * kW4;
+      for (const unsigned char* q = reinterpret_cast<const unsigned char*>(reinterpret_cast<uintptr_t>(p) & ~static_cast<uintptr_t>(127));
+           q < end; q += 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(q));
+    };
     int it = next_item(blockIdx.x, true);
     uint4 cur[9];
     if (it < n_items) {
       const Item I0 = item_at(it);
       const unsigned char* w0 = row_ptr(I0);
       const int a0 = align_of(I0.w);
+      prefetch_row(w0);
 #pragma unroll
       for (int i = 0; i < 9; ++i) cur[i] = load16(w0 + 16 * i, a0);
     }
@@ -258,6 +267,7 @@ grouped_gemm_i8_kernel(const unsigned char* const* __restrict__ w_tab, const int
         const Item In = item_at(it_next);
         wrow_next = row_ptr(In);
         walign_next = align_of(In.w);
+        prefetch_row(wrow_next);
       }
       jw.start(I.m_e, nb);
       int prev_abk = -1;
