@@ -356,7 +356,8 @@ typedef struct sgr_moe_prefill {
   uint16_t* u;              /* [R][n_ff] */
   void* hq;                 /* [R][n_ff/256] Q8_K blocks, 16-byte aligned */
   uint16_t* y_grouped;      /* [R][hidden] */
-  uint16_t* expert_y;       /* [n_max][n_used+1][hidden] combine slab */
+  uint16_t* expert_y;       /* [n_max][n_used+1][hidden] combine slab: used only when x_f16, y_grouped or sh_y is
+                               not 16-byte aligned - otherwise the combine reads the grouped rows in place */
   uint16_t* sh_g;           /* [n_max][n_ff] */
   uint16_t* sh_u;           /* [n_max][n_ff] */
   void* sh_q;               /* [n_max][n_ff/256] Q8_K blocks */

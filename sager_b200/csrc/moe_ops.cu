@@ -56,21 +56,45 @@ dispatch_scan_kernel(const int* __restrict__ idx, float* __restrict__ weight, in
   }
   __syncthreads();
 
-  if (tid == 0) {
-    int acc = 0, tacc = 0;
-    for (int e = 0; e < n_expert; ++e) {
-      off[e] = acc;
-      toff[e] = tacc;
-      fill[e] = acc;
-      acc += hist[e];
-      tacc += (hist[e] + tok_per - 1) / tok_per;
+  // exclusive prefixes of rows and of tiles over the experts: kScanThreads experts per round, scans
+  // inside the warps, the warps' totals and the running totals through shared memory
+  {
+    __shared__ int wsum[2][kScanThreads / 32];
+    __shared__ int carry[2];
+    const int lane = tid & 31, wp = tid >> 5;
+    if (tid == 0) carry[0] = carry[1] = 0;
+    __syncthreads();
+    for (int base = 0; base < n_expert; base += kScanThreads) {
+      const int e = base + tid;
+      const int c = e < n_expert ? hist[e] : 0;
+      const int t = (c + tok_per - 1) / tok_per;
+      int ic = c, it = t;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int uc = __shfl_up_sync(0xFFFFFFFFu, ic, o), ut = __shfl_up_sync(0xFFFFFFFFu, it, o);
+        if (lane >= o) { ic += uc; it += ut; }
+      }
+      if (lane == 31) { wsum[0][wp] = ic; wsum[1][wp] = it; }
+      __syncthreads();
+      int pc = carry[0], pt = carry[1];
+      for (int w = 0; w < wp; ++w) { pc += wsum[0][w]; pt += wsum[1][w]; }
+      if (e < n_expert) {
+        off[e] = pc + ic - c;
+        toff[e] = pt + it - t;
+        fill[e] = pc + ic - c;
+      }
+      __syncthreads();
+      if (tid == kScanThreads - 1) { carry[0] = pc + ic; carry[1] = pt + it; }
+      __syncthreads();
     }
-    off[n_expert] = acc;
-    toff[n_expert] = tacc;
-    meta[0] = acc;
-    meta[1] = tacc;
-    meta[2] = bad_sh;
-    if (mail_n != nullptr) *mail_n = 0;
+    if (tid == 0) {
+      off[n_expert] = carry[0];
+      toff[n_expert] = carry[1];
+      meta[0] = carry[0];
+      meta[1] = carry[1];
+      meta[2] = bad_sh;
+      if (mail_n != nullptr) *mail_n = 0;
+    }
   }
   __syncthreads();
 
