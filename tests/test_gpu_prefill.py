@@ -102,3 +102,27 @@ def test_prefill_chunk_uses_a_strided_pointer_table(chunk):
     lib().call("sgr_moe_layer_prefill", C.byref(a), stream_ptr())
     torch.cuda.synchronize()
     assert torch.equal(ya, yb)
+
+
+def test_prefill_combine_in_place_equals_the_slab_sequence(chunk):
+    """The chunk's tail reads the grouped rows and the shared rows in place when x, the grouped rows and
+    the shared rows are 16-byte aligned; otherwise it runs the reference's own tail (scatter into the
+    [n][K+1][H] slab, strided copy of the shared rows, combine over the slab). Same sums in the same
+    order: shared rows that start 8 bytes off a 16-byte boundary must give the same bits."""
+    import ctypes as C
+    from sager_b200.ops import stream_ptr
+    w, xn, logits = chunk
+    n = 333
+    resid = synth.normal_fp16((n, H), 4242, DEV)
+    layer = PrefillLayer(n, H, F, E, K, DEV)
+    xa, xb = resid.clone(), resid.clone()
+    layer.run(n, xn[:n], xa, w, w.table(), logits=logits[:n])
+    big = torch.empty(n * H + 8, dtype=torch.float16, device=DEV)
+    off = 4 if big.data_ptr() % 16 == 0 else 0          # 8 bytes past a 16-byte boundary
+    layer.sh_y = big[off:off + n * H].view(n, H)
+    assert layer.sh_y.data_ptr() % 16 == 8
+    a = layer.args(n, xn[:n], xb, w, w.table(), logits=logits[:n])
+    lib().call("sgr_moe_layer_prefill", C.byref(a), stream_ptr())
+    torch.cuda.synchronize()
+    assert lib().raw("sgr_status")(0) == 0
+    assert torch.equal(xa, xb)
